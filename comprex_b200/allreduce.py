@@ -1,0 +1,498 @@
+"""Allreduce collectives: AllToOne, Ring, BigRing, dense and compressed
+(reference: include/allreduce.hxx:15-211, src/allreduce.tpp:20-721, Python
+face allreduce.py:143-355).
+
+The reference moves data hop by hop through GaspiEx/ComprEx pairs because its
+transport is point-to-point RDMA.  Behind an NVSwitch every peer is one hop
+away at full bandwidth, so each schedule is re-expressed as direct stores:
+
+* **BigRing** ("everyone gets everyone's whole vector"): one compression whose
+  pairs are stored into all P-1 peers' slots by the same kernel, then one
+  kernel that scatter-adds all received payloads in the order the ring would
+  have delivered them.  Dense: one-shot push + reduce.
+* **Ring** (reduce-scatter + allgather over P chunks; rank r ends up owning
+  chunk (r+1) mod P like the reference): every rank compresses each foreign
+  chunk, with that chunk's residual, straight into the owner's slot; the owner
+  adds them to its dense chunk, re-selects the top-k of the reduced chunk and
+  stores it to all peers; everyone decodes.  Dense: two-shot.
+* **AllToOne**: workers store into the chief's slots, the chief reduces,
+  compresses once and stores to all workers (``writeRemote_sameAs`` of the
+  reference is "one compression, P-1 store streams" here).
+
+All classes keep the reference's surface: ``setup_connections``, ``apply``
+(in place, returns the vector), and for the compressed ones ``flush``,
+``reset``, ``set_compression_ratio``, ``getSize``.  Additions: ``dtype`` for
+bf16/fp16 vectors, ``consistent=True`` (every rank, the sender included,
+applies only what was transmitted, so replicas stay bit-identical),
+``state_dict``/``load_state_dict`` for the residuals, ``stats``.
+
+``apply`` is split into phases (``_plan_apply``) so that a
+:class:`~comprex_b200.parallel.env.LoopbackWorld` can run P virtual ranks on
+one device.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+from ._lib import ComprexError
+from .GaspiEx import to_device_vector, write_back
+from .ops import primitives as P
+
+
+def _chunks(size: int, nranks: int):
+    """Chunk sizes and starts of the ring (src/allreduce.tpp:279-295)."""
+    base, rem = divmod(size, nranks)
+    sizes = [base + (1 if i < rem else 0) for i in range(nranks)]
+    starts = [0] * nranks
+    for i in range(1, nranks):
+        starts[i] = starts[i - 1] + sizes[i - 1]
+    return sizes, starts
+
+
+def _cap_for(n: int, size_factor: float) -> int:
+    """Pair capacity of a buffer of n*4*size_factor bytes (src/comprEx.tpp:61)."""
+    return max(int(n * 4 * size_factor - 8) // 8, 1)
+
+
+class _AllreduceBase:
+    compressed = False
+
+    def __init__(self, gaspi_env):
+        self._env = gaspi_env.get()
+        self.gaspi_env = gaspi_env
+        self.size = None
+        self._step = 0
+
+    def get(self):
+        return self
+
+    def getSize(self):
+        return self.size
+
+    def _setup_common(self, size: int, dtype: torch.dtype) -> None:
+        if self.size is not None:
+            raise ComprexError("connections are already set up")
+        self.size = int(size)
+        self.dtype = dtype
+        self._status = self._env.new_status(type(self).__name__)
+        self._counters = self._env.scratch(64)
+
+    def _prep(self, vector):
+        if self.size is None:
+            raise ComprexError("setup_connections was not called")
+        n = vector.size if hasattr(vector, "size") and not callable(vector.size) else vector.numel()
+        if n != self.size:
+            raise ComprexError("Allreduce input vector of size %d does not match allreduce size %d!" % (n, self.size))
+        t, orig = to_device_vector(self._env, vector)
+        return t, orig
+
+    def _run(self, plan, t, orig, vector):
+        for phase in plan:
+            phase()
+        self._env.maybe_check()
+        write_back(t, orig)
+        return vector
+
+    def apply(self, vector):
+        """In-place allreduce of ``vector``; returns it (allreduce.py:159-166)."""
+        t, orig = self._prep(vector)
+        return self._run(self._plan_apply(t), t, orig, vector)
+
+    __call__ = apply
+
+
+# =====================================================================================
+# dense variants
+# =====================================================================================
+class AllToOneAllreduce(_AllreduceBase):
+    """Workers -> chief -> workers (src/allreduce.tpp:29-118)."""
+
+    def setup_connections(self, size, tag=0, chiefRank=0, dtype=torch.float32):
+        self._setup_common(size, dtype)
+        env, nb = self._env, size * torch.empty(0, dtype=dtype).element_size()
+        self.chiefRank = int(chiefRank)
+        self._rs = [[P.DenseSlot.create(env, nb) for _ in range(2)] for _ in range(env.ranks)]
+        self._bc = [P.DenseSlot.create(env, nb) for _ in range(2)]
+
+    def _plan_apply(self, t):
+        env, me, chief = self._env, self._env.rank, self.chiefRank
+        self._step += 1
+        seq, par = self._step, self._step & 1
+        workers = [r for r in range(env.ranks) if r != chief]
+
+        def send():
+            if me != chief:
+                P.dense_send(env, t, None, self.size, seq, P.make_targets([self._rs[me][par].endpoint(env, chief)]),
+                             self._counters)
+
+        def reduce():
+            if me == chief:
+                src = P.make_sources([self._rs[w][par].endpoint(env) for w in workers], [seq] * len(workers))
+                push = P.make_targets([self._bc[par].endpoint(env, w) for w in workers])
+                P.dense_reduce(env, t, t, self.size, src, self._status, push=push, push_seq=seq,
+                               counters=self._counters)
+
+        def recv():
+            if me != chief:
+                P.dense_reduce(env, t, None, self.size, P.make_sources([self._bc[par].endpoint(env)], [seq]),
+                               self._status)
+        return [send, reduce, recv]
+
+
+class RingAllreduce(_AllreduceBase):
+    """Reduce-scatter + allgather over P chunks (src/allreduce.tpp:273-351), two-shot."""
+
+    def setup_connections(self, size, tag=0, dtype=torch.float32):
+        self._setup_common(size, dtype)
+        env = self._env
+        self.segment_sizes, self.segment_starts = _chunks(size, env.ranks)
+        nb = max(self.segment_sizes) * torch.empty(0, dtype=dtype).element_size()
+        self._rs = [[P.DenseSlot.create(env, nb) for _ in range(2)] for _ in range(env.ranks)]
+        self._ag = [[P.DenseSlot.create(env, nb) for _ in range(2)] for _ in range(env.ranks)]
+
+    def _owner(self, chunk: int) -> int:
+        return (chunk - 1) % self._env.ranks
+
+    def _plan_apply(self, t):
+        env, me, nr = self._env, self._env.rank, self._env.ranks
+        self._step += 1
+        seq, par = self._step, self._step & 1
+        mine = (me + 1) % nr
+        others = [c for c in range(nr) if c != mine]
+        peers = [r for r in range(nr) if r != me]
+        my_view = t[self.segment_starts[mine]: self.segment_starts[mine] + self.segment_sizes[mine]]
+
+        def scatter():
+            if nr == 1:
+                return
+            tg = P.make_targets([self._rs[me][par].endpoint(env, self._owner(c)) for c in others])
+            P.dense_send(env, t, None, self.size, seq, tg, self._counters,
+                         ranges=[(self.segment_starts[c], self.segment_sizes[c]) for c in others])
+
+        def reduce():
+            if nr == 1:
+                return
+            src = P.make_sources([self._rs[j][par].endpoint(env) for j in peers], [seq] * len(peers))
+            push = P.make_targets([self._ag[me][par].endpoint(env, j) for j in peers])
+            P.dense_reduce(env, my_view, my_view, self.segment_sizes[mine], src, self._status, push=push,
+                           push_seq=seq, counters=self._counters)
+
+        def gather():
+            if nr == 1:
+                return
+            src = P.make_sources([self._ag[j][par].endpoint(env) for j in peers], [seq] * len(peers))
+            rg = [(self.segment_starts[(j + 1) % nr], self.segment_sizes[(j + 1) % nr]) for j in peers]
+            P.dense_reduce(env, t, None, self.size, src, self._status, ranges=rg)
+        return [scatter, reduce, gather]
+
+
+class BigRingAllreduce(_AllreduceBase):
+    """Every rank receives every other rank's whole vector (src/allreduce.tpp:542-601), one-shot."""
+
+    def setup_connections(self, size, tag=0, dtype=torch.float32):
+        self._setup_common(size, dtype)
+        env, nb = self._env, size * torch.empty(0, dtype=dtype).element_size()
+        self._slots = [[P.DenseSlot.create(env, nb) for _ in range(2)] for _ in range(env.ranks)]
+
+    def _plan_apply(self, t):
+        env, me, nr = self._env, self._env.rank, self._env.ranks
+        self._step += 1
+        seq, par = self._step, self._step & 1
+        arrival = [(me - k) % nr for k in range(1, nr)]  # the order the ring delivers in
+
+        def send():
+            if nr > 1:
+                tg = P.make_targets([self._slots[me][par].endpoint(env, r) for r in range(nr) if r != me])
+                P.dense_send(env, t, None, self.size, seq, tg, self._counters)
+
+        def reduce():
+            if nr > 1:
+                src = P.make_sources([self._slots[j][par].endpoint(env) for j in arrival], [seq] * len(arrival))
+                P.dense_reduce(env, t, t, self.size, src, self._status)
+        return [send, reduce]
+
+
+# =====================================================================================
+# compressed variants
+# =====================================================================================
+class _ComprexAllreduceBase(_AllreduceBase):
+    compressed = True
+
+    def _setup_compressed(self, size, compression_ratio, size_factor, consistent):
+        self._setup_common(size, torch.float32)
+        self.compression_ratio = float(compression_ratio)
+        self.size_factor = float(size_factor)
+        self.consistent = bool(consistent)
+        # sampling of the reduce-side threshold (src/allreduce.tpp:401-403, 625-627)
+        self._subsamples = 1000 // self._env.ranks
+        self._sample_factor = 4.0
+
+    def set_compression_ratio(self, compression_ratio):
+        """Change top-k for later calls.  The ring-specific sampling parameters are
+        kept (the reference silently falls back to the defaults here)."""
+        self.compression_ratio = float(compression_ratio)
+
+    def reset(self):
+        for r in self._residuals():
+            r.zero_()
+
+    def flush(self, vector):
+        """Drain all residuals into ``vector`` (see each class) and reset them."""
+        t, orig = self._prep(vector)
+        return self._run(self._plan_flush(t), t, orig, vector)
+
+    def state_dict(self):
+        return {"size": self.size, "ratio": self.compression_ratio, "step": self._step,
+                "world_size": self._env.ranks, "rank": self._env.rank, "kind": type(self).__name__,
+                "residuals": [r.detach().cpu().clone() for r in self._residuals()]}
+
+    def load_state_dict(self, state):
+        if state["size"] != self.size or state["kind"] != type(self).__name__:
+            raise ComprexError("state_dict belongs to a different allreduce")
+        self.compression_ratio = state["ratio"]
+        for dst, src in zip(self._residuals(), state["residuals"]):
+            dst.copy_(src.to(dst.device))
+
+    def stats(self):
+        """nnz / threshold / overflow of this rank's last compression (synchronises)."""
+        return self._comp.last_stats()
+
+    def _flush_rounds(self, n, cap):
+        return max(1, math.ceil(n / cap))
+
+
+class Comprex_BigRingAllreduce(_ComprexAllreduceBase):
+    """Top-k of (vector + residual) from every rank to every rank
+    (src/allreduce.tpp:616-721).
+
+    Reference semantics (default): rank r ends with its own dense vector plus
+    the sparse contributions of all peers, added in ring arrival order.
+    ``consistent=True``: every rank ends with exactly the sum of all sparse
+    contributions (its own included), identical bits everywhere.
+    """
+
+    def setup_connections(self, size, tag=0, compression_ratio=0.01, size_factor=1.0, consistent=False):
+        self._setup_compressed(size, compression_ratio, size_factor, consistent)
+        env = self._env
+        self.cap = _cap_for(size, size_factor)
+        self._slots = [[P.SparseSlot.create(env, size, self.cap) for _ in range(2)] for _ in range(env.ranks)]
+        self._comp = P.Compressor(env, size)
+        self.rests = torch.zeros(size, dtype=torch.float32, device=env.device)
+
+    def _residuals(self):
+        return [self.rests]
+
+    def _order(self):
+        me, nr = self._env.rank, self._env.ranks
+        return list(range(nr)) if self.consistent else [(me - k) % nr for k in range(1, nr)]
+
+    def _send_targets(self, par):
+        env, me = self._env, self._env.rank
+        dests = [r for r in range(env.ranks) if r != me or self.consistent]
+        return P.make_targets([self._slots[me][par].endpoint(env, r) for r in dests])
+
+    def _plan_common(self, t, g, fixed_thr, rounds=1):
+        env = self._env
+        phases = []
+        for _ in range(rounds):
+            self._step += 1
+            seq, par = self._step, self._step & 1
+
+            def send(seq=seq, par=par):
+                if env.ranks == 1 and not self.consistent:
+                    return
+                if fixed_thr is None:
+                    self._comp.threshold_topk(g, self.rests, self.size, self.compression_ratio, self._subsamples,
+                                              self._sample_factor)
+                else:
+                    self._comp.set_threshold(fixed_thr)
+                self._comp.compress(g, self.rests, self.size, self.cap, seq, self._send_targets(par))
+
+            def recv(seq=seq, par=par, first=(_ == 0)):
+                order = self._order()
+                if not order:
+                    return
+                src = P.make_sources([self._slots[j][par].endpoint(env) for j in order], [seq] * len(order))
+                args = P.args_set(t) if (self.consistent and first) else P.args_add(t)
+                P.apply_sparse(env, src, self.size, args, self._status)
+            phases += [send, recv]
+        return phases
+
+    def _plan_apply(self, t):
+        return self._plan_common(t, t, None)
+
+    def _plan_flush(self, t):
+        """Every rank sends its whole residual; ``vector`` gains the peers' (and, when
+        consistent, is replaced by everyone's) residuals; residuals end up zero."""
+        return self._plan_common(t, None, 0.0, rounds=self._flush_rounds(self.size, self.cap))
+
+
+class Comprex_RingAllreduce(_ComprexAllreduceBase):
+    """Compressed reduce-scatter to the chunk owners, compressed allgather back
+    (src/allreduce.tpp:366-528).
+
+    Rank r owns chunk (r+1) mod P and keeps it dense.  Each rank holds one
+    residual per chunk it sends (kept as one full-length tensor).  The
+    allgather sends top-k of the reduced chunk; with ``owner_residual=False``
+    (reference behaviour, ``writeRemote_NoResidual``) the remainder is dropped,
+    with ``True`` the owner accumulates it for the next call.
+    """
+
+    def setup_connections(self, size, tag=0, compression_ratio=0.01, size_factor=1.0, consistent=False,
+                          owner_residual=False):
+        self._setup_compressed(size, compression_ratio, size_factor, consistent)
+        env = self._env
+        self.owner_residual = bool(owner_residual)
+        self.segment_sizes, self.segment_starts = _chunks(size, env.ranks)
+        nmax = max(max(self.segment_sizes), 1)
+        self.cap = _cap_for(nmax, size_factor)
+        self._rs = [[P.SparseSlot.create(env, nmax, self.cap) for _ in range(2)] for _ in range(env.ranks)]
+        self._ag = [[P.SparseSlot.create(env, nmax, self.cap) for _ in range(2)] for _ in range(env.ranks)]
+        self._comp = P.Compressor(env, nmax)
+        self.rests = torch.zeros(size, dtype=torch.float32, device=env.device)
+        self.owner_rests = torch.zeros(nmax, dtype=torch.float32, device=env.device) if owner_residual else None
+
+    def _residuals(self):
+        return [self.rests] + ([self.owner_rests] if self.owner_rests is not None else [])
+
+    def _owner(self, chunk):
+        return (chunk - 1) % self._env.ranks
+
+    def _view(self, t, c):
+        return t[self.segment_starts[c]: self.segment_starts[c] + self.segment_sizes[c]]
+
+    def _plan_ring(self, t, flush, rounds=1):
+        env, me, nr = self._env, self._env.rank, self._env.ranks
+        mine = (me + 1) % nr
+        others = [c for c in range(nr) if c != mine]
+        peers = [r for r in range(nr) if r != me]
+        phases = []
+        for rnd in range(rounds):
+            self._step += 1
+            seq, par = self._step, self._step & 1
+
+            def scatter(seq=seq, par=par):
+                for c in others:
+                    n = self.segment_sizes[c]
+                    g, r = (None if flush else self._view(t, c)), self._view(self.rests, c)
+                    if flush:
+                        self._comp.set_threshold(0.0)
+                    else:
+                        self._comp.threshold_topk(g, r, n, self.compression_ratio, self._subsamples, self._sample_factor)
+                    self._comp.compress(g, r, n, self.cap, seq,
+                                        P.make_targets([self._rs[me][par].endpoint(env, self._owner(c))]))
+
+            def reduce(seq=seq, par=par, last=(rnd == rounds - 1)):
+                if nr == 1:
+                    return
+                n = self.segment_sizes[mine]
+                mv = self._view(t, mine)
+                src = P.make_sources([self._rs[j][par].endpoint(env) for j in peers], [seq] * len(peers))
+                P.apply_sparse(env, src, n, P.args_add(mv), self._status)
+                if flush and not last:
+                    return  # more residual rounds follow; broadcast once at the end
+                r = None
+                if flush:
+                    self._comp.set_threshold(0.0)
+                else:
+                    r = self.owner_rests[:n] if self.owner_rests is not None else None
+                    self._comp.threshold_topk(mv, r, n, self.compression_ratio)
+                self._comp.compress(mv, r, n, self.cap, seq,
+                                    P.make_targets([self._ag[me][par].endpoint(env, j) for j in peers]))
+
+            def gather(seq=seq, par=par, last=(rnd == rounds - 1)):
+                if flush and not last:
+                    return
+                for j in peers:
+                    c = (j + 1) % nr
+                    src = P.make_sources([self._ag[j][par].endpoint(env)], [seq])
+                    P.apply_sparse(env, src, self.segment_sizes[c], P.args_set(self._view(t, c)), self._status)
+            phases += [scatter, reduce, gather]
+        return phases
+
+    def _plan_apply(self, t):
+        return self._plan_ring(t, flush=False)
+
+    def _plan_flush(self, t):
+        """Owners receive all residuals of their chunk uncompressed-by-threshold and
+        everyone ends with the owners' exact chunks (src/allreduce.tpp:459-508).  When the
+        slots are smaller than a full chunk, the last allgather carries the top ``cap``
+        entries by index only; size the slots with ``size_factor > 2`` for an exact flush."""
+        plan = self._plan_ring(t, flush=True, rounds=self._flush_rounds(max(self.segment_sizes), self.cap))
+        return plan + [self.reset]
+
+
+class Comprex_AllToOneAllreduce(_ComprexAllreduceBase):
+    """Compressed gather to a chief and compressed broadcast back
+    (src/allreduce.tpp:133-258).
+
+    The chief accumulates densely; the broadcast has its own residual so that
+    what the chief's sum loses to the threshold is sent later.  Workers'
+    vectors are overwritten with the sparse broadcast.  The reference sends
+    both legs one call late (FastComprEx double buffering); here both legs are
+    fresh, ``FastComprex`` offers the stale behaviour as an engine.
+    ``flush`` drains the workers' residuals into the chief and does not
+    broadcast, like the reference.
+    """
+
+    def setup_connections(self, size, tag=0, chiefRank=0, compression_ratio=0.01, size_factor=1.0):
+        self._setup_compressed(size, compression_ratio, size_factor, False)
+        env = self._env
+        self.chiefRank = int(chiefRank)
+        self._subsamples, self._sample_factor = 1000, 10.0  # default sampling (src/allreduce.tpp:142)
+        self.cap = _cap_for(size, size_factor)
+        self._rs = [[P.SparseSlot.create(env, size, self.cap) for _ in range(2)] for _ in range(env.ranks)]
+        self._bc = [P.SparseSlot.create(env, size, self.cap) for _ in range(2)]
+        self._comp = P.Compressor(env, size)
+        self.rests = torch.zeros(size, dtype=torch.float32, device=env.device)
+
+    def _residuals(self):
+        return [self.rests]
+
+    def _plan_common(self, t, flush, rounds=1):
+        env, me, chief = self._env, self._env.rank, self.chiefRank
+        workers = [r for r in range(env.ranks) if r != chief]
+        phases = []
+        for _ in range(rounds):
+            self._step += 1
+            seq, par = self._step, self._step & 1
+
+            def send(seq=seq, par=par):
+                if me == chief:
+                    return
+                if flush:
+                    self._comp.set_threshold(0.0)
+                else:
+                    self._comp.threshold_topk(t, self.rests, self.size, self.compression_ratio,
+                                              self._subsamples, self._sample_factor)
+                self._comp.compress(None if flush else t, self.rests, self.size, self.cap, seq,
+                                    P.make_targets([self._rs[me][par].endpoint(env, chief)]))
+
+            def reduce(seq=seq, par=par):
+                if me != chief or not workers:
+                    return
+                src = P.make_sources([self._rs[w][par].endpoint(env) for w in workers], [seq] * len(workers))
+                P.apply_sparse(env, src, self.size, P.args_add(t), self._status)
+                if flush:
+                    return
+                self._comp.threshold_topk(t, self.rests, self.size, self.compression_ratio,
+                                          self._subsamples, self._sample_factor)
+                self._comp.compress(t, self.rests, self.size, self.cap, seq,
+                                    P.make_targets([self._bc[par].endpoint(env, w) for w in workers]))
+
+            def recv(seq=seq, par=par):
+                if me == chief or flush:
+                    return
+                P.apply_sparse(env, P.make_sources([self._bc[par].endpoint(env)], [seq]), self.size,
+                               P.args_set(t), self._status)
+            phases += [send, reduce, recv]
+        return phases
+
+    def _plan_apply(self, t):
+        return self._plan_common(t, flush=False)
+
+    def _plan_flush(self, t):
+        return self._plan_common(t, True, rounds=self._flush_rounds(self.size, self.cap)) + [self.reset]

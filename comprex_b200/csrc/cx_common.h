@@ -1,0 +1,228 @@
+// Shared host/device types of the comprex_b200 native runtime.
+//
+// Everything that crosses the C ABI (ctypes on the Python side) is a plain C
+// struct declared here.  The wire layout of a receive slot is
+//
+//   [CxHeader 64 B][prefix: (nsub_max+1) x u32, padded to 16 B][pairs: cap x {i32 idx, f32 val}]
+//
+// for sparse payloads (the IndexPairs codec of the reference,
+// src/compressor.hxx:539-661, plus a per-1024-element offset table that the
+// single-pass ordered compaction produces for free), and
+//
+//   [CxHeader 64 B][n x T]
+//
+// for dense payloads (GaspiEx / CompressorNone, src/gaspiEx.tpp:70-98).
+// CxHeader::seq is the notification: it is written last with release
+// semantics at system scope and polled with acquire semantics by the consumer.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CX_MAX_PEERS 16
+#define CX_TILE 4096      /* elements one CTA compacts per look-back step */
+#define CX_SUBTILE 1024   /* granularity of the prefix table on the wire   */
+#define CX_SUBS_PER_TILE (CX_TILE / CX_SUBTILE)
+
+/* device kinds */
+#define CX_DEV_HOST 0
+#define CX_DEV_CUDA 1
+
+/* element types of user vectors */
+#define CX_F32 0
+#define CX_BF16 1
+#define CX_F16 2
+
+/* payload kinds */
+#define CX_KIND_NONE 0
+#define CX_KIND_PAIRS 1
+#define CX_KIND_DENSE 2
+#define CX_KIND_RLE 3
+#define CX_KIND_ERROR 0xBAD
+
+/* status bits (OR-ed into a status word the host reads after a sync) */
+#define CX_OK 0u
+#define CX_ST_TIMEOUT 1u
+#define CX_ST_BAD_HEADER 2u
+#define CX_ST_OVERFLOW 4u   /* soft: survivors beyond capacity stayed in the residual */
+#define CX_ST_BAD_INDEX 8u
+#define CX_ST_LOOKBACK 16u  /* intra-kernel look-back wait ran out */
+
+/* apply ops */
+#define CX_OP_ADD 0       /* out += scale * sum(payloads)                         */
+#define CX_OP_SET 1       /* out  = scale * sum(payloads), zero elsewhere          */
+#define CX_OP_SGD 2       /* w = (1-wd)*w - scale*sum                              */
+#define CX_OP_MOMENTUM 3  /* mom = mu*mom + lr*scale*sum ; w = (1-wd)*w - mom      */
+#define CX_OP_ADAMW 4     /* g = scale*sum ; decoupled-weight-decay Adam           */
+
+typedef struct CxHeader {
+  uint64_t seq;        /* notification, written last                      */
+  uint64_t bytes;      /* payload bytes in the reference's sense           */
+  uint32_t n;          /* dense length of the vector                        */
+  uint32_t nnz;        /* pairs stored (<= capacity)                        */
+  uint32_t nnz_found;  /* survivors found (> nnz when capacity was hit)     */
+  uint32_t kind;
+  float threshold;
+  uint32_t nsub;
+  uint32_t src_rank;
+  uint32_t dtype;
+  uint32_t pad[4];
+} CxHeader;
+
+typedef struct CxPair {
+  int32_t idx;
+  uint32_t val;  /* bit pattern of the f32 (or i32) value */
+} CxPair;
+
+typedef struct CxEndpoint {
+  CxHeader* hdr;
+  uint32_t* prefix;
+  CxPair* pairs;  /* for dense slots: start of the n x T data region */
+} CxEndpoint;
+
+typedef struct CxTargets {
+  int32_t count;
+  int32_t pad;
+  CxEndpoint ep[CX_MAX_PEERS];
+} CxTargets;
+
+typedef struct CxSources {
+  int32_t count;
+  int32_t pad;
+  CxEndpoint ep[CX_MAX_PEERS];
+  uint64_t seq[CX_MAX_PEERS];  /* wait until hdr->seq >= seq[j] */
+} CxSources;
+
+/* scratch of one compressor: counters first, then one status word per tile */
+typedef struct CxWorkCounters {
+  uint32_t next_tile;
+  uint32_t done;
+  uint32_t nnz_found;
+  uint32_t error;
+  uint32_t pad[12];
+} CxWorkCounters;
+
+/* per-call statistics a kernel leaves behind (device or pinned memory) */
+typedef struct CxStats {
+  uint32_t n;
+  uint32_t nnz;
+  uint32_t nnz_found;
+  uint32_t status;
+  float threshold;
+  uint32_t pad[3];
+} CxStats;
+
+typedef struct CxApplyArgs {
+  int32_t op;
+  int32_t out_dtype;   /* CX_F32 / CX_BF16 / CX_F16 for ADD and SET */
+  void* out;           /* destination or f32 master weights            */
+  void* shadow;        /* optional low-precision copy of the weights   */
+  int32_t shadow_dtype;
+  int32_t pad;
+  float* m;
+  float* v;
+  float scale;
+  float lr;
+  float beta1;
+  float beta2;
+  float eps;
+  float wd;
+  float bc1;           /* 1 - beta1^t */
+  float bc2;           /* 1 - beta2^t */
+  float momentum;
+  float pad2;
+} CxApplyArgs;
+
+/* ---- exported C ABI ------------------------------------------------- */
+
+const char* cx_last_error(void);
+uint64_t cx_launch_count(void);
+void cx_reset_launch_count(void);
+int cx_version(void);
+
+/* bytes of scratch a compressor over n elements needs */
+int64_t cx_workspace_bytes(int64_t n);
+
+/* ThresholdTopK (src/threshold.hxx:127-242): writes |x|-threshold of the
+ * strided sample of (r + g) (either may be NULL) to *thr_out (device memory
+ * on CUDA). */
+int cx_threshold_topk(int dev, int gdtype, const void* g, const float* r,
+                      int64_t n, float ratio, int default_subsamples,
+                      float subsample_factor, float* thr_out, void* stream);
+
+/* IndexPairs compress_add_update / compress_update / compress
+ * (src/compressor.hxx:556-611) fused with the transfer: survivors are
+ * stored into every target slot, the residual is updated in the same pass,
+ * the notification is published by the last CTA. */
+int cx_compress(int dev, int gdtype, const void* g, float* r, int64_t n,
+                const float* thr, uint32_t cap, uint64_t seq,
+                const CxTargets* tg, void* workspace, int64_t ws_bytes,
+                CxStats* stats, uint32_t src_rank, void* stream);
+
+/* IndexPairs decompress / add (src/compressor.hxx:613-658) fused with the
+ * wait, the averaging and the parameter update. */
+int cx_apply(int dev, const CxSources* src, int64_t n, const CxApplyArgs* a,
+             uint32_t* status, uint64_t timeout_ns, void* stream);
+
+/* copy a received sparse slot verbatim into other slots (forward_buffer /
+ * readRemote_forward, src/comprEx.tpp:248-301); counters: one zeroed
+ * CxWorkCounters in device memory */
+int cx_forward(int dev, const CxEndpoint* from, uint64_t expect_seq,
+               const CxTargets* tg, uint64_t seq, uint32_t cap, void* counters,
+               uint32_t* status, uint64_t timeout_ns, void* stream);
+
+/* dense p2p (src/gaspiEx.tpp:70-119; CompressorNone src/compressor.hxx:84-151).
+ * With starts/lens, target k receives g[starts[k] .. starts[k]+lens[k]). */
+int cx_dense_send(int dev, int dtype, const void* g, float* r, int64_t n,
+                  uint64_t seq, const CxTargets* tg, const int64_t* starts,
+                  const int64_t* lens, void* counters, uint32_t src_rank,
+                  void* stream);
+/* out = scale * (own? + sum over sources, in source order); optional push of
+ * the result into further slots (chief broadcast / two-shot second phase).
+ * With starts/lens (gather mode) source j is copied to out[starts[j]..). */
+int cx_dense_reduce(int dev, int dtype, void* out, const void* own, int64_t n,
+                    const CxSources* src, float scale, const CxTargets* push,
+                    uint64_t push_seq, const int64_t* starts,
+                    const int64_t* lens, void* counters, uint32_t src_rank,
+                    uint32_t* status, uint64_t timeout_ns, void* stream);
+
+/* small elementwise helpers of the engines and the optimizer */
+int cx_axpy(int dev, int ydtype, void* y, int xdtype, const void* x, float a,
+            int64_t n, void* stream); /* y += a*x */
+int cx_fill_zero(int dev, void* p, int64_t bytes, void* stream);
+
+/* RLE codec (corrected restatement of src/compressor.hxx:159-532), host */
+int64_t cx_rle_compress_host(const float* g, float* r, int64_t n, float thr,
+                             void* out, int64_t out_bytes);
+int cx_rle_decode_host(const void* in, int64_t in_bytes, float* out, int64_t n,
+                       int add);
+
+/* ---- runtime: heaps ---------------------------------------------------- */
+int cx_cuda_device_count(void);
+int cx_cuda_set_device(int dev);
+void* cx_cuda_malloc(int64_t bytes);
+int cx_cuda_free(void* p);
+int cx_cuda_ipc_get(void* p, void* handle64);            /* 64-byte handle out */
+void* cx_cuda_ipc_open(const void* handle64);
+int cx_cuda_ipc_close(void* p);
+int cx_cuda_can_access_peer(int dev, int peer);
+void* cx_pinned_alloc(int64_t bytes, void** device_ptr); /* mapped host memory */
+int cx_pinned_free(void* p);
+int cx_cuda_stream_sync(void* stream);
+int cx_cuda_memcpy(void* dst, const void* src, int64_t bytes, int kind, void* stream);
+
+void* cx_shm_create(const char* name, int64_t bytes);    /* host ranks */
+void* cx_shm_open(const char* name, int64_t bytes);
+int cx_shm_close(void* p, int64_t bytes);
+int cx_shm_unlink(const char* name);
+void* cx_host_alloc(int64_t bytes);
+int cx_host_free(void* p);
+
+/* bounded wait on a header from the host (status in the return value) */
+int cx_host_wait_seq(const CxHeader* hdr, uint64_t seq, uint64_t timeout_ns);
+
+#ifdef __cplusplus
+}
+#endif

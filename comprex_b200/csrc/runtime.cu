@@ -1,0 +1,241 @@
+// C ABI of the native runtime: error reporting, launch accounting, the
+// host/CUDA dispatch of every primitive, and the memory runtime that stands in
+// for the reference's GASPI segment (include/gaspiEnvironment.hxx:9-28):
+// device segments shared between processes through CUDA IPC handles, POSIX
+// shared-memory segments for host ranks, and pinned mapped memory for the
+// status words kernels write and the host reads without a copy.
+#include <cuda_runtime.h>
+#include <errno.h>
+#include <fcntl.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <atomic>
+
+#include "cx_common.h"
+
+// ---- forward declarations of the two back ends --------------------------------
+int cx_threshold_topk_cuda(int, const void*, const float*, int64_t, float, int, float, float*, void*);
+int cx_threshold_topk_host(int, const void*, const float*, int64_t, float, int, float, float*);
+int cx_compress_cuda(int, const void*, float*, int64_t, const float*, uint32_t, uint64_t,
+                     const CxTargets*, void*, int64_t, CxStats*, uint32_t, void*);
+int cx_compress_host(int, const void*, float*, int64_t, const float*, uint32_t, uint64_t,
+                     const CxTargets*, CxStats*, uint32_t);
+int cx_apply_cuda(const CxSources*, int64_t, const CxApplyArgs*, uint32_t*, uint64_t, void*);
+int cx_apply_host(const CxSources*, int64_t, const CxApplyArgs*, uint32_t*, uint64_t);
+int cx_forward_cuda(const CxEndpoint*, uint64_t, const CxTargets*, uint64_t, uint32_t, void*,
+                    uint32_t*, uint64_t, void*);
+int cx_forward_host(const CxEndpoint*, uint64_t, const CxTargets*, uint64_t, uint32_t, uint32_t*,
+                    uint64_t);
+int cx_dense_send_cuda(int, const void*, float*, int64_t, uint64_t, const CxTargets*, const int64_t*,
+                       const int64_t*, void*, uint32_t, void*);
+int cx_dense_send_host(int, const void*, float*, int64_t, uint64_t, const CxTargets*, const int64_t*,
+                       const int64_t*, uint32_t);
+int cx_dense_reduce_cuda(int, void*, const void*, int64_t, const CxSources*, float, const CxTargets*,
+                         uint64_t, const int64_t*, const int64_t*, void*, uint32_t, uint32_t*,
+                         uint64_t, void*);
+int cx_dense_reduce_host(int, void*, const void*, int64_t, const CxSources*, float, const CxTargets*,
+                         uint64_t, const int64_t*, const int64_t*, uint32_t, uint32_t*, uint64_t);
+int cx_axpy_cuda(int, void*, int, const void*, float, int64_t, void*);
+int cx_axpy_host(int, void*, int, const void*, float, int64_t);
+
+// ---- errors and accounting -------------------------------------------------------
+static thread_local char g_err[512] = "";
+static std::atomic<uint64_t> g_launches{0};
+
+int cx_set_error(const char* where, int cuda_err) {
+  if (cuda_err)
+    snprintf(g_err, sizeof(g_err), "%s: %s", where, cudaGetErrorString((cudaError_t)cuda_err));
+  else
+    snprintf(g_err, sizeof(g_err), "%s", where);
+  return cuda_err ? -cuda_err : -1;
+}
+void cx_note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+int cx_check_launch(const char* where) {
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : cx_set_error(where, (int)e);
+}
+int cx_sm_count() {
+  static int sms[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!sms[dev]) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    sms[dev] = v;
+  }
+  return sms[dev];
+}
+
+extern "C" {
+
+const char* cx_last_error(void) { return g_err; }
+uint64_t cx_launch_count(void) { return g_launches.load(); }
+void cx_reset_launch_count(void) { g_launches.store(0); }
+int cx_version(void) { return 1; }
+
+int cx_threshold_topk(int dev, int gdtype, const void* g, const float* r, int64_t n, float ratio,
+                      int default_subsamples, float subsample_factor, float* thr_out, void* stream) {
+  return dev == CX_DEV_CUDA
+             ? cx_threshold_topk_cuda(gdtype, g, r, n, ratio, default_subsamples, subsample_factor, thr_out, stream)
+             : cx_threshold_topk_host(gdtype, g, r, n, ratio, default_subsamples, subsample_factor, thr_out);
+}
+
+int cx_compress(int dev, int gdtype, const void* g, float* r, int64_t n, const float* thr,
+                uint32_t cap, uint64_t seq, const CxTargets* tg, void* workspace, int64_t ws_bytes,
+                CxStats* stats, uint32_t src_rank, void* stream) {
+  return dev == CX_DEV_CUDA
+             ? cx_compress_cuda(gdtype, g, r, n, thr, cap, seq, tg, workspace, ws_bytes, stats, src_rank, stream)
+             : cx_compress_host(gdtype, g, r, n, thr, cap, seq, tg, stats, src_rank);
+}
+
+int cx_apply(int dev, const CxSources* src, int64_t n, const CxApplyArgs* a, uint32_t* status,
+             uint64_t timeout_ns, void* stream) {
+  return dev == CX_DEV_CUDA ? cx_apply_cuda(src, n, a, status, timeout_ns, stream)
+                            : cx_apply_host(src, n, a, status, timeout_ns);
+}
+
+int cx_forward(int dev, const CxEndpoint* from, uint64_t expect_seq, const CxTargets* tg,
+               uint64_t seq, uint32_t cap, void* counters, uint32_t* status, uint64_t timeout_ns,
+               void* stream) {
+  return dev == CX_DEV_CUDA
+             ? cx_forward_cuda(from, expect_seq, tg, seq, cap, counters, status, timeout_ns, stream)
+             : cx_forward_host(from, expect_seq, tg, seq, cap, status, timeout_ns);
+}
+
+int cx_dense_send(int dev, int dtype, const void* g, float* r, int64_t n, uint64_t seq,
+                  const CxTargets* tg, const int64_t* starts, const int64_t* lens, void* counters,
+                  uint32_t src_rank, void* stream) {
+  return dev == CX_DEV_CUDA
+             ? cx_dense_send_cuda(dtype, g, r, n, seq, tg, starts, lens, counters, src_rank, stream)
+             : cx_dense_send_host(dtype, g, r, n, seq, tg, starts, lens, src_rank);
+}
+
+int cx_dense_reduce(int dev, int dtype, void* out, const void* own, int64_t n, const CxSources* src,
+                    float scale, const CxTargets* push, uint64_t push_seq, const int64_t* starts,
+                    const int64_t* lens, void* counters, uint32_t src_rank, uint32_t* status,
+                    uint64_t timeout_ns, void* stream) {
+  return dev == CX_DEV_CUDA
+             ? cx_dense_reduce_cuda(dtype, out, own, n, src, scale, push, push_seq, starts, lens,
+                                    counters, src_rank, status, timeout_ns, stream)
+             : cx_dense_reduce_host(dtype, out, own, n, src, scale, push, push_seq, starts, lens,
+                                    src_rank, status, timeout_ns);
+}
+
+int cx_axpy(int dev, int ydtype, void* y, int xdtype, const void* x, float a, int64_t n, void* stream) {
+  return dev == CX_DEV_CUDA ? cx_axpy_cuda(ydtype, y, xdtype, x, a, n, stream)
+                            : cx_axpy_host(ydtype, y, xdtype, x, a, n);
+}
+
+int cx_fill_zero(int dev, void* p, int64_t bytes, void* stream) {
+  if (dev == CX_DEV_CUDA) {
+    const cudaError_t e = cudaMemsetAsync(p, 0, (size_t)bytes, reinterpret_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? 0 : cx_set_error("cx_fill_zero", (int)e);
+  }
+  memset(p, 0, (size_t)bytes);
+  return 0;
+}
+
+// ---- CUDA memory runtime -----------------------------------------------------------
+int cx_cuda_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+  return n;
+}
+int cx_cuda_set_device(int dev) {
+  const cudaError_t e = cudaSetDevice(dev);
+  return e == cudaSuccess ? 0 : cx_set_error("cudaSetDevice", (int)e);
+}
+void* cx_cuda_malloc(int64_t bytes) {
+  void* p = nullptr;
+  const cudaError_t e = cudaMalloc(&p, (size_t)bytes);
+  if (e != cudaSuccess) { cx_set_error("cudaMalloc", (int)e); return nullptr; }
+  const cudaError_t e2 = cudaMemset(p, 0, (size_t)bytes);
+  if (e2 != cudaSuccess) { cx_set_error("cudaMemset", (int)e2); cudaFree(p); return nullptr; }
+  return p;
+}
+int cx_cuda_free(void* p) {
+  const cudaError_t e = cudaFree(p);
+  return e == cudaSuccess ? 0 : cx_set_error("cudaFree", (int)e);
+}
+int cx_cuda_ipc_get(void* p, void* handle64) {
+  cudaIpcMemHandle_t h;
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  const cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) return cx_set_error("cudaIpcGetMemHandle", (int)e);
+  memcpy(handle64, &h, 64);
+  return 0;
+}
+void* cx_cuda_ipc_open(const void* handle64) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) { cx_set_error("cudaIpcOpenMemHandle", (int)e); return nullptr; }
+  return p;
+}
+int cx_cuda_ipc_close(void* p) {
+  const cudaError_t e = cudaIpcCloseMemHandle(p);
+  return e == cudaSuccess ? 0 : cx_set_error("cudaIpcCloseMemHandle", (int)e);
+}
+int cx_cuda_can_access_peer(int dev, int peer) {
+  int ok = 0;
+  if (cudaDeviceCanAccessPeer(&ok, dev, peer) != cudaSuccess) { cudaGetLastError(); return 0; }
+  return ok;
+}
+void* cx_pinned_alloc(int64_t bytes, void** device_ptr) {
+  void* p = nullptr;
+  cudaError_t e = cudaHostAlloc(&p, (size_t)bytes, cudaHostAllocMapped | cudaHostAllocPortable);
+  if (e != cudaSuccess) { cx_set_error("cudaHostAlloc", (int)e); return nullptr; }
+  memset(p, 0, (size_t)bytes);
+  void* d = nullptr;
+  e = cudaHostGetDevicePointer(&d, p, 0);
+  if (e != cudaSuccess) { cx_set_error("cudaHostGetDevicePointer", (int)e); cudaFreeHost(p); return nullptr; }
+  if (device_ptr) *device_ptr = d;
+  return p;
+}
+int cx_pinned_free(void* p) {
+  const cudaError_t e = cudaFreeHost(p);
+  return e == cudaSuccess ? 0 : cx_set_error("cudaFreeHost", (int)e);
+}
+int cx_cuda_stream_sync(void* stream) {
+  const cudaError_t e = cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : cx_set_error("cudaStreamSynchronize", (int)e);
+}
+int cx_cuda_memcpy(void* dst, const void* src, int64_t bytes, int kind, void* stream) {
+  const cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, (cudaMemcpyKind)kind,
+                                        reinterpret_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? 0 : cx_set_error("cudaMemcpyAsync", (int)e);
+}
+
+// ---- host segments -------------------------------------------------------------------
+static void* shm_map(const char* name, int64_t bytes, int create) {
+  const int fd = shm_open(name, create ? (O_CREAT | O_RDWR) : O_RDWR, 0600);
+  if (fd < 0) { snprintf(g_err, sizeof(g_err), "shm_open(%s): %s", name, strerror(errno)); return nullptr; }
+  if (create && ftruncate(fd, (off_t)bytes) != 0) {
+    snprintf(g_err, sizeof(g_err), "ftruncate(%s): %s", name, strerror(errno));
+    close(fd);
+    return nullptr;
+  }
+  void* p = mmap(nullptr, (size_t)bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (p == MAP_FAILED) { snprintf(g_err, sizeof(g_err), "mmap(%s): %s", name, strerror(errno)); return nullptr; }
+  return p;
+}
+void* cx_shm_create(const char* name, int64_t bytes) { return shm_map(name, bytes, 1); }
+void* cx_shm_open(const char* name, int64_t bytes) { return shm_map(name, bytes, 0); }
+int cx_shm_close(void* p, int64_t bytes) { return munmap(p, (size_t)bytes); }
+int cx_shm_unlink(const char* name) { return shm_unlink(name); }
+void* cx_host_alloc(int64_t bytes) {
+  void* p = nullptr;
+  if (posix_memalign(&p, 256, (size_t)(bytes > 0 ? bytes : 1)) != 0) return nullptr;
+  memset(p, 0, (size_t)bytes);
+  return p;
+}
+int cx_host_free(void* p) { free(p); return 0; }
+
+}  // extern "C"

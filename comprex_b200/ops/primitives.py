@@ -1,0 +1,210 @@
+"""Python face of the native primitives: slots, thresholds, compress, apply, dense.
+
+Each function is a thin, allocation-free launch wrapper: it packs tensor
+addresses into the C structs of csrc/cx_common.h and calls the exported
+function on the current stream of the tensor's device (or synchronously for
+host tensors).  Which reference routine each primitive replaces is stated in
+the corresponding ``.cu`` file.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from .. import _lib
+from .._lib import ApplyArgs, ComprexError, Endpoint, Sources, Targets
+from ..parallel.env import GaspiEnvironment, SymmAlloc
+
+HEADER_BYTES = 64
+
+
+def _round_up(x: int, a: int) -> int:
+    return (x + a - 1) // a * a
+
+
+@dataclass(frozen=True)
+class SparseSlot:
+    """Receive slot for an IndexPairs payload of a vector of up to ``n`` elements."""
+    alloc: SymmAlloc
+    n: int
+    cap: int
+
+    @staticmethod
+    def nbytes(n: int, cap: int) -> int:
+        nsub = (n + _lib.SUBTILE - 1) // _lib.SUBTILE
+        return HEADER_BYTES + _round_up(4 * (nsub + 1), 16) + 8 * max(cap, 1)
+
+    @staticmethod
+    def create(env: GaspiEnvironment, n: int, cap: int) -> "SparseSlot":
+        return SparseSlot(env.alloc(SparseSlot.nbytes(n, cap)), n, cap)
+
+    def endpoint(self, env: GaspiEnvironment, rank: int | None = None) -> Endpoint:
+        base = env.ptr(self.alloc, rank)
+        nsub = (self.n + _lib.SUBTILE - 1) // _lib.SUBTILE
+        return Endpoint(base, base + HEADER_BYTES, base + HEADER_BYTES + _round_up(4 * (nsub + 1), 16))
+
+
+@dataclass(frozen=True)
+class DenseSlot:
+    """Receive slot for a dense payload of up to ``nbytes_data`` bytes."""
+    alloc: SymmAlloc
+    nbytes_data: int
+
+    @staticmethod
+    def create(env: GaspiEnvironment, nbytes_data: int) -> "DenseSlot":
+        return DenseSlot(env.alloc(HEADER_BYTES + _round_up(max(nbytes_data, 16), 16)), nbytes_data)
+
+    def endpoint(self, env: GaspiEnvironment, rank: int | None = None) -> Endpoint:
+        base = env.ptr(self.alloc, rank)
+        return Endpoint(base, 0, base + HEADER_BYTES)
+
+
+def make_targets(eps) -> Targets:
+    eps = list(eps)
+    if len(eps) > _lib.MAX_PEERS:
+        raise ComprexError("too many targets")
+    t = Targets()
+    t.count = len(eps)
+    for i, e in enumerate(eps):
+        t.ep[i] = e
+    return t
+
+
+def make_sources(eps, seqs) -> Sources:
+    eps = list(eps)
+    if len(eps) > _lib.MAX_PEERS:
+        raise ComprexError("too many sources")
+    s = Sources()
+    s.count = len(eps)
+    for i, (e, q) in enumerate(zip(eps, seqs)):
+        s.ep[i] = e
+        s.seq[i] = q
+    return s
+
+
+def _ptr(t: torch.Tensor | None) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _flat(t: torch.Tensor, what: str) -> torch.Tensor:
+    if not t.is_contiguous():
+        raise ComprexError(f"{what} must be contiguous")
+    return t
+
+
+class Compressor:
+    """Scratch, threshold cell and statistics of one sparse sender.
+
+    The scratch (tile counters and one look-back word per 4096-element tile)
+    is rank-local device memory; the threshold lives in a one-element device
+    tensor that the threshold kernel writes and the compress kernel reads.
+    """
+
+    def __init__(self, env: GaspiEnvironment, n: int):
+        self.env, self.n = env, n
+        self.ws_bytes = int(env.lib.cx_workspace_bytes(n))
+        self.workspace = env.scratch(self.ws_bytes)
+        self.thr = torch.zeros(1, dtype=torch.float32, device=env.device)
+        self.stats = env.new_stats()
+
+    def set_threshold(self, value: float) -> None:
+        self.thr.fill_(float(value))
+
+    def threshold_topk(self, g, r, n: int, ratio: float, default_subsamples: int = 1000,
+                       subsample_factor: float = 10.0) -> None:
+        env = self.env
+        gd = _lib.dtype_code(g.dtype) if g is not None else _lib.F32
+        _lib.check(env.lib.cx_threshold_topk(env.dev, gd, _ptr(g), _ptr(r), n, ratio, int(default_subsamples),
+                                             float(subsample_factor), self.thr.data_ptr(),
+                                             _lib.stream_ptr(env.device)), "cx_threshold_topk")
+
+    def compress(self, g, r, n: int, cap: int, seq: int, targets: Targets) -> None:
+        """r += g; emit |r| > thr into every target; zero what was emitted."""
+        env = self.env
+        if n > self.n:
+            raise ComprexError(f"vector of {n} elements exceeds the compressor's size {self.n}")
+        gd = _lib.dtype_code(g.dtype) if g is not None else _lib.F32
+        if r is not None and r.dtype != torch.float32:
+            raise ComprexError("the residual must be float32")
+        _lib.check(env.lib.cx_compress(env.dev, gd, _ptr(g), _ptr(r), n, self.thr.data_ptr(), cap, seq,
+                                       C.byref(targets), self.workspace.data_ptr(), self.ws_bytes,
+                                       self.stats.dev_ptr, env.rank, _lib.stream_ptr(env.device)),
+                   "cx_compress")
+
+    def last_stats(self) -> dict:
+        """Statistics of the most recent compress call (synchronises)."""
+        self.env.flush()
+        return self.stats.read()
+
+
+def apply_sparse(env: GaspiEnvironment, sources: Sources, n: int, args: ApplyArgs, status) -> None:
+    _lib.check(env.lib.cx_apply(env.dev, C.byref(sources), n, C.byref(args), status.dev_ptr,
+                                env.timeout_ns, _lib.stream_ptr(env.device)), "cx_apply")
+
+
+def args_add(out: torch.Tensor, scale: float = 1.0) -> ApplyArgs:
+    a = ApplyArgs()
+    a.op, a.out, a.out_dtype, a.scale = _lib.OP_ADD, out.data_ptr(), _lib.dtype_code(out.dtype), scale
+    return a
+
+
+def args_set(out: torch.Tensor, scale: float = 1.0) -> ApplyArgs:
+    a = ApplyArgs()
+    a.op, a.out, a.out_dtype, a.scale = _lib.OP_SET, out.data_ptr(), _lib.dtype_code(out.dtype), scale
+    return a
+
+
+def args_update(op: int, w: torch.Tensor, scale: float, *, shadow=None, m=None, v=None, lr=0.0,
+                momentum=0.0, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0, step=1) -> ApplyArgs:
+    if w.dtype != torch.float32:
+        raise ComprexError("master weights must be float32")
+    a = ApplyArgs()
+    a.op, a.out, a.out_dtype, a.scale = op, w.data_ptr(), _lib.F32, scale
+    if shadow is not None:
+        a.shadow, a.shadow_dtype = shadow.data_ptr(), _lib.dtype_code(shadow.dtype)
+    a.m, a.v = _ptr(m), _ptr(v)
+    a.lr, a.momentum, a.beta1, a.beta2, a.eps, a.wd = lr, momentum, beta1, beta2, eps, wd
+    a.bc1 = 1.0 - beta1 ** step
+    a.bc2 = 1.0 - beta2 ** step
+    return a
+
+
+def forward(env: GaspiEnvironment, src: Endpoint, expect_seq: int, targets: Targets, seq: int, cap: int,
+            counters: torch.Tensor, status) -> None:
+    _lib.check(env.lib.cx_forward(env.dev, C.byref(src), expect_seq, C.byref(targets), seq, cap,
+                                  counters.data_ptr(), status.dev_ptr, env.timeout_ns,
+                                  _lib.stream_ptr(env.device)), "cx_forward")
+
+
+def _ranges(ranges):
+    if ranges is None:
+        return None, None
+    k = len(ranges)
+    starts = (C.c_int64 * k)(*[r[0] for r in ranges])
+    lens = (C.c_int64 * k)(*[r[1] for r in ranges])
+    return starts, lens
+
+
+def dense_send(env: GaspiEnvironment, g: torch.Tensor, r, n: int, seq: int, targets: Targets,
+               counters: torch.Tensor, ranges=None) -> None:
+    starts, lens = _ranges(ranges)
+    _lib.check(env.lib.cx_dense_send(env.dev, _lib.dtype_code(g.dtype), g.data_ptr(), _ptr(r), n, seq,
+                                     C.byref(targets), starts, lens, counters.data_ptr(), env.rank,
+                                     _lib.stream_ptr(env.device)), "cx_dense_send")
+
+
+def dense_reduce(env: GaspiEnvironment, out: torch.Tensor, own, n: int, sources: Sources, status,
+                 scale: float = 1.0, push: Targets | None = None, push_seq: int = 0,
+                 counters: torch.Tensor | None = None, ranges=None) -> None:
+    starts, lens = _ranges(ranges)
+    _lib.check(env.lib.cx_dense_reduce(env.dev, _lib.dtype_code(out.dtype), out.data_ptr(), _ptr(own), n,
+                                       C.byref(sources), scale, C.byref(push) if push is not None else None,
+                                       push_seq, starts, lens, _ptr(counters), env.rank, status.dev_ptr,
+                                       env.timeout_ns, _lib.stream_ptr(env.device)), "cx_dense_reduce")
+
+
+def axpy(env: GaspiEnvironment, y: torch.Tensor, x: torch.Tensor, a: float, n: int) -> None:
+    _lib.check(env.lib.cx_axpy(env.dev, _lib.dtype_code(y.dtype), y.data_ptr(), _lib.dtype_code(x.dtype),
+                               x.data_ptr(), a, n, _lib.stream_ptr(env.device)), "cx_axpy")
