@@ -294,7 +294,7 @@ class Comprex_BigRingAllreduce(_ComprexAllreduceBase):
         dests = [r for r in range(env.ranks) if r != me or self.consistent]
         return P.make_targets([self._slots[me][par].endpoint(env, r) for r in dests])
 
-    def _plan_common(self, t, g, fixed_thr, rounds=1):
+    def _plan_common(self, t, g, fixed_thr, rounds=1, recv_args=None):
         env = self._env
         phases = []
         for _ in range(rounds):
@@ -316,13 +316,16 @@ class Comprex_BigRingAllreduce(_ComprexAllreduceBase):
                 if not order:
                     return
                 src = P.make_sources([self._slots[j][par].endpoint(env) for j in order], [seq] * len(order))
-                args = P.args_set(t) if (self.consistent and first) else P.args_add(t)
+                if recv_args is not None:
+                    args = recv_args  # fused averaging + parameter update instead of a dense result
+                else:
+                    args = P.args_set(t) if (self.consistent and first) else P.args_add(t)
                 P.apply_sparse(env, src, self.size, args, self._status)
             phases += [send, recv]
         return phases
 
-    def _plan_apply(self, t):
-        return self._plan_common(t, t, None)
+    def _plan_apply(self, t, recv_args=None):
+        return self._plan_common(t, t, None, recv_args=recv_args)
 
     def _plan_flush(self, t):
         """Every rank sends its whole residual; ``vector`` gains the peers' (and, when

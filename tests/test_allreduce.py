@@ -1,0 +1,157 @@
+"""The six allreduce variants on P virtual ranks of one device.
+
+The compressed tests follow the reference's pattern (test/AllToOneAllreduce.cpp,
+test/RingAllreduce.cpp, test/BigRingAllreduce.cpp): one rank keeps accumulating
+across runs while the others reset their input; after ``flush`` the accumulator
+must equal ``(runs*(P-1)+1) * values`` exactly, i.e. nothing is lost to
+thresholding, residuals and flush together conserve the sum.
+"""
+import pytest
+import torch
+
+import comprex_b200 as cx
+
+from helpers import alt_ramp
+
+RANKS = [1, 2, 3, 4, 8]
+
+
+@pytest.fixture(params=RANKS)
+def world(request, device):
+    w = cx.LoopbackWorld(request.param, device=device, timeout_ms=500)
+    yield w
+    w.close()
+
+
+@pytest.mark.parametrize("cls,kw", [(cx.AllToOneAllreduce, dict(chiefRank=0)), (cx.RingAllreduce, {}),
+                                    (cx.BigRingAllreduce, {})])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_dense_allreduce(world, cls, kw, dtype):
+    n, P = 10007, world.size
+    ars = [cls(e) for e in world.envs]
+    for a in ars:
+        a.setup_connections(n, 1, dtype=dtype, **kw)
+    for step in range(3):
+        torch.manual_seed(step)
+        xs = [torch.randn(n).to(dtype).to(world.device) for _ in range(P)]
+        ref = sum(x.double() for x in xs)
+        world.run(ars, "apply", [(x,) for x in xs])
+        tol = 1e-5 if dtype == torch.float32 else 0.1
+        for x in xs:
+            assert (x.double() - ref).abs().max().item() < tol
+        if cls is not cx.BigRingAllreduce:   # one reducer per element: identical bits everywhere
+            for x in xs[1:]:
+                assert torch.equal(x, xs[0])
+
+
+@pytest.mark.parametrize("cls,kw", [(cx.Comprex_BigRingAllreduce, {}), (cx.Comprex_RingAllreduce, {}),
+                                    (cx.Comprex_AllToOneAllreduce, dict(chiefRank=0))])
+@pytest.mark.parametrize("n,ratio", [(50, 0.01), (1000, 0.01), (20011, 0.05)])
+def test_compressed_allreduce_conserves_sum(world, cls, kw, n, ratio):
+    P, dev = world.size, world.device
+    ars = [cls(e) for e in world.envs]
+    for a in ars:
+        a.setup_connections(n, 1, compression_ratio=ratio, size_factor=3.0, **kw)
+    vals = alt_ramp(n, dev)
+    runs = 6
+    acc = vals.clone()
+    for _ in range(runs):
+        xs = [acc] + [vals.clone() for _ in range(P - 1)]
+        world.run(ars, "apply", [(x,) for x in xs])
+    xs = [acc] + [torch.zeros(n, device=dev) for _ in range(P - 1)]
+    world.run(ars, "flush", [(x,) for x in xs])
+    expect = (runs * (P - 1) + 1) * vals
+    if cls is cx.Comprex_RingAllreduce and P > 1:
+        a = ars[0]
+        c = 1 % P   # rank 0 owns chunk 1 and keeps it dense (test/RingAllreduce.cpp:87-100)
+        sl = slice(a.segment_starts[c], a.segment_starts[c] + a.segment_sizes[c])
+        assert torch.equal(acc[sl], expect[sl])
+    else:
+        assert torch.equal(acc, expect)
+    for a in ars:
+        for r in a._residuals():
+            assert float(r.abs().sum()) == 0.0
+
+
+def test_consistent_bigring_replicas_identical_and_conserving(world):
+    P, dev, n = world.size, world.device, 30011
+    ars = [cx.Comprex_BigRingAllreduce(e) for e in world.envs]
+    for a in ars:
+        a.setup_connections(n, 1, compression_ratio=0.02, size_factor=3.0, consistent=True)
+    total = torch.zeros(n, dtype=torch.float64)
+    inputs = torch.zeros(n, dtype=torch.float64)
+    for step in range(8):
+        torch.manual_seed(step)
+        xs = [torch.randn(n).to(dev) for _ in range(P)]
+        inputs += sum(x.double().cpu() for x in xs)
+        world.run(ars, "apply", [(x,) for x in xs])
+        for x in xs[1:]:
+            assert torch.equal(x, xs[0])
+        frac = float((xs[0] != 0).float().mean())
+        assert frac <= min(1.0, 0.02 * 1.6 * P)
+        total += xs[0].double().cpu()
+    xs = [torch.zeros(n, device=dev) for _ in range(P)]
+    world.run(ars, "flush", [(x,) for x in xs])
+    total += xs[0].double().cpu()
+    assert (total - inputs).abs().max().item() < 1e-4
+
+
+def test_ring_result_is_topk_of_reduced_chunk(world):
+    """Non-owners receive exactly the entries of the owner's reduced chunk that pass its threshold."""
+    P, dev, n = world.size, world.device, 40000
+    if P < 2:
+        pytest.skip("needs peers")
+    ars = [cx.Comprex_RingAllreduce(e) for e in world.envs]
+    for a in ars:
+        a.setup_connections(n, 1, compression_ratio=0.05, size_factor=2.5)
+    torch.manual_seed(3)
+    xs = [torch.randn(n).to(dev) for _ in range(P)]
+    world.run(ars, "apply", [(x,) for x in xs])
+    a = ars[0]
+    for owner in range(P):
+        c = (owner + 1) % P
+        sl = slice(a.segment_starts[c], a.segment_starts[c] + a.segment_sizes[c])
+        dense = xs[owner][sl]
+        for r in range(P):
+            if r == owner:
+                continue
+            got = xs[r][sl]
+            nz = got != 0
+            assert torch.equal(got[nz], dense[nz])
+            assert 0 < int(nz.sum()) < 0.2 * dense.numel()
+
+
+def test_set_compression_ratio_and_state_dict(world):
+    P, dev, n = world.size, world.device, 20000
+    ars = [cx.Comprex_BigRingAllreduce(e) for e in world.envs]
+    for a in ars:
+        a.setup_connections(n, 1, compression_ratio=0.01, size_factor=2.5, consistent=True)
+    xs = [torch.randn(n).to(dev) for _ in range(P)]
+    world.run(ars, "apply", [(x.clone(),) for x in xs])
+    lo = ars[0].stats()["nnz"]
+    for a in ars:
+        a.set_compression_ratio(0.1)
+    world.run(ars, "apply", [(x.clone(),) for x in xs])
+    assert ars[0].stats()["nnz"] > 3 * lo
+    sd = ars[0].state_dict()
+    assert sd["ratio"] == pytest.approx(0.1) and sd["residuals"][0].abs().sum() > 0
+    saved = ars[0].rests.clone()
+    ars[0].reset()
+    assert float(ars[0].rests.abs().sum()) == 0.0
+    ars[0].load_state_dict(sd)
+    assert torch.equal(ars[0].rests, saved)
+
+
+def test_apply_checks_size_and_accepts_numpy():
+    import numpy as np
+    env = cx.GaspiEnvironment(1 << 20, device="cpu")
+    ar = cx.Comprex_BigRingAllreduce(env)
+    ar.setup_connections(100, 1, 0.1, 3.0)
+    with pytest.raises(cx.ComprexError, match="does not match allreduce size"):
+        ar.apply(torch.zeros(99))
+    v = np.arange(100, dtype=np.float32).reshape(10, 10)
+    out = ar.apply(v)
+    assert out is v and out.shape == (10, 10)      # single rank: own dense data is kept
+    assert np.array_equal(v.reshape(-1), np.arange(100, dtype=np.float32))
+    assert ar.getSize() == 100
+    env.close()

@@ -1,0 +1,372 @@
+"""Unit tests of the native primitives against plain PyTorch fp32 restatements.
+
+Every test runs on the host implementation (CPU) and, marked ``gpu``, on the
+CUDA kernels; the CUDA kernels are additionally compared bit for bit with the
+host implementation of the same primitive.
+"""
+import ctypes as C
+
+import pytest
+import torch
+
+import comprex_b200 as cx
+from comprex_b200 import _lib
+from comprex_b200.ops import primitives as P
+
+from helpers import ref_compress, ref_threshold_topk
+
+SIZES = [1, 31, 32, 33, 1023, 1024, 1025, 4095, 4096, 4097, 10007, 70001]
+
+
+@pytest.fixture
+def world(device):
+    w = cx.LoopbackWorld(2, device=device, timeout_ms=200)
+    yield w
+    w.close()
+
+
+def read_pairs(env, slot, rank=None):
+    ep = slot.endpoint(env, rank)
+    hdr = env.read_header(ep.hdr)
+    raw = env.read_bytes(ep.pairs, 8 * max(hdr.nnz, 1))[: 8 * hdr.nnz]
+    buf = torch.frombuffer(bytearray(raw), dtype=torch.int32).view(-1, 2) if hdr.nnz else torch.zeros(0, 2, dtype=torch.int32)
+    idx = buf[:, 0].clone()
+    val = buf[:, 1].clone().view(torch.float32)
+    nsub = (hdr.n + _lib.SUBTILE - 1) // _lib.SUBTILE
+    praw = env.read_bytes(ep.prefix, 4 * (nsub + 1))
+    prefix = torch.frombuffer(bytearray(praw), dtype=torch.int32).clone()
+    return hdr, idx, val, prefix
+
+
+@pytest.mark.parametrize("n", [1, 50, 999, 1000, 1001, 4096, 100003, 1 << 20])
+@pytest.mark.parametrize("ratio", [0.1, 0.01, 0.001])
+def test_threshold_matches_reference_rule(device, n, ratio):
+    torch.manual_seed(n)
+    env = cx.GaspiEnvironment(1 << 16, device=device)
+    g = torch.randn(n).to(device)
+    r = (0.5 * torch.randn(n)).to(device)
+    comp = P.Compressor(env, n)
+    comp.threshold_topk(g, r, n, ratio)
+    got = comp.thr.item()
+    want = ref_threshold_topk(r.cpu() + g.cpu(), ratio)
+    assert got == want
+    # sampling parameters of the ring variants
+    comp.threshold_topk(g, None, n, ratio, 250, 4.0)
+    assert comp.thr.item() == ref_threshold_topk(g.cpu(), ratio, 250, 4.0)
+    env.close()
+
+
+def test_threshold_reference_vector(device):
+    """test/threshold.cpp:58-85: 100 ints, top 10 % -> threshold 90, 10 elements pass with >=."""
+    from helpers import alt_ramp
+    v = alt_ramp(100, device)
+    thr = cx.ThresholdTopK(0.10)
+    thr.prepare(v)
+    assert thr.getThreshold() == 90.0
+    kept = thr.apply(v)
+    assert int((kept != 0).sum()) == 10
+    const = cx.ThresholdConst(20)
+    assert int((const.apply(v) != 0).sum()) == 80
+
+
+@pytest.mark.parametrize("n", SIZES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_compress_add_update(world, n, dtype):
+    torch.manual_seed(n)
+    e0, e1 = world.envs
+    dev = world.device
+    cap = n
+    slot0 = P.SparseSlot.create(e0, n, cap)
+    slot1 = P.SparseSlot.create(e1, n, cap)
+    assert slot0.alloc == slot1.alloc
+    g = torch.randn(n).to(dtype).to(dev)
+    r0 = (0.3 * torch.randn(n)).to(dev)
+    r = r0.clone()
+    comp = P.Compressor(e0, n)
+    comp.set_threshold(1.0)
+    comp.compress(g, r, n, cap, 7, P.make_targets([slot1.endpoint(e0, 1), slot0.endpoint(e0, 0)]))
+    e0.flush()
+    idx_w, val_w, r_w = ref_compress(g.cpu(), r0.cpu(), 1.0)
+    for env, slot in ((e1, slot1), (e0, slot0)):
+        hdr, idx, val, prefix = read_pairs(env, slot)
+        assert hdr.seq == 7 and hdr.n == n and hdr.kind == _lib.KIND_PAIRS
+        assert hdr.nnz == idx_w.numel() == hdr.nnz_found
+        assert torch.equal(idx, idx_w)           # ascending index order, like the reference format
+        assert torch.equal(val, val_w)
+        # prefix[s] == number of pairs with index < s*1024
+        bounds = torch.arange(prefix.numel()) * _lib.SUBTILE
+        assert torch.equal(prefix.long(), torch.searchsorted(idx_w.long(), bounds))
+    assert torch.equal(r.cpu(), r_w)
+    # conservation: what was sent plus what stayed equals what came in
+    dense = torch.zeros(n)
+    dense[idx_w.long()] = val_w
+    assert torch.equal(dense + r.cpu(), r0.cpu() + g.cpu().float())
+    st = comp.last_stats()
+    assert st["nnz"] == idx_w.numel() and st["status"] == 0
+
+
+def test_compress_capacity_overflow_keeps_residual(world):
+    e0, e1 = world.envs
+    dev, n, cap = world.device, 20000, 100
+    slot = [P.SparseSlot.create(e, n, cap) for e in world.envs][1]
+    g = torch.randn(n).to(dev)
+    r = torch.zeros(n, device=dev)
+    comp = P.Compressor(e0, n)
+    comp.set_threshold(0.5)
+    comp.compress(g, r, n, cap, 1, P.make_targets([slot.endpoint(e0, 1)]))
+    hdr, idx, val, _ = read_pairs(e1, slot)
+    idx_w, val_w, r_w = ref_compress(g.cpu(), torch.zeros(n), 0.5, cap)
+    assert hdr.nnz == cap and hdr.nnz_found > cap
+    assert torch.equal(idx, idx_w) and torch.equal(val, val_w)
+    assert torch.equal(r.cpu(), r_w)
+    assert comp.last_stats()["status"] & _lib.ST_OVERFLOW
+    e0.check()  # overflow is soft: no exception
+
+
+@pytest.mark.parametrize("mode", ["update", "plain"])
+def test_compress_modes(world, mode):
+    e0, e1 = world.envs
+    dev, n = world.device, 5000
+    slot = [P.SparseSlot.create(e, n, n) for e in world.envs][1]
+    x = torch.randn(n).to(dev)
+    x[::3] = 0
+    comp = P.Compressor(e0, n)
+    comp.set_threshold(0.0)
+    if mode == "update":   # flushRests: everything non-zero leaves, the residual ends up zero
+        r = x.clone()
+        comp.compress(None, r, n, n, 1, P.make_targets([slot.endpoint(e0, 1)]))
+        assert int(r.abs().sum().item()) == 0
+    else:                  # compressOnly: the input is untouched
+        comp.compress(x, None, n, n, 1, P.make_targets([slot.endpoint(e0, 1)]))
+    hdr, idx, val, _ = read_pairs(e1, slot)
+    nz = torch.nonzero(x.cpu()).flatten()
+    assert torch.equal(idx.long(), nz) and torch.equal(val, x.cpu()[nz])
+
+
+def _fill_slots(world, n, nsrc, seed=0):
+    """Each virtual rank j < nsrc compresses its own vector into rank 0's slot j."""
+    torch.manual_seed(seed)
+    dev = world.device
+    e0 = world.envs[0]
+    slots = [[P.SparseSlot.create(e, n, n) for e in world.envs] for _ in range(nsrc)]
+    dense = []
+    for j in range(nsrc):
+        x = torch.randn(n)
+        x[torch.rand(n) > 0.2] = 0
+        dense.append(x)
+        comp = P.Compressor(e0, n)
+        comp.set_threshold(0.0)
+        comp.compress(x.to(dev), None, n, n, 3, P.make_targets([slots[j][0].endpoint(e0, 0)]))
+    src = P.make_sources([slots[j][0].endpoint(e0, 0) for j in range(nsrc)], [3] * nsrc)
+    return src, dense
+
+
+@pytest.mark.parametrize("n", [1, 1000, 1024, 4097, 50001])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_apply_add_and_set(world, n, out_dtype):
+    e0 = world.envs[0]
+    dev = world.device
+    src, dense = _fill_slots(world, n, 3)
+    st = e0.new_status("t")
+    base = torch.randn(n).to(out_dtype)
+    out = base.clone().to(dev)
+    P.apply_sparse(e0, src, n, P.args_add(out, 0.5), st)
+    want = base.clone()
+    for d in dense:   # same order, same rounding as the kernel: one source after the other
+        want = (want.float() + 0.5 * d).to(out_dtype)
+    assert torch.equal(out.cpu(), want)
+    out2 = torch.full((n,), 7.0, dtype=out_dtype, device=dev)
+    P.apply_sparse(e0, src, n, P.args_set(out2, 0.25), st)
+    acc = torch.zeros(n)
+    for d in dense:
+        acc += d
+    assert torch.equal(out2.cpu(), (0.25 * acc).to(out_dtype))
+    e0.flush()
+    assert st.value == 0
+
+
+@pytest.mark.parametrize("op", ["sgd", "sgd_wd", "momentum", "adamw"])
+@pytest.mark.parametrize("shadow", [False, True])
+def test_apply_fused_updates(world, op, shadow):
+    e0 = world.envs[0]
+    dev, n = world.device, 30011
+    src, dense = _fill_slots(world, n, 4, seed=5)
+    g = torch.zeros(n)
+    for d in dense:
+        g += d
+    g *= 0.25
+    w0, m0, v0 = torch.randn(n), 0.1 * torch.randn(n), 0.01 * torch.rand(n) + 0.01
+    w, m, v = w0.clone().to(dev), m0.clone().to(dev), v0.clone().to(dev)
+    sh = w0.to(torch.bfloat16).to(dev) if shadow else None  # the shadow starts in sync, as in real use
+    st = e0.new_status("t")
+    lr, mu, wd, b1, b2, eps, step = 0.1, 0.9, 0.01, 0.9, 0.999, 1e-8, 3
+    if op == "sgd":
+        args = P.args_update(_lib.OP_SGD, w, 0.25, shadow=sh)
+        want_w = w0 - g
+    elif op == "sgd_wd":
+        args = P.args_update(_lib.OP_SGD, w, 0.25, shadow=sh, wd=wd)
+        want_w = (1 - wd) * w0 - g
+    elif op == "momentum":
+        args = P.args_update(_lib.OP_MOMENTUM, w, 0.25, shadow=sh, m=m, lr=lr, momentum=mu, wd=wd)
+        want_m = mu * m0 + lr * g
+        want_w = (1 - wd) * w0 - want_m
+    else:
+        args = P.args_update(_lib.OP_ADAMW, w, 0.25, shadow=sh, m=m, v=v, lr=lr, beta1=b1, beta2=b2, eps=eps,
+                             wd=wd, step=step)
+        want_m = b1 * m0 + (1 - b1) * g
+        want_v = b2 * v0 + (1 - b2) * g * g
+        want_w = w0 * (1 - lr * wd) - lr * (want_m / (1 - b1 ** step)) / ((want_v / (1 - b2 ** step)).sqrt() + eps)
+    P.apply_sparse(e0, src, n, args, st)
+    e0.flush()
+    assert st.value == 0
+    torch.testing.assert_close(w.cpu(), want_w, rtol=1e-5, atol=1e-6)
+    if op in ("momentum", "adamw"):
+        torch.testing.assert_close(m.cpu(), want_m, rtol=1e-5, atol=1e-7)
+    if op == "adamw":
+        torch.testing.assert_close(v.cpu(), want_v, rtol=1e-5, atol=1e-8)
+    if shadow:
+        assert torch.equal(sh.cpu(), w.cpu().to(torch.bfloat16))
+
+
+def test_apply_timeout_sets_status_and_leaves_output(world):
+    """A notification that never arrives: the wait gives up, the output is untouched."""
+    e0 = world.envs[0]
+    n = 2048
+    slot = [P.SparseSlot.create(e, n, n) for e in world.envs][0]
+    out = torch.ones(n, device=world.device)
+    st = e0.new_status("waiter")
+    P.apply_sparse(e0, P.make_sources([slot.endpoint(e0)], [1]), n, P.args_add(out), st)
+    with pytest.raises(cx.ComprexError, match="TIMEOUT"):
+        e0.flush()
+    assert torch.equal(out.cpu(), torch.ones(n))
+    e0.flush()  # the status word was cleared, the context is still usable
+    comp = P.Compressor(e0, n)
+    comp.set_threshold(0.0)
+    comp.compress(out, None, n, n, 1, P.make_targets([slot.endpoint(e0)]))
+    P.apply_sparse(e0, P.make_sources([slot.endpoint(e0)], [1]), n, P.args_add(out), st)
+    e0.flush()
+    assert torch.equal(out.cpu(), 2 * torch.ones(n))
+
+
+def test_apply_rejects_corrupt_header_and_index(world):
+    """Host-written garbage in a local slot is reported, never dereferenced."""
+    e0 = world.envs[0]
+    n = 3000
+    slot = [P.SparseSlot.create(e, n, n) for e in world.envs][0]
+    x = torch.zeros(n, device=world.device)
+    x[5] = 1.0
+    comp = P.Compressor(e0, n)
+    comp.set_threshold(0.0)
+    comp.compress(x, None, n, n, 1, P.make_targets([slot.endpoint(e0)]))
+    e0.flush()
+    ep = slot.endpoint(e0)
+    bad_pair = (C.c_int32 * 2)(2_000_000, 0x3F800000)
+    if world.device.type == "cuda":
+        _lib.check(e0.lib.cx_cuda_memcpy(ep.pairs, bad_pair, 8, 1, None))
+        torch.cuda.synchronize()
+    else:
+        C.memmove(ep.pairs, bad_pair, 8)
+    out = torch.zeros(n, device=world.device)
+    st = e0.new_status("decoder")
+    P.apply_sparse(e0, P.make_sources([ep], [1]), n, P.args_add(out), st)
+    with pytest.raises(cx.ComprexError, match="BAD_INDEX"):
+        e0.flush()
+    assert float(out.abs().sum()) == 0.0
+    # wrong length in the header
+    P.apply_sparse(e0, P.make_sources([ep], [1]), n + 1, P.args_add(torch.zeros(n + 1, device=world.device)), st)
+    with pytest.raises(cx.ComprexError, match="BAD_HEADER"):
+        e0.flush()
+
+
+@pytest.mark.parametrize("n", [1, 5, 1000, 4099, 65537])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_dense_send_reduce(world, n, dtype):
+    e0, e1 = world.envs
+    dev = world.device
+    es = torch.empty(0, dtype=dtype).element_size()
+    slots = [[P.DenseSlot.create(e, n * es) for e in world.envs] for _ in range(2)]
+    ctr = e0.scratch(64)
+    a, b = torch.randn(n).to(dtype), torch.randn(n).to(dtype)
+    own = torch.randn(n).to(dtype)
+    P.dense_send(e0, a.to(dev), None, n, 1, P.make_targets([slots[0][1].endpoint(e0, 1)]), ctr)
+    P.dense_send(e0, b.to(dev), None, n, 1, P.make_targets([slots[1][1].endpoint(e0, 1)]), ctr)
+    st = e1.new_status("t")
+    out = own.clone().to(dev)
+    src = P.make_sources([slots[0][1].endpoint(e1), slots[1][1].endpoint(e1)], [1, 1])
+    P.dense_reduce(e1, out, out, n, src, st, scale=0.5)
+    want = ((own.float() + a.float() + b.float()) * 0.5).to(dtype)
+    assert torch.equal(out.cpu(), want)
+    cp = torch.empty(n, dtype=dtype, device=dev)
+    P.dense_reduce(e1, cp, None, n, P.make_sources([slots[0][1].endpoint(e1)], [1]), st)
+    assert torch.equal(cp.cpu(), a)
+    e1.flush()
+
+
+def test_dense_send_with_residual_is_compressor_none(world):
+    e0, e1 = world.envs
+    dev, n = world.device, 3001
+    slot = [P.DenseSlot.create(e, 4 * n) for e in world.envs][1]
+    g, r0 = torch.randn(n), torch.randn(n)
+    r = r0.clone().to(dev)
+    P.dense_send(e0, g.to(dev), r, n, 1, P.make_targets([slot.endpoint(e0, 1)]), e0.scratch(64))
+    out = torch.empty(n, device=dev)
+    P.dense_reduce(e1, out, None, n, P.make_sources([slot.endpoint(e1)], [1]), e1.new_status("t"))
+    assert torch.equal(out.cpu(), g + r0)
+    assert float(r.abs().sum()) == 0.0
+
+
+def test_rle_roundtrip_and_residual():
+    """Corrected RLE codec: round trip with a threshold above zero, plus error feedback."""
+    torch.manual_seed(1)
+    n = 1000
+    g, r0 = torch.randn(n), 0.2 * torch.randn(n)
+    r = r0.clone()
+    payload = cx.CompressorRLE.encode(g, r, 1.0)
+    v = g + r0
+    keep = v.abs() >= 1.0
+    out = torch.full((n,), 9.0)
+    cx.CompressorRLE.decode(payload, out)
+    assert torch.equal(out, torch.where(keep, v, torch.zeros(n)))
+    assert torch.equal(r, torch.where(keep, torch.zeros(n), v))
+    acc = torch.ones(n)
+    cx.CompressorRLE.decode(payload, acc, add=True)
+    assert torch.equal(acc, 1 + torch.where(keep, v, torch.zeros(n)))
+    # the sparse test vector of test/compressor.cpp (75 % zeros, threshold 0)
+    x = torch.arange(16).float() * (torch.arange(16) % 4 == 0)
+    out = torch.empty(16)
+    cx.CompressorRLE.decode(cx.CompressorRLE.encode(x, None, 0.0), out)
+    assert torch.equal(out, x)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [1000, 4096, 100003, (1 << 22) + 5])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_cuda_kernels_match_host_bitwise(n, dtype):
+    """threshold + compress + apply on the GPU produce the bits of the host implementation."""
+    torch.manual_seed(n)
+    g = torch.randn(n).to(dtype)
+    r0 = 0.7 * torch.randn(n)
+    w0 = torch.randn(n)
+    res = {}
+    for dev in ("cpu", "cuda"):
+        world = cx.LoopbackWorld(2, device=dev)
+        e0, e1 = world.envs
+        cap = n // 8
+        slot = [P.SparseSlot.create(e, n, cap) for e in world.envs][1]
+        comp = P.Compressor(e0, n)
+        r = r0.clone().to(dev)
+        comp.threshold_topk(g.to(dev), r, n, 0.02)
+        comp.compress(g.to(dev), r, n, cap, 1, P.make_targets([slot.endpoint(e0, 1)]))
+        hdr, idx, val, prefix = read_pairs(e1, slot)
+        w = w0.clone().to(dev)
+        m = torch.zeros(n, device=dev)
+        v = torch.zeros(n, device=dev)
+        sh = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+        st = e1.new_status("t")
+        P.apply_sparse(e1, P.make_sources([slot.endpoint(e1)], [1]), n,
+                       P.args_update(_lib.OP_ADAMW, w, 0.5, shadow=sh, m=m, v=v, lr=0.01, wd=0.1, step=2), st)
+        e1.flush()
+        res[dev] = (comp.thr.cpu().clone(), idx, val, prefix, r.cpu(), w.cpu(), m.cpu(), v.cpu(), sh.cpu())
+        world.close()
+    for a, b in zip(res["cpu"], res["cuda"]):
+        assert torch.equal(a, b)
