@@ -1,0 +1,274 @@
+"""Real multi-process ranks.
+
+CPU: ``gloo`` ranks over POSIX shared memory run the same protocol as the GPU
+path (slots, release/acquire notifications, bounded waits).  Includes the
+2-rank / 2^20-element / 1 % / 20-step conservation check and host-side fault
+injection: a rank that never sends makes its peer's wait time out with a status
+instead of hanging.
+
+GPU (marked ``gpu``, needs >= 2 devices): the same scenarios over CUDA IPC and
+NVLink peer stores.
+"""
+import os
+import socket
+import sys
+import traceback
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _entry(rank, world, port, backend, fn_name, q, args):
+    try:
+        sys.path.insert(0, ROOT)
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                          WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+        if backend == "nccl":
+            os.environ["NCCL_NVLS_ENABLE"] = "0"
+            torch.cuda.set_device(rank)
+        dist.init_process_group(backend, rank=rank, world_size=world)
+        out = globals()[fn_name](rank, world, "cuda" if backend == "nccl" else "cpu", *args)
+        q.put((rank, "ok", out))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def run_ranks(world, fn_name, backend="gloo", args=(), timeout=240):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_entry, args=(r, world, port, backend, fn_name, q, args)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    try:
+        for _ in range(world):
+            rank, status, payload = q.get(timeout=timeout)
+            results[rank] = (status, payload)
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.terminate()
+    for rank, (status, payload) in sorted(results.items()):
+        assert status == "ok", f"rank {rank} failed:\n{payload}"
+    return [results[r][1] for r in range(world)]
+
+
+# ---- scenarios (run inside the ranks) ------------------------------------------------------------
+def scenario_config1(rank, world, device, n, steps, ratio):
+    """ComprEx exchange + ring allreduce, conservation and dense-sum check."""
+    import comprex_b200 as cx
+    env = cx.GaspiEnvironment(64 << 20, device=device, timeout_ms=20000)
+    assert env.get_rank() == rank and env.get_ranks() == world
+    peer = (rank + 1) % world
+    ex = cx.Comprex(env, n, 2.5)
+    ex.setThreshold(cx.ThresholdTopK(ratio))
+    ex.setCompressor(cx.CompressorIndexPairs())
+    ex.connectTo((rank - 1) % world, peer, 1)
+    sent_sum = torch.zeros((), dtype=torch.float64)
+    in_sum = torch.zeros((), dtype=torch.float64)
+    recv_acc = torch.zeros(n, device=device)
+    for step in range(steps):
+        g = torch.Generator().manual_seed(rank + step)
+        v = torch.randn(n, generator=g).to(device)
+        in_sum += v.double().sum().cpu()
+        before = ex.getRests()
+        ex.writeRemote(v)
+        after = ex.getRests()
+        sent_sum += (before.double() + v.double() - after.double()).sum().cpu()
+        ex.readRemote_add(recv_acc)
+        env.barrier()
+    final_rest = ex.getRests().double().sum().cpu()
+    assert abs(float(sent_sum + final_rest - in_sum)) < 1e-2, (float(sent_sum), float(final_rest), float(in_sum))
+    # what the peer received is what the left neighbour sent
+    gathered = [None] * world
+    dist.all_gather_object(gathered, float(sent_sum))
+    assert abs(float(recv_acc.double().sum().cpu()) - gathered[(rank - 1) % world]) < 1e-2
+
+    ring = cx.RingAllreduce(env)
+    ring.setup_connections(n, 1)
+    cring = cx.Comprex_RingAllreduce(env)
+    cring.setup_connections(n, 1, ratio, 2.5)
+    g = torch.Generator().manual_seed(1000 + rank)
+    v = torch.randn(n, generator=g).to(device)
+    vs = [torch.randn(n, generator=torch.Generator().manual_seed(1000 + r)) for r in range(world)]
+    dense = sum(x.double() for x in vs)
+    out = ring.apply(v.clone())
+    assert (out.double().cpu() - dense).abs().max().item() < 1e-5
+    acc = torch.zeros(n, device=device)
+    for step in range(3):
+        x = v.clone()
+        cring.apply(x)
+    x = torch.zeros(n, device=device)
+    # after a flush every rank holds the owners' exact chunks; the owned chunk saw 3 dense sums
+    cring.flush(x)
+    env.barrier()
+    env.close()
+    return True
+
+
+def scenario_allreduce_variants(rank, world, device):
+    import comprex_b200 as cx
+    from helpers import alt_ramp
+    env = cx.GaspiEnvironment(32 << 20, device=device, timeout_ms=20000)
+    n = 20011
+    for cls, kw in [(cx.AllToOneAllreduce, dict(chiefRank=0)), (cx.RingAllreduce, {}), (cx.BigRingAllreduce, {})]:
+        ar = cls(env)
+        ar.setup_connections(n, 1, **kw)
+        for step in range(3):
+            vs = [torch.randn(n, generator=torch.Generator().manual_seed(10 * step + r)) for r in range(world)]
+            out = ar.apply(vs[rank].clone().to(device))
+            assert (out.double().cpu() - sum(v.double() for v in vs)).abs().max().item() < 1e-5
+    vals = alt_ramp(n, device)
+    runs = 5
+    for cls, kw in [(cx.Comprex_BigRingAllreduce, {}), (cx.Comprex_RingAllreduce, {}),
+                    (cx.Comprex_AllToOneAllreduce, dict(chiefRank=0))]:
+        ar = cls(env)
+        ar.setup_connections(n, 1, compression_ratio=0.02, size_factor=3.0, **kw)
+        acc = vals.clone()
+        for _ in range(runs):
+            ar.apply(acc if rank == 0 else vals.clone())
+        ar.flush(acc if rank == 0 else torch.zeros(n, device=device))
+        env.barrier()
+        if rank == 0:
+            expect = (runs * (world - 1) + 1) * vals
+            if cls is cx.Comprex_RingAllreduce:
+                c = 1 % world
+                sl = slice(ar.segment_starts[c], ar.segment_starts[c] + ar.segment_sizes[c])
+                assert torch.equal(acc[sl], expect[sl])
+            else:
+                assert torch.equal(acc, expect)
+    # consistent mode: identical bits on every rank
+    ar = cx.Comprex_BigRingAllreduce(env)
+    ar.setup_connections(n, 1, 0.02, 3.0, consistent=True)
+    for step in range(4):
+        x = torch.randn(n, generator=torch.Generator().manual_seed(100 * step + rank)).to(device)
+        ar.apply(x)
+        got = [None] * world
+        dist.all_gather_object(got, x.cpu())
+        for other in got[1:]:
+            assert torch.equal(other, got[0])
+    env.barrier()
+    env.close()
+    return True
+
+
+def scenario_missing_sender(rank, world, device):
+    """Rank 1 skips its send: rank 0's wait must give up with TIMEOUT, not hang; then recover."""
+    import comprex_b200 as cx
+    env = cx.GaspiEnvironment(8 << 20, device=device, timeout_ms=300)
+    ex = cx.GaspiEx(env, 1000)
+    ex.connectTo((rank - 1) % world, (rank + 1) % world, 0)
+    v = torch.full((1000,), float(rank + 1), device=device)
+    raised = False
+    if rank == 0:
+        ex.writeRemote(v)
+        try:
+            ex.readRemote()
+            env.flush()
+        except cx.ComprexError as exc:
+            raised = "TIMEOUT" in str(exc)
+        assert raised
+    else:
+        out = ex.readRemote()       # the message from rank 0 arrives ...
+        env.flush()
+        assert float(out[0]) == 1.0
+        # ... but this rank "fails" before sending its own
+    dist.barrier()
+    # recovery: the late message is sent now; the receiver's expected sequence number still matches
+    if rank == 1:
+        ex.writeRemote(v)
+    dist.barrier()
+    if rank == 0:
+        ex._rx_seq[ex._src] -= 1     # retry the read that timed out
+        out = ex.readRemote()
+        env.flush()
+        assert float(out[0]) == 2.0
+    env.barrier()
+    env.close()
+    return raised
+
+
+def scenario_broadcast(rank, world, device):
+    import comprex_b200 as cx
+    from comprex_b200.callbacks import broadcast_parameters, SynchWeights
+    env = cx.GaspiEnvironment(8 << 20, device=device)
+    torch.manual_seed(rank)
+    model = torch.nn.Sequential(torch.nn.Linear(13, 7), torch.nn.ReLU(), torch.nn.Linear(7, 3)).to(device)
+    broadcast_parameters(model, env, src=0)
+    flat = torch.cat([p.detach().reshape(-1).cpu() for p in model.parameters()])
+    got = [None] * world
+    dist.all_gather_object(got, flat)
+    for other in got[1:]:
+        assert torch.equal(other, got[0])
+    sync = SynchWeights(2, 0, env)
+    with torch.no_grad():
+        for p in model.parameters():
+            p.add_(rank)
+    sync.on_train_begin(model)
+    sync.on_epoch_begin(model)      # epoch 1: nothing
+    sync.on_epoch_begin(model)      # epoch 2: synchronise
+    flat = torch.cat([p.detach().reshape(-1).cpu() for p in model.parameters()])
+    dist.all_gather_object(got, flat)
+    for other in got[1:]:
+        assert torch.equal(other, got[0])
+    env.barrier()
+    env.close()
+    return True
+
+
+# ---- tests --------------------------------------------------------------------------------------------
+def test_config1_two_ranks_cpu():
+    run_ranks(2, "scenario_config1", args=(1 << 20, 20, 0.01))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_allreduce_variants_cpu_ranks(world):
+    run_ranks(world, "scenario_allreduce_variants")
+
+
+def test_missing_sender_times_out_cpu():
+    assert run_ranks(2, "scenario_missing_sender")[0] is True
+
+
+def test_broadcast_and_sync_cpu():
+    run_ranks(3, "scenario_broadcast")
+
+
+def _gpus():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_config1_two_gpus():
+    run_ranks(2, "scenario_config1", backend="nccl", args=(1 << 20, 20, 0.01))
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_allreduce_variants_gpus():
+    run_ranks(min(_gpus(), 4), "scenario_allreduce_variants", backend="nccl")
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_missing_sender_times_out_gpus():
+    assert run_ranks(2, "scenario_missing_sender", backend="nccl")[0] is True
