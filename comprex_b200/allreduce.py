@@ -317,7 +317,9 @@ class Comprex_BigRingAllreduce(_ComprexAllreduceBase):
                     return
                 src = P.make_sources([self._slots[j][par].endpoint(env) for j in order], [seq] * len(order))
                 if recv_args is not None:
-                    args = recv_args  # fused averaging + parameter update instead of a dense result
+                    # fused averaging + parameter update instead of a dense result; ``True``
+                    # means "whatever the owner sets in _recv_args_now before this phase runs"
+                    args = self._recv_args_now if recv_args is True else recv_args
                 else:
                     args = P.args_set(t) if (self.consistent and first) else P.args_add(t)
                 P.apply_sparse(env, src, self.size, args, self._status)

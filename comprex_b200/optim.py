@@ -6,7 +6,7 @@ momentum buffer scaled by the learning rate (``mom = m*mom + lr*g``),
 concatenates everything into one blob, allreduces the blob with one of six
 collectives (default ``comprex_bigring``), divides by the number of ranks and
 applies ``var = (1-wd)*var - update``.  This class keeps those semantics for
-PyTorch and maps them onto three kernel launches per step and blob:
+PyTorch and maps the exchange onto three kernel launches per bucket:
 
 1. threshold estimate of ``residual + update`` (device resident),
 2. fused ``residual += update`` / select / store pairs into every peer's slot,
@@ -15,12 +15,17 @@ PyTorch and maps them onto three kernel launches per step and blob:
    in bf16 or fp16.
 
 The parameters live in one flat fp32 master buffer (the model's tensors are
-views of it, or of its low-precision shadow), gradients accumulate directly
-into one flat buffer, so no concatenation or slicing copy happens.  Every
-rank, the sender included, applies exactly what was transmitted (its own dense
-remainder stays in its residual), so replicas stay bit-identical.  Unlike the
-reference the single-rank case uses the same rule as the multi-rank case (the
-reference drops the learning rate there, keras/comprex_optimizer.py:134-141).
+views of it, or of its low-precision shadow) and gradients accumulate directly
+into one flat buffer, so no concatenation or slicing copy happens.  The flat
+buffers are laid out in reverse parameter order and cut into buckets of
+``bucket_cap_mb``; with ``overlap=True`` a bucket's steps 1-2 are launched on a
+side stream from a post-accumulate-grad hook as soon as its last gradient is
+produced, i.e. while backward is still running for earlier layers, and
+``step()`` only launches the receive/update kernels.  Every rank, the sender
+included, applies exactly what was transmitted (its own dense remainder stays
+in its residual), so replicas stay bit-identical.  Unlike the reference the
+single-rank case uses the same rule as the multi-rank case (the reference
+drops the learning rate there, keras/comprex_optimizer.py:134-141).
 
 ``rule="adamw"`` exchanges the clipped gradient itself and runs AdamW in the
 receive kernel.  Residuals, momentum and master weights travel in
@@ -41,11 +46,20 @@ _TYPES = {
 }
 
 
+class _Bucket:
+    __slots__ = ("start", "end", "params", "grad_views", "ar", "ready", "sent")
+
+    def __init__(self, start):
+        self.start, self.end = start, start
+        self.params, self.grad_views = [], []
+        self.ar, self.ready, self.sent = None, 0, False
+
+
 class ComprexOptimizer(torch.optim.Optimizer):
     def __init__(self, params, gaspi_env, lr=0.01, momentum=0.9, compression_ratio=0.01, nesterov=False,
                  allreduce_type="comprex_bigring", size_factor=1.0, logging=False, pre_clipnorm=5.0,
                  weight_decay=0.0, local_momentum=True, rule="sgd", betas=(0.9, 0.999), eps=1e-8,
-                 learning_rate=None):
+                 learning_rate=None, bucket_cap_mb=None, overlap=False):
         if learning_rate is not None:
             lr = learning_rate
         if not 0 <= momentum <= 1:
@@ -69,6 +83,9 @@ class ComprexOptimizer(torch.optim.Optimizer):
         self.betas, self.eps = betas, eps
         self.momentum_correction = 1.0
         self._t = 0
+        self._fused = allreduce_type == "comprex_bigring"
+        if (bucket_cap_mb or overlap) and not self._fused:
+            raise ComprexError("buckets and overlap need allreduce_type='comprex_bigring'")
 
         plist = [p for g in self.param_groups for p in g["params"] if p.requires_grad]
         if not plist:
@@ -76,30 +93,51 @@ class ComprexOptimizer(torch.optim.Optimizer):
         dt = plist[0].dtype
         if any(p.dtype != dt or p.device != env.device for p in plist):
             raise ComprexError("all parameters must share one dtype and live on the environment's device")
-        self._params = plist
-        # 16-byte aligned segments keep every tensor view vectorisable
-        self._offsets, off = [], 0
-        for p in plist:
+        # reverse order: the gradients that backward produces first come first
+        self._params = plist[::-1]
+        es = torch.empty(0, dtype=dt).element_size()
+        cap_elems = int(bucket_cap_mb * (1 << 20) / es) if bucket_cap_mb else None
+        self._buckets, self._offsets, off = [_Bucket(0)], [], 0
+        for p in self._params:
+            b = self._buckets[-1]
+            if cap_elems and b.params and (off - b.start) + p.numel() > cap_elems:
+                off = (off + 1023) // 1024 * 1024          # buckets start on a sub-tile boundary
+                b = _Bucket(off)
+                self._buckets.append(b)
             self._offsets.append(off)
-            off += (p.numel() + 3) // 4 * 4
+            b.params.append(p)
+            off += (p.numel() + 3) // 4 * 4                 # 16-byte aligned tensors
+            b.end = off
         self.blob_size = n = off
         dev = env.device
         self._master = torch.zeros(n, dtype=torch.float32, device=dev)
         self._shadow = torch.zeros(n, dtype=dt, device=dev) if dt != torch.float32 else None
         self._grad = torch.zeros(n, dtype=dt, device=dev)
         store = self._shadow if self._shadow is not None else self._master
-        for p, o in zip(plist, self._offsets):
+        self._bucket_of = {}
+        bi = 0
+        for p, o in zip(self._params, self._offsets):
             k = p.numel()
             self._master[o:o + k].copy_(p.detach().reshape(-1))
             store[o:o + k].copy_(p.detach().reshape(-1))
             p.data = store[o:o + k].view_as(p)
             p.grad = self._grad[o:o + k].view_as(p)
-        self._grad_views = [self._grad[o:o + p.numel()] for p, o in zip(plist, self._offsets)]
+            while o >= self._buckets[bi].end:
+                bi += 1
+            self._buckets[bi].grad_views.append(self._grad[o:o + k])
+            self._bucket_of[p] = self._buckets[bi]
         self._update = torch.zeros(n, dtype=torch.float32, device=dev)   # momentum_var / exchanged vector
         self._m = torch.zeros(n, dtype=torch.float32, device=dev) if rule == "adamw" or not local_momentum else None
         self._v = torch.zeros(n, dtype=torch.float32, device=dev) if rule == "adamw" else None
         self.comprex_allreducers = {}
-        self._allreduce = None
+        self._xbuf = None
+        self._comm = None
+        self.overlap = bool(overlap) and dev.type == "cuda"
+        self._armed = False
+        self._hooks = []
+        if self.overlap:
+            for p in self._params:
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad))
 
     # ---- reference surface -----------------------------------------------------------------
     def set_compression_ratio(self, compression_ratio) -> None:
@@ -124,34 +162,81 @@ class ComprexOptimizer(torch.optim.Optimizer):
             ar.setup_connections(size, 1)
         return ar
 
+    def _ensure_allreducers(self) -> None:
+        if self.comprex_allreducers:
+            return
+        if self._fused:
+            for i, b in enumerate(self._buckets):
+                b.ar = self.comprex_allreducers[i] = self.create_allreduce_op(self.allreduce_type, b.end - b.start)
+        else:
+            self._buckets[0].ar = self.comprex_allreducers[0] = self.create_allreduce_op(self.allreduce_type, self.blob_size)
+        self._armed = True
+
     def zero_grad(self, set_to_none: bool = False) -> None:
         """Zero the flat gradient buffer; the per-parameter views stay attached."""
         self._grad.zero_()
+        es = self._grad.element_size()
         for p, o in zip(self._params, self._offsets):
-            if p.grad is None or p.grad.data_ptr() != self._grad.data_ptr() + o * self._grad.element_size():
+            if p.grad is None or p.grad.data_ptr() != self._grad.data_ptr() + o * es:
                 p.grad = self._grad[o:o + p.numel()].view_as(p)
 
     # ---- the step ---------------------------------------------------------------------------------
-    def _clip_coefficients(self):
-        if self.pre_clipnorm is None:
-            return None
-        norms = torch._foreach_norm(self._grad_views)
-        clip = float(self.pre_clipnorm)
-        # tf.clip_by_norm: g * clip / max(norm, clip)
-        return [clip / torch.clamp(nrm.float(), min=clip) for nrm in norms]
-
-    def _fold(self, lr: float, mu: float) -> torch.Tensor:
-        """Clip per tensor and build the vector that is exchanged."""
-        coefs = self._clip_coefficients()
-        if coefs is not None:
-            torch._foreach_mul_(self._grad_views, [c.to(self._grad.dtype) for c in coefs])
+    def _fold(self, b: _Bucket, lr: float, mu: float) -> torch.Tensor:
+        """Clip per tensor and build the vector that is exchanged for one bucket."""
+        if self.pre_clipnorm is not None:
+            clip = float(self.pre_clipnorm)
+            norms = torch._foreach_norm(b.grad_views)
+            # tf.clip_by_norm: g * clip / max(norm, clip)
+            coefs = [(clip / torch.clamp(nrm.float(), min=clip)).to(self._grad.dtype) for nrm in norms]
+            torch._foreach_mul_(b.grad_views, coefs)
+        g = self._grad[b.start:b.end]
+        u = self._update[b.start:b.end]
         if self.rule == "sgd" and self.local_momentum:
-            self._update.mul_(mu * self.momentum_correction).add_(self._grad, alpha=lr)
-            return self._update
-        if self._grad.dtype == torch.float32:
-            return self._grad
-        self._update.copy_(self._grad)
-        return self._update
+            u.mul_(mu * self.momentum_correction).add_(g, alpha=lr)
+            return u
+        if g.dtype == torch.float32:
+            return g
+        u.copy_(g)
+        return u
+
+    def _hyper(self):
+        group = self.param_groups[0]
+        return float(group["lr"]), float(group["momentum"]), float(group["weight_decay"])
+
+    def _comm_stream(self):
+        if self._comm is None:
+            self._comm = torch.cuda.Stream(self._env.device, priority=-1)
+        return self._comm
+
+    def _send(self, b: _Bucket) -> None:
+        lr, mu, _ = self._hyper()
+        x = self._fold(b, lr, mu)
+        ar = b.ar
+        ar._pending_plan = ar._plan_apply(x, recv_args=True)
+        ar._pending_plan[0]()
+        b.sent = True
+
+    def _on_grad(self, p) -> None:
+        b = self._bucket_of[p]
+        b.ready += 1
+        if not self._armed or b.ready < len(b.params) or b.sent:
+            return
+        comm = self._comm_stream()
+        comm.wait_stream(torch.cuda.current_stream(self._env.device))
+        with torch.cuda.stream(comm):
+            self._send(b)
+
+    def _recv_args(self, b: _Bucket, lr, mu, wd):
+        nr = self._env.ranks
+        sl = slice(b.start, b.end)
+        sh = None if self._shadow is None else self._shadow[sl]
+        if self.rule == "adamw":
+            return P.args_update(_lib.OP_ADAMW, self._master[sl], 1.0 / nr, shadow=sh, m=self._m[sl], v=self._v[sl],
+                                 lr=lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps, wd=wd, step=self._t)
+        if self.local_momentum:
+            return P.args_update(_lib.OP_SGD, self._master[sl], 1.0 / nr, shadow=sh, wd=wd)
+        return P.args_update(_lib.OP_MOMENTUM, self._master[sl], 1.0 / nr, shadow=sh, m=self._m[sl], lr=lr,
+                             momentum=mu * self.momentum_correction, wd=wd)
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -159,32 +244,38 @@ class ComprexOptimizer(torch.optim.Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
-        group = self.param_groups[0]
-        lr, mu, wd = float(group["lr"]), float(group["momentum"]), float(group["weight_decay"])
+        lr, mu, wd = self._hyper()
         self._t += 1
-        x = self._fold(lr, mu)
-        if self._allreduce is None:
-            self._allreduce = self.comprex_allreducers[0] = self.create_allreduce_op(self.allreduce_type, self.blob_size)
-        ar, nr = self._allreduce, self._env.ranks
-        if self.rule == "adamw":
-            args = P.args_update(_lib.OP_ADAMW, self._master, 1.0 / nr, shadow=self._shadow, m=self._m, v=self._v,
-                                 lr=lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps, wd=wd, step=self._t)
-        elif self.local_momentum:
-            args = P.args_update(_lib.OP_SGD, self._master, 1.0 / nr, shadow=self._shadow, wd=wd)
+        first = not self.comprex_allreducers
+        self._ensure_allreducers()
+        if not self._fused:
+            self._generic_step(self._buckets[0].ar, self._fold(self._buckets[0], lr, mu), lr, mu, wd)
+            self._env.maybe_check()
+            return loss
+        use_side = self.overlap and not first
+        if use_side:
+            comm = self._comm_stream()
+            comm.wait_stream(torch.cuda.current_stream(self._env.device))
+            ctx = torch.cuda.stream(comm)
         else:
-            args = P.args_update(_lib.OP_MOMENTUM, self._master, 1.0 / nr, shadow=self._shadow, m=self._m, lr=lr,
-                                 momentum=mu * self.momentum_correction, wd=wd)
-        if isinstance(ar, _ar.Comprex_BigRingAllreduce):
-            for phase in ar._plan_apply(x, recv_args=args):
-                phase()
-        else:
-            self._generic_step(ar, x, lr, mu, wd)
+            import contextlib
+            ctx = contextlib.nullcontext()
+        with ctx:
+            for b in self._buckets:          # everything that the hooks did not send yet
+                if not b.sent:
+                    self._send(b)
+            for b in self._buckets:          # then receive: all peers' payloads are on their way
+                b.ar._recv_args_now = self._recv_args(b, lr, mu, wd)
+                b.ar._pending_plan[1]()
+                b.sent, b.ready = False, 0
+        if use_side:
+            torch.cuda.current_stream(self._env.device).wait_stream(comm)
         self._env.maybe_check()
         return loss
 
     def _generic_step(self, ar, x, lr, mu, wd) -> None:
         """Other collectives: allreduce a copy of the vector in place, then update with tensor ops."""
-        if getattr(self, "_xbuf", None) is None:
+        if self._xbuf is None:
             self._xbuf = torch.empty(self.blob_size, dtype=torch.float32, device=self._env.device)
         buf = self._xbuf
         buf.copy_(x)
@@ -207,30 +298,38 @@ class ComprexOptimizer(torch.optim.Optimizer):
 
     def flush(self) -> None:
         """Apply everything still held in residuals (end of training)."""
-        if self._allreduce is None or not self._allreduce.compressed:
+        if not self.comprex_allreducers:
             return
-        buf = torch.zeros(self.blob_size, dtype=torch.float32, device=self._env.device)
-        self._allreduce.flush(buf)
-        if self.rule == "sgd" and self.local_momentum:
-            # residuals hold lr-scaled updates: apply them like a received update
-            self._master.sub_(buf / self._env.ranks)
-            if self._shadow is not None:
-                self._shadow.copy_(self._master)
+        for b in self._buckets:
+            ar = b.ar
+            if ar is None or not ar.compressed:
+                continue
+            buf = torch.zeros(ar.size, dtype=torch.float32, device=self._env.device)
+            ar.flush(buf)
+            if self.rule == "sgd" and self.local_momentum:
+                # residuals hold lr-scaled updates: apply them like a received update
+                sl = slice(b.start, b.start + ar.size)
+                self._master[sl].sub_(buf / self._env.ranks)
+                if self._shadow is not None:
+                    self._shadow[sl].copy_(self._master[sl])
 
     def stats(self) -> dict:
-        return self._allreduce.stats() if self._allreduce is not None and self._allreduce.compressed else {}
+        """Statistics of the first bucket's last compression (synchronises)."""
+        ar = self._buckets[0].ar
+        return ar.stats() if ar is not None and ar.compressed else {}
 
     # ---- checkpoint ---------------------------------------------------------------------------------
     def state_dict(self):
         sd = super().state_dict()
-        ar = self._allreduce
+        self._env.flush()
+        ars = [b.ar for b in self._buckets]
         sd["comprex"] = {
             "version": 1, "world_size": self._env.ranks, "rank": self._env.rank, "ratio": self.compression_ratio,
             "topology": self.allreduce_type, "step": self._t, "rule": self.rule,
             "master": self._master.detach().cpu().clone(), "update": self._update.detach().cpu().clone(),
             "m": None if self._m is None else self._m.detach().cpu().clone(),
             "v": None if self._v is None else self._v.detach().cpu().clone(),
-            "allreduce": ar.state_dict() if ar is not None and ar.compressed else None,
+            "allreduce": [a.state_dict() if a is not None and a.compressed else None for a in ars],
         }
         return sd
 
@@ -253,14 +352,16 @@ class ComprexOptimizer(torch.optim.Optimizer):
             self._v.copy_(cs["v"].to(dev))
         if self._shadow is not None:
             self._shadow.copy_(self._master)
-        if cs["allreduce"] is not None:
-            if self._allreduce is None:
-                self._allreduce = self.comprex_allreducers[0] = self.create_allreduce_op(self.allreduce_type, self.blob_size)
-            if cs["world_size"] == self._env.ranks:
-                self._allreduce.load_state_dict(cs["allreduce"])
-            else:
-                # residuals are rank-local errors: a restart with another world size keeps
-                # what this rank had and starts the new ranks from zero
-                for dst, src in zip(self._allreduce._residuals(), cs["allreduce"]["residuals"]):
-                    if dst.numel() == src.numel():
-                        dst.copy_(src.to(dev))
+        if any(s is not None for s in cs["allreduce"]):
+            self._ensure_allreducers()
+            for b, s in zip(self._buckets, cs["allreduce"]):
+                if s is None or b.ar is None:
+                    continue
+                if cs["world_size"] == self._env.ranks:
+                    b.ar.load_state_dict(s)
+                else:
+                    # residuals are rank-local errors: a restart with another world size keeps
+                    # what this rank had and starts the new ranks from zero
+                    for dst, src in zip(b.ar._residuals(), s["residuals"]):
+                        if dst.numel() == src.numel():
+                            dst.copy_(src.to(dev))

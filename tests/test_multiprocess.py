@@ -38,7 +38,13 @@ def _entry(rank, world, port, backend, fn_name, q, args):
             os.environ["NCCL_NVLS_ENABLE"] = "0"
             torch.cuda.set_device(rank)
         dist.init_process_group(backend, rank=rank, world_size=world)
-        out = globals()[fn_name](rank, world, "cuda" if backend == "nccl" else "cpu", *args)
+        if ":" in fn_name:   # "module:function" for scenarios that live in another test file
+            import importlib
+            mod, name = fn_name.split(":")
+            fn = getattr(importlib.import_module(mod), name)
+        else:
+            fn = globals()[fn_name]
+        out = fn(rank, world, "cuda" if backend == "nccl" else "cpu", *args)
         q.put((rank, "ok", out))
     except Exception:
         q.put((rank, "error", traceback.format_exc()))

@@ -1,0 +1,272 @@
+"""ComprexOptimizer and the DDP hook: update rule vs a plain restatement of
+keras/comprex_optimizer.py:97-133,150-163, conservation through flush,
+bucketed layout, checkpoint/resume, replica consistency across real ranks.
+"""
+import copy
+
+import pytest
+import torch
+import torch.distributed as dist
+
+import comprex_b200 as cx
+from comprex_b200.models.lenet import LeNet5
+from comprex_b200.optim import ComprexOptimizer
+
+from test_multiprocess import run_ranks
+
+
+def _const_grad_model(device, seed=0):
+    torch.manual_seed(seed)
+    return torch.nn.ParameterList([torch.nn.Parameter(torch.randn(s, device=device)) for s in
+                                   [(300, 7), (1000,), (5,), (64, 64)]])
+
+
+def _set_grads(opt, params, cs):
+    opt.zero_grad()
+    for p, c in zip(params, cs):
+        p.grad.add_(c)
+
+
+@pytest.mark.parametrize("buckets", [None, 0.004])
+@pytest.mark.parametrize("local_momentum", [True, False])
+def test_sgd_rule_matches_reference_after_flush(device, buckets, local_momentum):
+    env = cx.GaspiEnvironment(8 << 20, device=device)
+    params = _const_grad_model(device)
+    w0 = [p.detach().clone() for p in params]
+    cs = [torch.randn_like(p) * 3 for p in params]
+    lr, mu, wd, clip, steps = 0.1, 0.9, 0.0, 5.0, 7
+    opt = ComprexOptimizer(params, env, lr=lr, momentum=mu, compression_ratio=0.05, size_factor=3.0,
+                           pre_clipnorm=clip, weight_decay=wd, local_momentum=local_momentum, bucket_cap_mb=buckets)
+    if buckets:
+        assert len(opt._buckets) > 1
+    for _ in range(steps):
+        _set_grads(opt, params, cs)
+        opt.step()
+    # restatement: clip_by_norm, mom = mu*mom + lr*g, w -= mom  (all of it arrives once residuals are flushed)
+    if local_momentum:
+        opt.flush()
+        for p, w, c in zip(params, w0, cs):
+            g = c * clip / max(float(c.norm()), clip)
+            mom, ref = torch.zeros_like(w), w.clone()
+            for _ in range(steps):
+                mom = mu * mom + lr * g
+                ref = ref - mom
+            torch.testing.assert_close(p.detach(), ref, rtol=1e-4, atol=1e-4)
+    else:
+        assert all(torch.isfinite(p).all() for p in params)
+    env.close()
+
+
+def test_training_reduces_loss_and_bf16_shadow(device):
+    torch.manual_seed(0)
+    env = cx.GaspiEnvironment(8 << 20, device=device)
+    model = LeNet5().to(device).to(torch.bfloat16)
+    opt = ComprexOptimizer(model.parameters(), env, lr=0.05, momentum=0.9, compression_ratio=0.1, size_factor=1.0)
+    x = torch.rand(64, 1, 28, 28, device=device).to(torch.bfloat16)
+    y = torch.randint(0, 10, (64,), device=device)
+    losses = []
+    for _ in range(40):
+        opt.zero_grad()
+        loss = torch.nn.functional.cross_entropy(model(x).float(), y)
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.detach()))
+    assert losses[-1] < losses[0] - 0.05
+    for p in model.parameters():   # the model's tensors are views of the bf16 shadow of the fp32 master
+        assert p.dtype == torch.bfloat16
+    assert torch.equal(opt._shadow, opt._master.to(torch.bfloat16))
+    st = opt.stats()
+    assert 0 < st["nnz"] < st["n"]
+    env.close()
+
+
+@pytest.mark.parametrize("rule", ["sgd", "adamw"])
+def test_checkpoint_resume_is_bit_exact(device, rule):
+    def make(seed=0):
+        torch.manual_seed(seed)
+        env = cx.GaspiEnvironment(8 << 20, device=device)
+        model = LeNet5().to(device)
+        opt = ComprexOptimizer(model.parameters(), env, lr=0.02, momentum=0.9, compression_ratio=0.02,
+                               size_factor=1.0, rule=rule, weight_decay=0.01, bucket_cap_mb=0.05)
+        return env, model, opt
+
+    def run(model, opt, steps, start):
+        for i in range(start, start + steps):
+            g = torch.Generator().manual_seed(i)
+            x = torch.rand(16, 1, 28, 28, generator=g).to(device)
+            y = torch.randint(0, 10, (16,), generator=g).to(device)
+            opt.zero_grad()
+            torch.nn.functional.cross_entropy(model(x), y).backward()
+            opt.step()
+
+    env_a, model_a, opt_a = make()
+    run(model_a, opt_a, 5, 0)
+    sd = copy.deepcopy(opt_a.state_dict())
+    assert sd["comprex"]["step"] == 5 and sd["comprex"]["allreduce"][0]["residuals"][0].abs().sum() > 0
+    run(model_a, opt_a, 4, 5)
+    env_b, model_b, opt_b = make(seed=99)          # fresh objects, different init
+    opt_b.load_state_dict(sd)
+    run(model_b, opt_b, 4, 5)
+    assert torch.equal(opt_a._master, opt_b._master)
+    for pa, pb in zip(model_a.parameters(), model_b.parameters()):
+        assert torch.equal(pa, pb)
+    env_a.close()
+    env_b.close()
+
+
+def test_other_allreduce_types_and_validation(device):
+    env = cx.GaspiEnvironment(8 << 20, device=device)
+    with pytest.raises(ValueError):
+        ComprexOptimizer(_const_grad_model(device), env, allreduce_type="nope")
+    with pytest.raises(ValueError):
+        ComprexOptimizer(_const_grad_model(device), env, momentum=1.5)
+    for kind in ["ring", "bigring", "alltoone", "comprex_ring", "comprex_alltoone"]:
+        params = _const_grad_model(device)
+        w0 = [p.detach().clone() for p in params]
+        cs = [torch.randn_like(p) for p in params]
+        opt = ComprexOptimizer(params, env, lr=0.1, momentum=0.0, compression_ratio=0.5, size_factor=3.0,
+                               allreduce_type=kind, pre_clipnorm=None)
+        _set_grads(opt, params, cs)
+        opt.step()
+        if not kind.startswith("comprex"):   # single rank, dense: exactly one SGD step
+            for p, w, c in zip(params, w0, cs):
+                torch.testing.assert_close(p.detach(), w - 0.1 * c)
+        opt.set_compression_ratio(0.25)
+    env.close()
+
+
+# ---- real ranks -------------------------------------------------------------------------------------
+def scenario_optimizer_ranks(rank, world, device, overlap):
+    env = cx.GaspiEnvironment(16 << 20, device=device)
+    torch.manual_seed(7)                      # same initial weights everywhere
+    model = LeNet5().to(device)
+    opt = ComprexOptimizer(model.parameters(), env, lr=0.05, momentum=0.9, compression_ratio=0.05, size_factor=1.0,
+                           bucket_cap_mb=0.05, overlap=overlap)
+    first = None
+    for i in range(12):
+        g = torch.Generator().manual_seed(1000 * rank + i)
+        x = torch.rand(32, 1, 28, 28, generator=g).to(device)
+        y = (x.mean(dim=(1, 2, 3)) * 20).long().clamp(0, 9).to(device)
+        opt.zero_grad()
+        loss = torch.nn.functional.cross_entropy(model(x), y)
+        loss.backward()
+        opt.step()
+        first = first if first is not None else float(loss)
+        flat = opt._master.detach().cpu()
+        got = [None] * world
+        dist.all_gather_object(got, flat)
+        for other in got[1:]:
+            assert torch.equal(other, got[0]), "replicas diverged"
+    env.barrier()
+    env.close()
+    return first, float(loss)
+
+
+def scenario_ddp_hook(rank, world, device):
+    from torch.nn.parallel import DistributedDataParallel as DDP
+    from comprex_b200.ddp_hook import ComprexHookState, comprex_hook
+    import pickle
+    env = cx.GaspiEnvironment(16 << 20, device=device)
+    torch.manual_seed(3)
+    base = torch.nn.Sequential(torch.nn.Linear(50, 200), torch.nn.ReLU(), torch.nn.Linear(200, 10)).to(device)
+    ids = [rank] if device == "cuda" else None
+    # dense fallback for every bucket: must equal the stock averaging allreduce
+    m_ref, m_dense = copy.deepcopy(base), copy.deepcopy(base)
+    ddp_ref = DDP(m_ref, device_ids=ids)
+    ddp_dense = DDP(m_dense, device_ids=ids)
+    ddp_dense.register_comm_hook(ComprexHookState(env, dense_fallback_bytes=1 << 40), comprex_hook)
+    g = torch.Generator().manual_seed(rank)
+    x, y = torch.randn(16, 50, generator=g).to(device), torch.randint(0, 10, (16,), generator=g).to(device)
+    for ddp in (ddp_ref, ddp_dense):
+        torch.nn.functional.cross_entropy(ddp(x), y).backward()
+    if device == "cuda":
+        torch.cuda.synchronize()
+    for a, b in zip(m_ref.parameters(), m_dense.parameters()):
+        torch.testing.assert_close(a.grad, b.grad, rtol=1e-5, atol=1e-6)
+    # compressed: what arrives over the steps plus the residuals is the true average gradient sum
+    m_c = copy.deepcopy(base)
+    ddp_c = DDP(m_c, device_ids=ids)
+    state = ComprexHookState(env, compression_ratio=0.05, dense_fallback_bytes=0, capacity_slack=4.0)
+    ddp_c.register_comm_hook(state, comprex_hook)
+    applied = [torch.zeros_like(p) for p in m_c.parameters()]
+    true_sum = [torch.zeros_like(p) for p in m_c.parameters()]
+    for step in range(5):
+        for p in list(m_c.parameters()) + list(m_ref.parameters()):
+            p.grad = None
+        torch.nn.functional.cross_entropy(ddp_c(x), y).backward()
+        torch.nn.functional.cross_entropy(ddp_ref(x), y).backward()
+        if device == "cuda":
+            torch.cuda.synchronize()
+        for acc, p in zip(applied, m_c.parameters()):
+            acc += p.grad
+        for acc, p in zip(true_sum, m_ref.parameters()):
+            acc += p.grad
+        got = [None] * world
+        dist.all_gather_object(got, torch.cat([p.grad.reshape(-1).cpu() for p in m_c.parameters()]))
+        for other in got[1:]:
+            assert torch.equal(other, got[0])
+    res_total = 0.0
+    for red in state.reducers.values():
+        if red.compressed:
+            r = red.rests.clone()
+            dist.all_reduce(r)
+            res_total += float(r.double().sum()) / world
+    lhs = sum(float(a.double().sum()) for a in applied) + res_total
+    rhs = sum(float(t.double().sum()) for t in true_sum)
+    assert abs(lhs - rhs) < 1e-3 * max(1.0, abs(rhs)), (lhs, rhs)
+    blob = pickle.dumps(state)
+    restored = pickle.loads(blob).attach(env)
+    assert restored.compression_ratio == state.compression_ratio and len(restored._pending) > 0
+    env.barrier()
+    env.close()
+    return True
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_optimizer_replicas_stay_identical_cpu(world):
+    out = run_ranks(world, "test_optimizer:scenario_optimizer_ranks", args=(False,))
+    assert all(last < first for first, last in out)
+
+
+def test_ddp_hook_cpu():
+    run_ranks(2, "test_optimizer:scenario_ddp_hook")
+
+
+def _gpus():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("overlap", [False, True])
+def test_optimizer_replicas_stay_identical_gpus(overlap):
+    run_ranks(2, "test_optimizer:scenario_optimizer_ranks", backend="nccl", args=(overlap,))
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_ddp_hook_gpus():
+    run_ranks(2, "test_optimizer:scenario_ddp_hook", backend="nccl")
+
+
+@pytest.mark.gpu
+def test_overlap_matches_no_overlap_single_gpu():
+    """Hooks on a side stream give the same bits as launching everything in step()."""
+    res = []
+    for overlap in (False, True):
+        torch.manual_seed(0)
+        env = cx.GaspiEnvironment(16 << 20, device="cuda")
+        model = LeNet5().cuda()
+        opt = ComprexOptimizer(model.parameters(), env, lr=0.05, compression_ratio=0.05, size_factor=1.0,
+                               bucket_cap_mb=0.05, overlap=overlap)
+        for i in range(6):
+            g = torch.Generator().manual_seed(i)
+            x = torch.rand(32, 1, 28, 28, generator=g).cuda()
+            y = torch.randint(0, 10, (32,), generator=g).cuda()
+            opt.zero_grad()
+            torch.nn.functional.cross_entropy(model(x), y).backward()
+            opt.step()
+        env.flush()
+        res.append(opt._master.clone())
+        env.close()
+    assert torch.equal(res[0], res[1])
