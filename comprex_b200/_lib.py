@@ -13,13 +13,12 @@ import threading
 import torch
 
 MAX_PEERS = 16
-TILE = 4096
 SUBTILE = 1024
 
 DEV_HOST, DEV_CUDA = 0, 1
 F32, BF16, F16 = 0, 1, 2
 KIND_PAIRS, KIND_DENSE, KIND_RLE = 1, 2, 3
-ST_TIMEOUT, ST_BAD_HEADER, ST_OVERFLOW, ST_BAD_INDEX, ST_LOOKBACK = 1, 2, 4, 8, 16
+ST_TIMEOUT, ST_BAD_HEADER, ST_OVERFLOW, ST_BAD_INDEX = 1, 2, 4, 8
 OP_ADD, OP_SET, OP_SGD, OP_MOMENTUM, OP_ADAMW = 0, 1, 2, 3, 4
 
 _DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
@@ -37,7 +36,7 @@ class Header(C.Structure):
 
 
 class Endpoint(C.Structure):
-    _fields_ = [("hdr", C.c_void_p), ("prefix", C.c_void_p), ("pairs", C.c_void_p)]
+    _fields_ = [("hdr", C.c_void_p), ("table", C.c_void_p), ("pairs", C.c_void_p)]
 
 
 class Targets(C.Structure):
@@ -170,7 +169,7 @@ def stream_ptr(device: torch.device) -> int:
 def decode_status(bits: int) -> str:
     names = []
     for bit, name in ((ST_TIMEOUT, "TIMEOUT"), (ST_BAD_HEADER, "BAD_HEADER"), (ST_OVERFLOW, "OVERFLOW"),
-                      (ST_BAD_INDEX, "BAD_INDEX"), (ST_LOOKBACK, "LOOKBACK")):
+                      (ST_BAD_INDEX, "BAD_INDEX")):
         if bits & bit:
             names.append(name)
     return "|".join(names) or "OK"

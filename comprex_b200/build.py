@@ -56,7 +56,9 @@ def _compile(src: Path, verbose: bool, ptxas_v: bool) -> Path:
     if not _stale(obj, [src] + headers):
         return obj
     if src.suffix == ".cu":
-        cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_v else []) + ["-c", str(src), "-o", str(obj)]
+        extra = os.environ.get("COMPREX_NVCC_EXTRA", "").split()   # e.g. -DCX_COMPRESS_MIN_BLOCKS=3
+        cmd = ([_nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if ptxas_v else [])
+               + ["-c", str(src), "-o", str(obj)])
     else:
         cmd = [os.environ.get("CXX", "g++")] + CXX_FLAGS + ["-c", str(src), "-o", str(obj)]
     if verbose:

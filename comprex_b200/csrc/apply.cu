@@ -5,9 +5,10 @@
 // src/comprEx.tpp:224-246; optimizer math keras/comprex_optimizer.py:150-163).
 //
 // Ownership instead of atomics: every payload carries, per 1024-element
-// sub-tile of the vector, the offset of that sub-tile's first pair.  A warp
-// owns one sub-tile at a time, looks the ranges [prefix[s], prefix[s+1]) of
-// all sources up directly and applies them source after source.  Indices are
+// sub-tile of the vector, a table entry {start, count} that says where that
+// sub-tile's pairs sit in the pair list.  A warp owns one sub-tile at a time,
+// looks the ranges of all sources up directly and applies them source after
+// source.  Indices are
 // unique inside one payload and a sub-tile has a single owner, so no atomic
 // is needed and the floating-point sum order is the same on every rank, which
 // keeps data-parallel replicas bit-identical.
@@ -84,9 +85,9 @@ __global__ void __launch_bounds__(kThreads) apply_sparse_kernel(const ApplyParam
     const uint32_t lo = sub * CX_SUBTILE;
     uint32_t a = 0, b = 0;
     if (lane < p.src.count) {
-      a = __ldcg(p.src.ep[lane].prefix + sub);
-      b = __ldcg(p.src.ep[lane].prefix + sub + 1);
-      b = min(b, s_nnz[lane]);
+      const uint2 entry = __ldcg(reinterpret_cast<const uint2*>(p.src.ep[lane].table) + sub);
+      a = entry.x;
+      b = min(entry.x + min(entry.y, (uint32_t)CX_SUBTILE), s_nnz[lane]);
       a = min(a, b);
     }
     for (int j = 0; j < p.src.count; ++j) {
@@ -191,9 +192,9 @@ __global__ void __launch_bounds__(kThreads) apply_dense_kernel(const ApplyParams
     const uint32_t lo = sub * CX_SUBTILE;
     uint32_t a = 0, b = 0;
     if (lane < p.src.count) {
-      a = __ldcg(p.src.ep[lane].prefix + sub);
-      b = __ldcg(p.src.ep[lane].prefix + sub + 1);
-      b = min(b, s_nnz[lane]);
+      const uint2 entry = __ldcg(reinterpret_cast<const uint2*>(p.src.ep[lane].table) + sub);
+      a = entry.x;
+      b = min(entry.x + min(entry.y, (uint32_t)CX_SUBTILE), s_nnz[lane]);
       a = min(a, b);
     }
 #pragma unroll
@@ -259,9 +260,11 @@ __global__ void __launch_bounds__(kThreads) forward_kernel(const ForwardParams p
   const uint32_t nsub = h->nsub;
   const uint64_t gtid = (uint64_t)blockIdx.x * kThreads + threadIdx.x;
   const uint64_t gsz = (uint64_t)gridDim.x * kThreads;
-  for (uint64_t i = gtid; i <= nsub; i += gsz) {
-    const uint32_t v = min(__ldcg(p.from.prefix + i), p.cap);
-    for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].prefix[i] = v;
+  for (uint64_t i = gtid; i < nsub; i += gsz) {
+    uint2 v = __ldcg(reinterpret_cast<const uint2*>(p.from.table) + i);
+    if (v.x >= nnz) v.x = v.y = 0;
+    else v.y = min(v.y, nnz - v.x);
+    for (int k = 0; k < p.tg.count; ++k) reinterpret_cast<uint2*>(p.tg.ep[k].table)[i] = v;
   }
   for (uint64_t i = gtid; i < nnz; i += gsz) {
     const uint2 v = __ldcg(reinterpret_cast<const uint2*>(p.from.pairs + i));

@@ -1,4 +1,4 @@
-// Fused residual-add / threshold-select / ordered compaction / peer store.
+// Fused residual-add / threshold-select / compaction / peer store.
 //
 // One pass over the vector does what the reference does in
 // ThresholdFunction + CompressorIndexPairs::compress_add_update followed by
@@ -7,15 +7,22 @@
 //
 //     r += g ; if |r| > thr { emit (i, r) ; r = 0 }
 //
-// The survivors leave the SM exactly once, as coalesced 8-byte (index, value)
-// stores that go straight into the receive slots of up to CX_MAX_PEERS
-// targets (peer GPUs' memory mapped over NVLink, or local slots).  Output is
-// in ascending index order like the reference's wire format: tiles are handed
-// out by an atomic counter and chained with a single-pass decoupled look-back
-// scan, so no second pass over the data and no sort is needed.  As a
-// by-product every 1024-element sub-tile's offset into the pair list is
-// written next to the pairs; receivers use it to find, without searching, the
-// pairs that fall into the part of the vector they own.
+// Work is warp-granular and free of block-wide barriers: a warp owns one
+// 1024-element sub-tile at a time, loads it with 16-byte accesses (32
+// elements per lane, all loads in flight together), ranks the survivors with
+// warp ballots, reserves room for them in the pair list with ONE atomicAdd on
+// a counter in this GPU's memory, and stores them through a small shared
+// staging buffer as coalesced 8-byte (index, value) pairs straight into the
+// receive slots of up to CX_MAX_PEERS targets (peer GPUs' memory mapped over
+// NVLink, or local slots).  No warp ever waits for another one, so the kernel
+// has no spin loop at all.
+//
+// Inside a sub-tile the pairs are in ascending index order like the
+// reference's wire format; sub-tiles land in the list in the order of their
+// reservations.  Next to the pairs every target receives one table entry per
+// sub-tile, {start, count}: receivers use it to find, without searching or
+// sorting, the pairs that fall into the part of the vector they own, and to
+// apply them in a fixed order.
 //
 // Survivors that do not fit into the slot (position >= cap) are not emitted
 // and stay in the residual, which error feedback makes safe; the count is
@@ -26,10 +33,14 @@
 
 namespace {
 
+#ifndef CX_COMPRESS_MIN_BLOCKS
+#define CX_COMPRESS_MIN_BLOCKS 2  // CTAs per SM the register budget is tuned for
+#endif
+
 constexpr int kThreads = 256;
-constexpr uint64_t kFlagAgg = 1ull << 32;
-constexpr uint64_t kFlagIncl = 2ull << 32;
-constexpr uint64_t kFlagMask = 3ull << 32;
+constexpr int kWarps = kThreads / 32;
+constexpr int kChunks = CX_SUBTILE / 128;  // 128 elements = 32 lanes x 4
+constexpr int kStage = 128;                // pairs staged per warp and pass
 
 struct CompressParams {
   const void* g;
@@ -37,169 +48,176 @@ struct CompressParams {
   int64_t n;
   const float* thr;
   uint32_t cap;
-  uint32_t ntiles;
   uint32_t nsub;
-  uint32_t epoch;
   uint64_t seq;
   CxWorkCounters* ctr;
-  uint64_t* tile_status;
   CxStats* stats;
   uint32_t src_rank;
-  uint32_t spin_limit;
   CxTargets tg;
 };
-
-__device__ __forceinline__ uint64_t shfl_up64(uint64_t v, int d) {
-  return __shfl_up_sync(0xffffffffu, (unsigned long long)v, d);
-}
 
 // T: element type of g.  HAS_G / HAS_R select compress_add_update (both),
 // compress_update (r only) and compress (g only).  VEC: 16-byte aligned views.
 template <typename T, bool HAS_G, bool HAS_R, bool VEC>
-__global__ void __launch_bounds__(kThreads, 4) compress_kernel(const CompressParams p) {
-  __shared__ CxPair s_pairs[CX_TILE];
-  __shared__ uint64_t s_wtot[kThreads / 32];
-  __shared__ uint32_t s_tile;
-  __shared__ uint32_t s_base;
+__global__ void __launch_bounds__(kThreads, CX_COMPRESS_MIN_BLOCKS) compress_kernel(const CompressParams p) {
+  __shared__ CxPair s_stage[kWarps][kStage];
   __shared__ uint32_t s_last;
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
+  const uint32_t lt = (1u << lane) - 1u;
   const float thr = *p.thr;
   const T* __restrict__ g = reinterpret_cast<const T*>(p.g);
   float* __restrict__ r = p.r;
-  const uint64_t ep_tag = (uint64_t)p.epoch << 34;
+  CxPair* stage = s_stage[warp];
+  const uint32_t nwarps = gridDim.x * kWarps;
 
-  for (;;) {
-    if (tid == 0) s_tile = atomicAdd(&p.ctr->next_tile, 1u);
-    __syncthreads();
-    const uint32_t tile = s_tile;
-    if (tile >= p.ntiles) break;
-    const int64_t tile_base = (int64_t)tile * CX_TILE;
+  for (uint32_t sub = blockIdx.x * kWarps + warp; sub < p.nsub; sub += nwarps) {
+    const int64_t sub_base = (int64_t)sub * CX_SUBTILE;
 
-    // ---- load, add, classify ------------------------------------------
-    float v[CX_SUBS_PER_TILE][4];
-    uint32_t mask = 0;  // bit c*4+e
-    uint64_t packed = 0;
+    // ---- load, add, classify ------------------------------------------------
+    // r first (all eight 16-byte loads in flight), then g folded in chunk by chunk:
+    // the values live in 32 registers per lane.
+    float v[kChunks][4];
 #pragma unroll
-    for (int c = 0; c < CX_SUBS_PER_TILE; ++c) {
-      const int64_t i0 = tile_base + c * CX_SUBTILE + tid * 4;
-      if (VEC && i0 + 3 < p.n) {
-        float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
-        if (HAS_R) cx::load4(r + i0, a);
-        if (HAS_G) cx::load4(g + i0, b);
+    for (int c = 0; c < kChunks; ++c) {
+      const int64_t i0 = sub_base + c * 128 + lane * 4;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) v[c][e] = a[e] + b[e];
-      } else {
+      for (int e = 0; e < 4; ++e) v[c][e] = 0.f;
+      if (HAS_R) {
+        if (VEC && i0 + 3 < p.n) {
+          cx::load4(r + i0, v[c]);
+        } else {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float a = 0.f, b = 0.f;
-          if (i0 + e < p.n) {
-            if (HAS_R) a = r[i0 + e];
-            if (HAS_G) b = cx::Elem<T>::to_f(g[i0 + e]);
-          }
-          v[c][e] = a + b;
+          for (int e = 0; e < 4; ++e)
+            if (i0 + e < p.n) v[c][e] = r[i0 + e];
         }
       }
-      uint32_t m = 0;
+    }
+    if (HAS_G) {
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
+        const int64_t i0 = sub_base + c * 128 + lane * 4;
+        float b[4] = {0.f, 0.f, 0.f, 0.f};
+        if (VEC && i0 + 3 < p.n) {
+          cx::load4(g + i0, b);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (i0 + e < p.n) b[e] = cx::Elem<T>::to_f(g[i0 + e]);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[c][e] = v[c][e] + b[e];
+      }
+    }
+    const int64_t left = p.n - sub_base;  // elements of this sub-tile that exist
+    uint32_t mask = 0;                    // bit c*4+e
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
 #pragma unroll
       for (int e = 0; e < 4; ++e)
-        if (fabsf(v[c][e]) > thr && i0 + e < p.n) m |= 1u << e;  // strict '>' like the reference
-      mask |= m << (4 * c);
-      packed |= (uint64_t)__popc(m) << (16 * c);
+        if (fabsf(v[c][e]) > thr && c * 128 + lane * 4 + e < left) mask |= 1u << (4 * c + e);  // strict '>'
     }
 
-    // ---- block exclusive scan of the four packed counters ---------------
-    uint64_t incl = packed;
+    // ---- rank the survivors: per 128-element chunk, lanes in index order -----
+    // ex: survivors of lower lanes in the same chunk, tot: survivors of the chunk,
+    // both packed 8 bits per chunk (at most 124 and 128).
+    uint32_t ex_lo = 0, ex_hi = 0, tot_lo = 0, tot_hi = 0, count = 0;
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const uint64_t t = shfl_up64(incl, d);
-      if (lane >= d) incl += t;
+    for (int c = 0; c < kChunks; ++c) {
+      const uint32_t cnt = __popc((mask >> (4 * c)) & 0xfu);
+      const uint32_t b0 = __ballot_sync(0xffffffffu, cnt & 1u);
+      const uint32_t b1 = __ballot_sync(0xffffffffu, cnt & 2u);
+      const uint32_t b2 = __ballot_sync(0xffffffffu, cnt & 4u);
+      const uint32_t ex = __popc(b0 & lt) + 2 * __popc(b1 & lt) + 4 * __popc(b2 & lt);
+      const uint32_t tot = __popc(b0) + 2 * __popc(b1) + 4 * __popc(b2);
+      if (c < 4) { ex_lo |= ex << (8 * c); tot_lo |= tot << (8 * c); }
+      else { ex_hi |= ex << (8 * (c - 4)); tot_hi |= tot << (8 * (c - 4)); }
+      count += tot;
     }
-    if (lane == 31) s_wtot[warp] = incl;
-    __syncthreads();
-    uint64_t woff = 0, total = 0;
-#pragma unroll
-    for (int w = 0; w < kThreads / 32; ++w) {
-      const uint64_t t = s_wtot[w];
-      if (w < warp) woff += t;
-      total += t;
-    }
-    const uint64_t excl = incl - packed + woff;
-    const uint32_t t0 = (uint32_t)(total & 0xffff), t1 = (uint32_t)((total >> 16) & 0xffff),
-                   t2 = (uint32_t)((total >> 32) & 0xffff), t3 = (uint32_t)((total >> 48) & 0xffff);
-    const uint32_t coff[CX_SUBS_PER_TILE] = {0u, t0, t0 + t1, t0 + t1 + t2};
-    const uint32_t tile_count = t0 + t1 + t2 + t3;
+#define CX_EX(c) ((((c) < 4 ? ex_lo : ex_hi) >> (8 * ((c)&3))) & 0xffu)
+#define CX_TOT(c) ((((c) < 4 ? tot_lo : tot_hi) >> (8 * ((c)&3))) & 0xffu)
 
-    // ---- decoupled look-back: exclusive prefix over earlier tiles -------
-    if (warp == 0) {
-      if (lane == 0)
-        cx::st_relaxed_gpu(&p.tile_status[tile],
-                           ep_tag | (tile == 0 ? kFlagIncl : kFlagAgg) | tile_count);
-      uint32_t exclusive = 0;
-      bool failed = false;
-      int64_t look = (int64_t)tile - 1;
-      while (look >= 0) {
-        const int64_t idx = look - lane;
-        uint64_t st = kFlagIncl;  // virtual predecessor before tile 0: inclusive, value 0
-        if (idx >= 0) {
-          uint32_t spins = 0;
-          for (;;) {
-            st = cx::ld_relaxed_gpu(&p.tile_status[idx]);
-            if ((st >> 34) == p.epoch && (st & kFlagMask)) break;
-            if (++spins > p.spin_limit) { failed = true; st = kFlagIncl; break; }
-            __nanosleep(20);
+    // ---- reserve room in the pair list -----------------------------------------
+    uint32_t base = 0;
+    if (count) {
+      if (lane == 0) base = atomicAdd(&p.ctr->nnz_found, count);
+      base = __shfl_sync(0xffffffffu, base, 0);
+    }
+    const uint32_t emit = base >= p.cap ? 0u : min(count, p.cap - base);  // pairs that fit
+    if (lane < p.tg.count) {
+      uint2 entry;
+      entry.x = emit ? base : 0u;
+      entry.y = emit;
+      reinterpret_cast<uint2*>(p.tg.ep[lane].table)[sub] = entry;
+    }
+
+    // ---- stage in shared memory, store coalesced to every target -----------------
+    const int32_t lane_idx0 = (int32_t)sub_base + lane * 4;
+    if (count <= kStage) {
+      uint32_t off = 0;
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
+        uint32_t pos = off + CX_EX(c);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (mask & (1u << (4 * c + e))) {
+            CxPair pr;
+            pr.idx = lane_idx0 + c * 128 + e;
+            pr.val = __float_as_uint(v[c][e]);
+            stage[pos++] = pr;
           }
         }
-        const uint32_t incl_lanes = __ballot_sync(0xffffffffu, (st & kFlagMask) == kFlagIncl);
-        const int first = __ffs(incl_lanes) - 1;  // nearest predecessor with an inclusive prefix
-        uint32_t val = (first < 0 || lane <= first) ? (uint32_t)(st & 0xffffffffu) : 0u;
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) val += __shfl_xor_sync(0xffffffffu, val, d);
-        exclusive += val;
-        if (first >= 0) break;
-        look -= 32;
+        off += CX_TOT(c);
       }
-      failed = __any_sync(0xffffffffu, failed);
-      if (lane == 0) {
-        if (failed) atomicOr(&p.ctr->error, CX_ST_LOOKBACK);
-        cx::st_relaxed_gpu(&p.tile_status[tile], ep_tag | kFlagIncl | (exclusive + tile_count));
-        s_base = exclusive;
+      __syncwarp();
+      for (uint32_t i = lane; i < emit; i += 32) {
+        const CxPair pr = stage[i];
+        for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].pairs[base + i] = pr;
       }
-    }
-
-    // ---- stage survivors in shared memory, in index order ---------------
+      __syncwarp();
+    } else {
+      uint32_t off = 0;
 #pragma unroll
-    for (int c = 0; c < CX_SUBS_PER_TILE; ++c) {
-      uint32_t pos = coff[c] + (uint32_t)((excl >> (16 * c)) & 0xffff);
-      const int32_t i0 = (int32_t)(tile_base + c * CX_SUBTILE + tid * 4);
+      for (int c = 0; c < kChunks; ++c) {
+        uint32_t pos = CX_EX(c);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        if (mask & (1u << (4 * c + e))) {
-          CxPair pr;
-          pr.idx = i0 + e;
-          pr.val = __float_as_uint(v[c][e]);
-          s_pairs[pos++] = pr;
+        for (int e = 0; e < 4; ++e) {
+          if (mask & (1u << (4 * c + e))) {
+            CxPair pr;
+            pr.idx = lane_idx0 + c * 128 + e;
+            pr.val = __float_as_uint(v[c][e]);
+            stage[pos++] = pr;
+          }
         }
+        __syncwarp();
+        const uint32_t tot = CX_TOT(c);
+        const uint32_t lim = emit > off ? min(emit - off, tot) : 0u;
+        for (uint32_t i = lane; i < lim; i += 32) {
+          const CxPair pr = stage[i];
+          for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].pairs[base + off + i] = pr;
+        }
+        __syncwarp();
+        off += tot;
       }
     }
-    __syncthreads();
-    const uint32_t base = s_base;
 
-    // ---- residual: zero what was emitted, keep the rest ------------------
+    // ---- residual: zero what was emitted, keep the rest ------------------------------
     if (HAS_R) {
+      uint32_t off = 0;
 #pragma unroll
-      for (int c = 0; c < CX_SUBS_PER_TILE; ++c) {
+      for (int c = 0; c < kChunks; ++c) {
         const uint32_t m = (mask >> (4 * c)) & 0xfu;
+        uint32_t pos = off + CX_EX(c);
+        off += CX_TOT(c);
         if (!HAS_G && m == 0) continue;  // nothing changed in this vector
-        uint32_t pos = base + coff[c] + (uint32_t)((excl >> (16 * c)) & 0xffff);
-        const int64_t i0 = tile_base + c * CX_SUBTILE + tid * 4;
+        const int64_t i0 = sub_base + c * 128 + lane * 4;
         float out[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const bool sel = m & (1u << e);
-          out[e] = (sel && pos < p.cap) ? 0.f : v[c][e];
+          out[e] = (sel && pos < emit) ? 0.f : v[c][e];
           pos += sel ? 1u : 0u;
         }
         if (VEC && i0 + 3 < p.n) {
@@ -211,32 +229,11 @@ __global__ void __launch_bounds__(kThreads, 4) compress_kernel(const CompressPar
         }
       }
     }
-
-    // ---- sub-tile offsets and the pairs themselves, to every target ------
-    if (tid < CX_SUBS_PER_TILE) {
-      const uint32_t sub = tile * CX_SUBS_PER_TILE + tid;
-      if (sub < p.nsub) {
-        const uint32_t before = tid == 0 ? 0u : tid == 1 ? t0 : tid == 2 ? t0 + t1 : t0 + t1 + t2;
-        const uint32_t off = min(base + before, p.cap);
-        for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].prefix[sub] = off;
-      }
-    }
-    if (tile == p.ntiles - 1 && tid == 0) {
-      const uint32_t found = base + tile_count;
-      for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].prefix[p.nsub] = min(found, p.cap);
-      p.ctr->nnz_found = found;
-    }
-    for (uint32_t i = tid; i < tile_count; i += kThreads) {
-      const uint32_t gpos = base + i;
-      if (gpos < p.cap) {
-        const CxPair pr = s_pairs[i];
-        for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].pairs[gpos] = pr;
-      }
-    }
-    __syncthreads();  // s_pairs, s_tile, s_base are reused by the next tile
+#undef CX_EX
+#undef CX_TOT
   }
 
-  // ---- completion: the CTA that arrives last publishes ---------------------
+  // ---- completion: the CTA that arrives last publishes -------------------------------
   __threadfence_system();
   __syncthreads();
   if (tid == 0) {
@@ -247,15 +244,14 @@ __global__ void __launch_bounds__(kThreads, 4) compress_kernel(const CompressPar
   if (!s_last) return;
   __threadfence();
   const uint32_t found = *reinterpret_cast<volatile uint32_t*>(&p.ctr->nnz_found);
-  const uint32_t err = *reinterpret_cast<volatile uint32_t*>(&p.ctr->error);
-  const uint32_t nnz = err ? 0u : min(found, p.cap);
+  const uint32_t nnz = min(found, p.cap);
   if (tid < p.tg.count) {
     CxHeader* h = p.tg.ep[tid].hdr;
     h->bytes = 8ull + 8ull * nnz;
     h->n = (uint32_t)p.n;
     h->nnz = nnz;
     h->nnz_found = found;
-    h->kind = err ? CX_KIND_ERROR : CX_KIND_PAIRS;
+    h->kind = CX_KIND_PAIRS;
     h->threshold = thr;
     h->nsub = p.nsub;
     h->src_rank = p.src_rank;
@@ -268,13 +264,11 @@ __global__ void __launch_bounds__(kThreads, 4) compress_kernel(const CompressPar
       p.stats->n = (uint32_t)p.n;
       p.stats->nnz = nnz;
       p.stats->nnz_found = found;
-      p.stats->status = err | (found > p.cap ? CX_ST_OVERFLOW : 0u);
+      p.stats->status = found > p.cap ? CX_ST_OVERFLOW : 0u;
       p.stats->threshold = thr;
     }
-    p.ctr->next_tile = 0;
     p.ctr->done = 0;
     p.ctr->nnz_found = 0;
-    p.ctr->error = 0;
   }
 }
 
@@ -283,7 +277,6 @@ __global__ void compress_empty_kernel(const CompressParams p) {
   const int tid = threadIdx.x;
   if (tid < p.tg.count) {
     CxHeader* h = p.tg.ep[tid].hdr;
-    p.tg.ep[tid].prefix[0] = 0;
     h->bytes = 8; h->n = 0; h->nnz = 0; h->nnz_found = 0; h->kind = CX_KIND_PAIRS;
     h->threshold = *p.thr; h->nsub = 0; h->src_rank = p.src_rank; h->dtype = CX_F32;
     __threadfence_system();
@@ -296,33 +289,26 @@ __global__ void compress_empty_kernel(const CompressParams p) {
 }
 
 template <typename T, bool HAS_G, bool HAS_R>
-int launch_typed(const CompressParams& p, bool vec, int grid, cudaStream_t s) {
+void launch_typed(const CompressParams& p, bool vec, int grid, cudaStream_t s) {
   if (vec)
     compress_kernel<T, HAS_G, HAS_R, true><<<grid, kThreads, 0, s>>>(p);
   else
     compress_kernel<T, HAS_G, HAS_R, false><<<grid, kThreads, 0, s>>>(p);
-  return 0;
 }
 
 template <typename T>
-int launch_mode(const CompressParams& p, bool vec, int grid, cudaStream_t s) {
-  if (p.g && p.r) return launch_typed<T, true, true>(p, vec, grid, s);
-  if (p.r) return launch_typed<T, false, true>(p, vec, grid, s);
-  return launch_typed<T, true, false>(p, vec, grid, s);
-}
-
-uint32_t next_epoch() {
-  static uint32_t e = 0;
-  e = (e + 1) & 0x3fffffffu;
-  if (e == 0) e = 1;
-  return e;
+void launch_mode(const CompressParams& p, bool vec, int grid, cudaStream_t s) {
+  if (p.g && p.r) launch_typed<T, true, true>(p, vec, grid, s);
+  else if (p.r) launch_typed<T, false, true>(p, vec, grid, s);
+  else launch_typed<T, true, false>(p, vec, grid, s);
 }
 
 }  // namespace
 
+// The only scratch a compressor needs: one zero-initialised CxWorkCounters block.
 extern "C" int64_t cx_workspace_bytes(int64_t n) {
-  const int64_t ntiles = (n + CX_TILE - 1) / CX_TILE;
-  return (int64_t)sizeof(CxWorkCounters) + 8 * (ntiles > 0 ? ntiles : 1);
+  (void)n;
+  return (int64_t)sizeof(CxWorkCounters);
 }
 
 int cx_compress_cuda(int gdtype, const void* g, float* r, int64_t n, const float* thr,
@@ -334,14 +320,10 @@ int cx_compress_cuda(int gdtype, const void* g, float* r, int64_t n, const float
   if (ws_bytes < cx_workspace_bytes(n)) return cx_set_error("cx_compress: workspace too small", 0);
   CompressParams p;
   p.g = g; p.r = r; p.n = n; p.thr = thr; p.cap = cap;
-  p.ntiles = (uint32_t)((n + CX_TILE - 1) / CX_TILE);
   p.nsub = (uint32_t)((n + CX_SUBTILE - 1) / CX_SUBTILE);
-  p.epoch = next_epoch();
   p.seq = seq;
   p.ctr = reinterpret_cast<CxWorkCounters*>(workspace);
-  p.tile_status = reinterpret_cast<uint64_t*>(reinterpret_cast<char*>(workspace) + sizeof(CxWorkCounters));
   p.stats = stats; p.src_rank = src_rank;
-  p.spin_limit = 1u << 22;
   p.tg = *tg;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (n == 0) {
@@ -352,8 +334,9 @@ int cx_compress_cuda(int gdtype, const void* g, float* r, int64_t n, const float
   const size_t esz = gdtype == CX_F32 ? 4 : 2;
   const bool vec = (!r || (reinterpret_cast<uintptr_t>(r) & 15) == 0) &&
                    (!g || (reinterpret_cast<uintptr_t>(g) & (4 * esz - 1)) == 0);
-  int grid = cx_sm_count() * 4;
-  if ((uint32_t)grid > p.ntiles) grid = (int)p.ntiles;
+  int grid = cx_sm_count() * CX_COMPRESS_MIN_BLOCKS;
+  const int need = (int)((p.nsub + kWarps - 1) / kWarps);
+  if (grid > need) grid = need;
   switch (gdtype) {
     case CX_F32: launch_mode<float>(p, vec, grid, s); break;
     case CX_BF16: launch_mode<__nv_bfloat16>(p, vec, grid, s); break;

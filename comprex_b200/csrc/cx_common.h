@@ -3,11 +3,11 @@
 // Everything that crosses the C ABI (ctypes on the Python side) is a plain C
 // struct declared here.  The wire layout of a receive slot is
 //
-//   [CxHeader 64 B][prefix: (nsub_max+1) x u32, padded to 16 B][pairs: cap x {i32 idx, f32 val}]
+//   [CxHeader 64 B][table: nsub_max x {u32 start, u32 count}, padded to 16 B][pairs: cap x {i32 idx, f32 val}]
 //
 // for sparse payloads (the IndexPairs codec of the reference,
-// src/compressor.hxx:539-661, plus a per-1024-element offset table that the
-// single-pass ordered compaction produces for free), and
+// src/compressor.hxx:539-661, plus one table entry per 1024-element sub-tile
+// that says where the sub-tile's pairs sit in the pair list), and
 //
 //   [CxHeader 64 B][n x T]
 //
@@ -22,9 +22,7 @@ extern "C" {
 #endif
 
 #define CX_MAX_PEERS 16
-#define CX_TILE 4096      /* elements one CTA compacts per look-back step */
-#define CX_SUBTILE 1024   /* granularity of the prefix table on the wire   */
-#define CX_SUBS_PER_TILE (CX_TILE / CX_SUBTILE)
+#define CX_SUBTILE 1024   /* elements per table entry on the wire; one warp's unit of work */
 
 /* device kinds */
 #define CX_DEV_HOST 0
@@ -48,7 +46,6 @@ extern "C" {
 #define CX_ST_BAD_HEADER 2u
 #define CX_ST_OVERFLOW 4u   /* soft: survivors beyond capacity stayed in the residual */
 #define CX_ST_BAD_INDEX 8u
-#define CX_ST_LOOKBACK 16u  /* intra-kernel look-back wait ran out */
 
 /* apply ops */
 #define CX_OP_ADD 0       /* out += scale * sum(payloads)                         */
@@ -78,7 +75,7 @@ typedef struct CxPair {
 
 typedef struct CxEndpoint {
   CxHeader* hdr;
-  uint32_t* prefix;
+  uint32_t* table;  /* 2 words per sub-tile: start, count */
   CxPair* pairs;  /* for dense slots: start of the n x T data region */
 } CxEndpoint;
 
@@ -95,7 +92,7 @@ typedef struct CxSources {
   uint64_t seq[CX_MAX_PEERS];  /* wait until hdr->seq >= seq[j] */
 } CxSources;
 
-/* scratch of one compressor: counters first, then one status word per tile */
+/* scratch of one sender: zero-initialised, reset by the kernel that used it */
 typedef struct CxWorkCounters {
   uint32_t next_tile;
   uint32_t done;

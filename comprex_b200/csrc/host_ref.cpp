@@ -168,31 +168,36 @@ int cx_compress_host(int gdtype, const void* g, float* r, int64_t n, const float
   const float thr = *thr_p;
   const uint32_t nsub = (uint32_t)((n + CX_SUBTILE - 1) / CX_SUBTILE);
   uint32_t found = 0;
-  for (int64_t i = 0; i < n; ++i) {
-    if ((i % CX_SUBTILE) == 0) {
-      const uint32_t off = std::min(found, cap);
-      for (int k = 0; k < tg->count; ++k) tg->ep[k].prefix[i / CX_SUBTILE] = off;
-    }
-    float a = 0.f, b = 0.f;
-    if (r) a = r[i];
-    if (g) b = load_elem(gdtype, g, i);
-    const float v = a + b;
-    bool emitted = false;
-    if (fabsf(v) > thr) {
-      if (found < cap) {
-        CxPair pr;
-        pr.idx = (int32_t)i;
-        memcpy(&pr.val, &v, 4);
-        for (int k = 0; k < tg->count; ++k) tg->ep[k].pairs[found] = pr;
-        emitted = true;
+  for (uint32_t sub = 0; sub < nsub; ++sub) {
+    const int64_t lo = (int64_t)sub * CX_SUBTILE, hi = std::min<int64_t>(lo + CX_SUBTILE, n);
+    const uint32_t start = found;
+    uint32_t emitted_here = 0;
+    for (int64_t i = lo; i < hi; ++i) {
+      float a = 0.f, b = 0.f;
+      if (r) a = r[i];
+      if (g) b = load_elem(gdtype, g, i);
+      const float v = a + b;
+      bool emitted = false;
+      if (fabsf(v) > thr) {
+        if (found < cap) {
+          CxPair pr;
+          pr.idx = (int32_t)i;
+          memcpy(&pr.val, &v, 4);
+          for (int k = 0; k < tg->count; ++k) tg->ep[k].pairs[found] = pr;
+          emitted = true;
+          ++emitted_here;
+        }
+        ++found;
       }
-      ++found;
+      if (r && (g || emitted)) r[i] = emitted ? 0.f : v;
     }
-    if (r && (g || emitted)) r[i] = emitted ? 0.f : v;
+    for (int k = 0; k < tg->count; ++k) {
+      tg->ep[k].table[2 * sub] = emitted_here ? start : 0u;
+      tg->ep[k].table[2 * sub + 1] = emitted_here;
+    }
   }
   const uint32_t nnz = std::min(found, cap);
   for (int k = 0; k < tg->count; ++k) {
-    tg->ep[k].prefix[nsub] = nnz;
     CxHeader* h = tg->ep[k].hdr;
     h->bytes = 8ull + 8ull * nnz; h->n = (uint32_t)n; h->nnz = nnz; h->nnz_found = found;
     h->kind = CX_KIND_PAIRS; h->threshold = thr; h->nsub = nsub; h->src_rank = src_rank;
@@ -233,8 +238,10 @@ int cx_apply_host(const CxSources* src, int64_t n, const CxApplyArgs* a, uint32_
     const int64_t hi = std::min<int64_t>(lo + CX_SUBTILE, n);
     if (!sparse) memset(acc, 0, sizeof(acc));
     for (int j = 0; j < src->count; ++j) {
-      uint32_t b = std::min(src->ep[j].prefix[sub + 1], nnz[j]);
-      uint32_t s = std::min(src->ep[j].prefix[sub], b);
+      const uint32_t e_start = src->ep[j].table[2 * sub];
+      const uint32_t e_count = std::min<uint32_t>(src->ep[j].table[2 * sub + 1], CX_SUBTILE);
+      uint32_t b = std::min(e_start + e_count, nnz[j]);
+      uint32_t s = std::min(e_start, b);
       for (uint32_t i = s; i < b; ++i) {
         const CxPair pr = src->ep[j].pairs[i];
         float val;
@@ -282,7 +289,13 @@ int cx_forward_host(const CxEndpoint* from, uint64_t expect_seq, const CxTargets
   const CxHeader h = *from->hdr;
   const uint32_t nnz = std::min(h.nnz, cap);
   for (int k = 0; k < tg->count; ++k) {
-    for (uint32_t i = 0; i <= h.nsub; ++i) tg->ep[k].prefix[i] = std::min(from->prefix[i], cap);
+    for (uint32_t i = 0; i < h.nsub; ++i) {
+      uint32_t st = from->table[2 * i], ct = from->table[2 * i + 1];
+      if (st >= nnz) st = ct = 0;
+      else ct = std::min(ct, nnz - st);
+      tg->ep[k].table[2 * i] = st;
+      tg->ep[k].table[2 * i + 1] = ct;
+    }
     memcpy(tg->ep[k].pairs, from->pairs, (size_t)nnz * sizeof(CxPair));
     CxHeader* o = tg->ep[k].hdr;
     o->bytes = 8ull + 8ull * nnz; o->n = h.n; o->nnz = nnz; o->nnz_found = h.nnz_found;

@@ -34,7 +34,7 @@ class SparseSlot:
     @staticmethod
     def nbytes(n: int, cap: int) -> int:
         nsub = (n + _lib.SUBTILE - 1) // _lib.SUBTILE
-        return HEADER_BYTES + _round_up(4 * (nsub + 1), 16) + 8 * max(cap, 1)
+        return HEADER_BYTES + _round_up(8 * max(nsub, 1), 16) + 8 * max(cap, 1)
 
     @staticmethod
     def create(env: GaspiEnvironment, n: int, cap: int) -> "SparseSlot":
@@ -43,7 +43,7 @@ class SparseSlot:
     def endpoint(self, env: GaspiEnvironment, rank: int | None = None) -> Endpoint:
         base = env.ptr(self.alloc, rank)
         nsub = (self.n + _lib.SUBTILE - 1) // _lib.SUBTILE
-        return Endpoint(base, base + HEADER_BYTES, base + HEADER_BYTES + _round_up(4 * (nsub + 1), 16))
+        return Endpoint(base, base + HEADER_BYTES, base + HEADER_BYTES + _round_up(8 * max(nsub, 1), 16))
 
 
 @dataclass(frozen=True)
@@ -97,7 +97,7 @@ def _flat(t: torch.Tensor, what: str) -> torch.Tensor:
 class Compressor:
     """Scratch, threshold cell and statistics of one sparse sender.
 
-    The scratch (tile counters and one look-back word per 4096-element tile)
+    The scratch (a 64-byte block of counters that the kernel resets itself)
     is rank-local device memory; the threshold lives in a one-element device
     tensor that the threshold kernel writes and the compress kernel reads.
     """

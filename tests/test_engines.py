@@ -126,7 +126,7 @@ def test_comprex_topk_fraction_and_threshold_readback(world):
     cm[0].writeRemote(v)
     out = cm[1].readRemote()
     frac = float((out != 0).float().mean())
-    assert 0.005 <= frac <= 0.015                        # the estimate lets about top-k pass
+    assert 0.002 <= frac <= 0.03   # the estimate uses the 10th largest of 1000 samples: about top-k
     t = cm[0].threshold.getThreshold()
     assert torch.equal(out, torch.where(v.abs() > t, v, torch.zeros_like(v)))
     assert cm[0].getSize() == n
