@@ -41,18 +41,23 @@ def peak_gbs():
         return 6650.0, "fallback"
 
 
-def timed(fn, iters, flush):
+def timed(fn, iters, flush, reps=1):
+    """Median / best device time of one launch in microseconds.
+
+    ``reps`` > 1 queues that many launches behind a long-running filler kernel, so the
+    events bracket back-to-back kernels and not the host's launch latency (used for
+    vectors that fit in L2 anyway, where a flush between launches would not be the
+    situation a training step sees)."""
     times = []
     for _ in range(iters):
-        if flush is not None:
-            flush.add_(1)
+        flush.add_(1)          # flushes L2 and keeps the GPU busy while the launches queue up
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
         a.record()
-        fn()
+        for _ in range(reps):
+            fn()
         b.record()
         torch.cuda.synchronize()
-        times.append(a.elapsed_time(b) * 1e3)
+        times.append(a.elapsed_time(b) * 1e3 / reps)
     return statistics.median(times), min(times)
 
 
@@ -126,8 +131,9 @@ def main():
                         continue   # only the compress kernel reads the gradient dtype
                     for _ in range(args.warmup):
                         fn()
-                    med, best = timed(fn, args.iters, flush)
-                    row = {"kernel": name, "n": n, "ratio": ratio, "dtype": dname, "nnz": nnz,
+                    reps = 10 if n * 12 < (100 << 20) else 1
+                    med, best = timed(fn, args.iters, flush, reps)
+                    row = {"kernel": name, "n": n, "ratio": ratio, "dtype": dname, "nnz": nnz, "reps": reps,
                            "targets": args.targets, "sources": args.sources, "us_median": round(med, 2),
                            "us_min": round(best, 2), "algo_bytes": nbytes,
                            "gbs": round(nbytes / med / 1e3, 1) if nbytes else None,

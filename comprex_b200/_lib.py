@@ -45,7 +45,7 @@ class Targets(C.Structure):
 
 class Sources(C.Structure):
     _fields_ = [("count", C.c_int32), ("pad", C.c_int32), ("ep", Endpoint * MAX_PEERS),
-                ("seq", C.c_uint64 * MAX_PEERS)]
+                ("seq", C.c_uint64 * MAX_PEERS), ("cap", C.c_uint32 * MAX_PEERS)]
 
 
 class Stats(C.Structure):

@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(kThreads) apply_sparse_kernel(const ApplyParam
     if (lane < p.src.count) {
       const uint2 entry = __ldcg(reinterpret_cast<const uint2*>(p.src.ep[lane].table) + sub);
       a = entry.x;
-      b = min(entry.x + min(entry.y, (uint32_t)CX_SUBTILE), s_nnz[lane]);
+      b = min(entry.x + min(entry.y, (uint32_t)CX_SUBTILE), p.src.cap[lane]);  // never beyond the slot
       a = min(a, b);
     }
     for (int j = 0; j < p.src.count; ++j) {
@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(kThreads) apply_dense_kernel(const ApplyParams
     if (lane < p.src.count) {
       const uint2 entry = __ldcg(reinterpret_cast<const uint2*>(p.src.ep[lane].table) + sub);
       a = entry.x;
-      b = min(entry.x + min(entry.y, (uint32_t)CX_SUBTILE), s_nnz[lane]);
+      b = min(entry.x + min(entry.y, (uint32_t)CX_SUBTILE), p.src.cap[lane]);  // never beyond the slot
       a = min(a, b);
     }
 #pragma unroll
@@ -258,17 +258,19 @@ __global__ void __launch_bounds__(kThreads) forward_kernel(const ForwardParams p
   const CxHeader* h = &hv;
   const uint32_t nnz = min(h->nnz, p.cap);
   const uint32_t nsub = h->nsub;
-  const uint64_t gtid = (uint64_t)blockIdx.x * kThreads + threadIdx.x;
-  const uint64_t gsz = (uint64_t)gridDim.x * kThreads;
-  for (uint64_t i = gtid; i < nsub; i += gsz) {
-    uint2 v = __ldcg(reinterpret_cast<const uint2*>(p.from.table) + i);
-    if (v.x >= nnz) v.x = v.y = 0;
-    else v.y = min(v.y, nnz - v.x);
-    for (int k = 0; k < p.tg.count; ++k) reinterpret_cast<uint2*>(p.tg.ep[k].table)[i] = v;
-  }
-  for (uint64_t i = gtid; i < nnz; i += gsz) {
-    const uint2 v = __ldcg(reinterpret_cast<const uint2*>(p.from.pairs + i));
-    for (int k = 0; k < p.tg.count; ++k) *reinterpret_cast<uint2*>(p.tg.ep[k].pairs + i) = v;
+  // a warp per sub-tile: its table entry and its pairs keep their positions
+  const int lane = threadIdx.x & 31;
+  const uint32_t nwarps = gridDim.x * kWarps;
+  for (uint32_t sub = blockIdx.x * kWarps + (threadIdx.x >> 5); sub < nsub; sub += nwarps) {
+    uint2 v = __ldcg(reinterpret_cast<const uint2*>(p.from.table) + sub);
+    v.y = min(v.y, (uint32_t)CX_SUBTILE);
+    if (v.x >= p.cap) v.x = v.y = 0;
+    else v.y = min(v.y, p.cap - v.x);
+    if (lane < p.tg.count) reinterpret_cast<uint2*>(p.tg.ep[lane].table)[sub] = v;
+    for (uint32_t i = lane; i < v.y; i += 32) {
+      const uint2 pr = __ldcg(reinterpret_cast<const uint2*>(p.from.pairs + v.x + i));
+      for (int k = 0; k < p.tg.count; ++k) *reinterpret_cast<uint2*>(p.tg.ep[k].pairs + v.x + i) = pr;
+    }
   }
   __threadfence_system();
   __syncthreads();

@@ -49,6 +49,8 @@ struct CompressParams {
   const float* thr;
   uint32_t cap;
   uint32_t nsub;
+  uint32_t nregions;     // power of two; sub-tile s reserves in region s % nregions
+  uint32_t region_size;  // cap / nregions pairs each
   uint64_t seq;
   CxWorkCounters* ctr;
   CxStats* stats;
@@ -140,12 +142,17 @@ __global__ void __launch_bounds__(kThreads, CX_COMPRESS_MIN_BLOCKS) compress_ker
 #define CX_TOT(c) ((((c) < 4 ? tot_lo : tot_hi) >> (8 * ((c)&3))) & 0xffu)
 
     // ---- reserve room in the pair list -----------------------------------------
+    // The pair list is cut into nregions equal regions with one counter each, and
+    // neighbouring sub-tiles use different regions: atomics on one address are
+    // serialised by the L2, a single counter would cap the kernel's throughput.
+    const uint32_t region = sub & (p.nregions - 1);
     uint32_t base = 0;
     if (count) {
-      if (lane == 0) base = atomicAdd(&p.ctr->nnz_found, count);
+      if (lane == 0) base = atomicAdd(&p.ctr->region[region][0], count);
       base = __shfl_sync(0xffffffffu, base, 0);
     }
-    const uint32_t emit = base >= p.cap ? 0u : min(count, p.cap - base);  // pairs that fit
+    const uint32_t emit = base >= p.region_size ? 0u : min(count, p.region_size - base);  // pairs that fit
+    base += region * p.region_size;
     if (lane < p.tg.count) {
       uint2 entry;
       entry.x = emit ? base : 0u;
@@ -243,8 +250,18 @@ __global__ void __launch_bounds__(kThreads, CX_COMPRESS_MIN_BLOCKS) compress_ker
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  const uint32_t found = *reinterpret_cast<volatile uint32_t*>(&p.ctr->nnz_found);
-  const uint32_t nnz = min(found, p.cap);
+  __shared__ uint32_t s_found, s_nnz;
+  if (tid == 0) { s_found = 0; s_nnz = 0; }
+  __syncthreads();
+  if ((uint32_t)tid < p.nregions) {
+    const uint32_t f = *reinterpret_cast<volatile uint32_t*>(&p.ctr->region[tid][0]);
+    atomicAdd(&s_found, f);
+    atomicAdd(&s_nnz, min(f, p.region_size));
+    p.ctr->region[tid][0] = 0;
+  }
+  __syncthreads();
+  const uint32_t found = s_found;  // survivors
+  const uint32_t nnz = s_nnz;      // pairs stored
   if (tid < p.tg.count) {
     CxHeader* h = p.tg.ep[tid].hdr;
     h->bytes = 8ull + 8ull * nnz;
@@ -264,11 +281,10 @@ __global__ void __launch_bounds__(kThreads, CX_COMPRESS_MIN_BLOCKS) compress_ker
       p.stats->n = (uint32_t)p.n;
       p.stats->nnz = nnz;
       p.stats->nnz_found = found;
-      p.stats->status = found > p.cap ? CX_ST_OVERFLOW : 0u;
+      p.stats->status = found > nnz ? CX_ST_OVERFLOW : 0u;
       p.stats->threshold = thr;
     }
     p.ctr->done = 0;
-    p.ctr->nnz_found = 0;
   }
 }
 
@@ -321,6 +337,11 @@ int cx_compress_cuda(int gdtype, const void* g, float* r, int64_t n, const float
   CompressParams p;
   p.g = g; p.r = r; p.n = n; p.thr = thr; p.cap = cap;
   p.nsub = (uint32_t)((n + CX_SUBTILE - 1) / CX_SUBTILE);
+  // at least 8 sub-tiles and 256 pairs per region, so that regions fill evenly
+  p.nregions = 1;
+  while (p.nregions < CX_MAX_REGIONS && p.nsub / (2 * p.nregions) >= 8 && cap / (2 * p.nregions) >= 256)
+    p.nregions *= 2;
+  p.region_size = cap / p.nregions;
   p.seq = seq;
   p.ctr = reinterpret_cast<CxWorkCounters*>(workspace);
   p.stats = stats; p.src_rank = src_rank;

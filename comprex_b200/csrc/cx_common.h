@@ -90,15 +90,15 @@ typedef struct CxSources {
   int32_t pad;
   CxEndpoint ep[CX_MAX_PEERS];
   uint64_t seq[CX_MAX_PEERS];  /* wait until hdr->seq >= seq[j] */
+  uint32_t cap[CX_MAX_PEERS];  /* pair capacity of slot j: no table entry may point beyond it */
 } CxSources;
 
 /* scratch of one sender: zero-initialised, reset by the kernel that used it */
+#define CX_MAX_REGIONS 32
 typedef struct CxWorkCounters {
-  uint32_t next_tile;
-  uint32_t done;
-  uint32_t nnz_found;
-  uint32_t error;
-  uint32_t pad[12];
+  uint32_t done;                        /* CTAs that finished                          */
+  uint32_t pad[31];
+  uint32_t region[CX_MAX_REGIONS][32];  /* pairs reserved per region, one 128-byte line each */
 } CxWorkCounters;
 
 /* per-call statistics a kernel leaves behind (device or pinned memory) */

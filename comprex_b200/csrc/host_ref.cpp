@@ -217,12 +217,10 @@ int cx_apply_host(const CxSources* src, int64_t n, const CxApplyArgs* a, uint32_
   if (!a->out) return cx_set_error("cx_apply: out is NULL", 0);
   if (n == 0) return 0;
   uint32_t bad = wait_all(src, timeout_ns);
-  uint32_t nnz[CX_MAX_PEERS];
   if (!bad)
     for (int j = 0; j < src->count; ++j) {
       const CxHeader* h = src->ep[j].hdr;
       if (h->kind != CX_KIND_PAIRS || h->n != (uint32_t)n) bad |= CX_ST_BAD_HEADER;
-      nnz[j] = h->nnz;
     }
   if (bad) { if (status) *status |= bad; return 0; }
   const bool update = a->op != CX_OP_ADD && a->op != CX_OP_SET;
@@ -240,7 +238,7 @@ int cx_apply_host(const CxSources* src, int64_t n, const CxApplyArgs* a, uint32_
     for (int j = 0; j < src->count; ++j) {
       const uint32_t e_start = src->ep[j].table[2 * sub];
       const uint32_t e_count = std::min<uint32_t>(src->ep[j].table[2 * sub + 1], CX_SUBTILE);
-      uint32_t b = std::min(e_start + e_count, nnz[j]);
+      uint32_t b = std::min(e_start + e_count, src->cap[j]);  // never beyond the slot
       uint32_t s = std::min(e_start, b);
       for (uint32_t i = s; i < b; ++i) {
         const CxPair pr = src->ep[j].pairs[i];
@@ -289,14 +287,14 @@ int cx_forward_host(const CxEndpoint* from, uint64_t expect_seq, const CxTargets
   const CxHeader h = *from->hdr;
   const uint32_t nnz = std::min(h.nnz, cap);
   for (int k = 0; k < tg->count; ++k) {
-    for (uint32_t i = 0; i < h.nsub; ++i) {
-      uint32_t st = from->table[2 * i], ct = from->table[2 * i + 1];
-      if (st >= nnz) st = ct = 0;
-      else ct = std::min(ct, nnz - st);
+    for (uint32_t i = 0; i < h.nsub; ++i) {   // entries and pairs keep their positions
+      uint32_t st = from->table[2 * i], ct = std::min<uint32_t>(from->table[2 * i + 1], CX_SUBTILE);
+      if (st >= cap) st = ct = 0;
+      else ct = std::min(ct, cap - st);
       tg->ep[k].table[2 * i] = st;
       tg->ep[k].table[2 * i + 1] = ct;
+      memcpy(tg->ep[k].pairs + st, from->pairs + st, (size_t)ct * sizeof(CxPair));
     }
-    memcpy(tg->ep[k].pairs, from->pairs, (size_t)nnz * sizeof(CxPair));
     CxHeader* o = tg->ep[k].hdr;
     o->bytes = 8ull + 8ull * nnz; o->n = h.n; o->nnz = nnz; o->nnz_found = h.nnz_found;
     o->kind = h.kind; o->threshold = h.threshold; o->nsub = h.nsub; o->src_rank = h.src_rank;

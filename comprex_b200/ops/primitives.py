@@ -43,7 +43,9 @@ class SparseSlot:
     def endpoint(self, env: GaspiEnvironment, rank: int | None = None) -> Endpoint:
         base = env.ptr(self.alloc, rank)
         nsub = (self.n + _lib.SUBTILE - 1) // _lib.SUBTILE
-        return Endpoint(base, base + HEADER_BYTES, base + HEADER_BYTES + _round_up(8 * max(nsub, 1), 16))
+        ep = Endpoint(base, base + HEADER_BYTES, base + HEADER_BYTES + _round_up(8 * max(nsub, 1), 16))
+        ep.cap = self.cap   # travels to make_sources: receivers never read beyond their slot
+        return ep
 
 
 @dataclass(frozen=True)
@@ -81,6 +83,7 @@ def make_sources(eps, seqs) -> Sources:
     for i, (e, q) in enumerate(zip(eps, seqs)):
         s.ep[i] = e
         s.seq[i] = q
+        s.cap[i] = getattr(e, "cap", 0)
     return s
 
 
