@@ -7,7 +7,7 @@ ComprEx.py:100-199; thresholds src/threshold.hxx, codecs src/compressor.hxx).
 1. the threshold kernel estimates the magnitude cut of ``rests + v`` with the
    reference's sampling rule (bit-exact) and leaves it in device memory;
 2. the compress kernel does ``rests += v``, selects ``|rests| > thr``, stores
-   the (index, value) pairs in ascending index order directly into the
+   the (index, value) pairs, grouped by 1024-element sub-tile, directly into the
    destination rank's receive slot over NVLink, zeroes what it sent and
    publishes the sequence number.
 

@@ -10,31 +10,31 @@
 // Work is warp-granular and free of block-wide barriers: a warp owns one
 // 1024-element sub-tile at a time, loads it with 16-byte accesses (32
 // elements per lane, all loads in flight together), ranks the survivors with
-// warp ballots, reserves room for them in the pair list with ONE atomicAdd on
-// a counter in this GPU's memory, and stores them through a small shared
+// one warp scan, reserves room for them in the pair list with ONE atomicAdd
+// on a counter in this GPU's memory, and stores them through a small shared
 // staging buffer as coalesced 8-byte (index, value) pairs straight into the
 // receive slots of up to CX_MAX_PEERS targets (peer GPUs' memory mapped over
 // NVLink, or local slots).  No warp ever waits for another one, so the kernel
 // has no spin loop at all.
 //
-// Inside a sub-tile the pairs are in ascending index order like the
-// reference's wire format; sub-tiles land in the list in the order of their
-// reservations.  Next to the pairs every target receives one table entry per
-// sub-tile, {start, count}: receivers use it to find, without searching or
-// sorting, the pairs that fall into the part of the vector they own, and to
-// apply them in a fixed order.
+// The pairs of one sub-tile are contiguous in the list; sub-tiles land in the
+// list in the order of their reservations.  Next to the pairs every target
+// receives one table entry per sub-tile, {start, count}: receivers use it to
+// find, without searching or sorting, the pairs that fall into the part of
+// the vector they own, and to apply them in a fixed order.  (The reference's
+// wire format lists the pairs in ascending index order; nothing on the
+// receiving side depends on that order, each index occurs once per payload.)
 //
-// Survivors that do not fit into the slot (position >= cap) are not emitted
-// and stay in the residual, which error feedback makes safe; the count is
-// reported.  The CTA that finishes last writes the header and publishes the
-// notification (st.release.sys) after every CTA's stores were fenced at
-// system scope.
+// Survivors that do not fit into the slot are not emitted and stay in the
+// residual, which error feedback makes safe; the count is reported.  The CTA
+// that finishes last writes the header and publishes the notification
+// (st.release.sys) after every CTA's stores were fenced at system scope.
 #include "cx_device.cuh"
 
 namespace {
 
 #ifndef CX_COMPRESS_MIN_BLOCKS
-#define CX_COMPRESS_MIN_BLOCKS 2  // CTAs per SM the register budget is tuned for
+#define CX_COMPRESS_MIN_BLOCKS 4  // CTAs per SM the register budget is tuned for
 #endif
 
 constexpr int kThreads = 256;
@@ -51,6 +51,7 @@ struct CompressParams {
   uint32_t nsub;
   uint32_t nregions;     // power of two; sub-tile s reserves in region s % nregions
   uint32_t region_size;  // cap / nregions pairs each
+  uint32_t vec;          // g and r are aligned for 16-byte (8-byte for 16-bit g) accesses
   uint64_t seq;
   CxWorkCounters* ctr;
   CxStats* stats;
@@ -58,186 +59,182 @@ struct CompressParams {
   CxTargets tg;
 };
 
+// One sub-tile, one warp.  Lane L holds elements {c*128 + 4L + e}; FULL means
+// "aligned and entirely inside the vector" and takes the unguarded vector path.
+template <typename T, bool HAS_G, bool HAS_R, bool FULL>
+__device__ __forceinline__ void compress_subtile(const CompressParams& p, const uint32_t sub,
+                                                 const int lane, const float thr,
+                                                 const T* __restrict__ g, float* __restrict__ r,
+                                                 CxPair* stage) {
+  const int64_t sub_base = (int64_t)sub * CX_SUBTILE;
+  const T* gp = g + sub_base + lane * 4;
+  float* rp = r + sub_base + lane * 4;
+  const int left = (int)min((int64_t)CX_SUBTILE, p.n - sub_base) - lane * 4;  // my elements e < left - c*128
+
+  // ---- load, add -------------------------------------------------------------
+  float v[kChunks][4];
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) v[c][e] = 0.f;
+    if (HAS_R) {
+      if (FULL) {
+        cx::load4(rp + c * 128, v[c]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (c * 128 + e < left) v[c][e] = rp[c * 128 + e];
+      }
+    }
+  }
+  if (HAS_G) {
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+      float b[4] = {0.f, 0.f, 0.f, 0.f};
+      if (FULL) {
+        cx::load4(gp + c * 128, b);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (c * 128 + e < left) b[e] = cx::Elem<T>::to_f(gp[c * 128 + e]);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[c][e] = v[c][e] + b[e];
+    }
+  }
+
+  // ---- classify: bit c*4+e of mask, strict '>' like the reference --------------
+  uint32_t mask = 0;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const bool sel = fabsf(v[c][e]) > thr && (FULL || c * 128 + e < left);
+      mask |= (sel ? 1u : 0u) << (4 * c + e);
+    }
+  }
+
+  // ---- rank: lanes in order, each lane's survivors consecutive --------------------
+  const uint32_t mine = __popc(mask);
+  uint32_t incl = mine;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += t;
+  }
+  const uint32_t count = __shfl_sync(0xffffffffu, incl, 31);
+  const uint32_t first = incl - mine;  // position of my first survivor inside the sub-tile
+
+  // ---- reserve room in the pair list ----------------------------------------------
+  // The list is cut into nregions equal regions with one counter each, neighbouring
+  // sub-tiles use different regions: atomics on one address are serialised by the L2.
+  const uint32_t region = sub & (p.nregions - 1);
+  uint32_t base = 0;
+  if (count) {
+    if (lane == 0) base = atomicAdd(&p.ctr->region[region][0], count);
+    base = __shfl_sync(0xffffffffu, base, 0);
+  }
+  const uint32_t emit = base >= p.region_size ? 0u : min(count, p.region_size - base);  // pairs that fit
+  base += region * p.region_size;
+  if (lane < p.tg.count) {
+    uint2 entry;
+    entry.x = emit ? base : 0u;
+    entry.y = emit;
+    reinterpret_cast<uint2*>(p.tg.ep[lane].table)[sub] = entry;
+  }
+
+  // ---- stage in shared memory, store coalesced to every target ------------------------
+  const int32_t idx0 = (int32_t)sub_base + lane * 4;
+  for (uint32_t w0 = 0; w0 < emit; w0 += kStage) {   // one pass unless the sub-tile is dense
+    uint32_t pos = first - w0;                        // wraps below the window: fails the test
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (mask & (1u << (4 * c + e))) {
+          if (pos < (uint32_t)kStage) {
+            CxPair pr;
+            pr.idx = idx0 + c * 128 + e;
+            pr.val = __float_as_uint(v[c][e]);
+            stage[pos] = pr;
+          }
+          ++pos;
+        }
+      }
+    }
+    __syncwarp();
+    const uint32_t lim = min((uint32_t)kStage, emit - w0);
+    for (uint32_t i = lane; i < lim; i += 32) {
+      const CxPair pr = stage[i];
+      for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].pairs[base + w0 + i] = pr;
+    }
+    __syncwarp();
+  }
+
+  // ---- residual: zero what was emitted, keep the rest ---------------------------------------
+  if (HAS_R) {
+    if (emit < count) {  // the slot is full: survivors from position emit on stay in the residual
+      uint32_t pos = first;
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (mask & (1u << (4 * c + e))) {
+            if (pos >= emit) mask &= ~(1u << (4 * c + e));
+            ++pos;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+      const uint32_t m = (mask >> (4 * c)) & 0xfu;
+      if (!HAS_G && m == 0) continue;  // nothing changed in this vector
+      float out[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) out[e] = (m & (1u << e)) ? 0.f : v[c][e];
+      if (FULL) {
+        cx::store4(rp + c * 128, out);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (c * 128 + e < left) rp[c * 128 + e] = out[e];
+      }
+    }
+  }
+}
+
+// The guarded path (unaligned views, the last partial sub-tile) is kept out of line
+// so that its register needs do not weigh on the fast path.
+template <typename T, bool HAS_G, bool HAS_R>
+__device__ __noinline__ void compress_subtile_guarded(const CompressParams& p, const uint32_t sub,
+                                                      const int lane, const float thr, const T* g,
+                                                      float* r, CxPair* stage) {
+  compress_subtile<T, HAS_G, HAS_R, false>(p, sub, lane, thr, g, r, stage);
+}
+
 // T: element type of g.  HAS_G / HAS_R select compress_add_update (both),
-// compress_update (r only) and compress (g only).  VEC: 16-byte aligned views.
-template <typename T, bool HAS_G, bool HAS_R, bool VEC>
-__global__ void __launch_bounds__(kThreads, CX_COMPRESS_MIN_BLOCKS) compress_kernel(const CompressParams p) {
+// compress_update (r only) and compress (g only).
+template <typename T, bool HAS_G, bool HAS_R>
+__global__ void __launch_bounds__(kThreads, CX_COMPRESS_MIN_BLOCKS)
+compress_kernel(const __grid_constant__ CompressParams p) {
   __shared__ CxPair s_stage[kWarps][kStage];
   __shared__ uint32_t s_last;
+  __shared__ uint32_t s_found, s_nnz;
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const uint32_t lt = (1u << lane) - 1u;
   const float thr = *p.thr;
   const T* __restrict__ g = reinterpret_cast<const T*>(p.g);
   float* __restrict__ r = p.r;
   CxPair* stage = s_stage[warp];
   const uint32_t nwarps = gridDim.x * kWarps;
+  const uint32_t nfull = p.vec ? (uint32_t)(p.n / CX_SUBTILE) : 0u;  // sub-tiles on the fast path
 
   for (uint32_t sub = blockIdx.x * kWarps + warp; sub < p.nsub; sub += nwarps) {
-    const int64_t sub_base = (int64_t)sub * CX_SUBTILE;
-
-    // ---- load, add, classify ------------------------------------------------
-    // r first (all eight 16-byte loads in flight), then g folded in chunk by chunk:
-    // the values live in 32 registers per lane.
-    float v[kChunks][4];
-#pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
-      const int64_t i0 = sub_base + c * 128 + lane * 4;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) v[c][e] = 0.f;
-      if (HAS_R) {
-        if (VEC && i0 + 3 < p.n) {
-          cx::load4(r + i0, v[c]);
-        } else {
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            if (i0 + e < p.n) v[c][e] = r[i0 + e];
-        }
-      }
-    }
-    if (HAS_G) {
-#pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        const int64_t i0 = sub_base + c * 128 + lane * 4;
-        float b[4] = {0.f, 0.f, 0.f, 0.f};
-        if (VEC && i0 + 3 < p.n) {
-          cx::load4(g + i0, b);
-        } else {
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            if (i0 + e < p.n) b[e] = cx::Elem<T>::to_f(g[i0 + e]);
-        }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) v[c][e] = v[c][e] + b[e];
-      }
-    }
-    const int64_t left = p.n - sub_base;  // elements of this sub-tile that exist
-    uint32_t mask = 0;                    // bit c*4+e
-#pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        if (fabsf(v[c][e]) > thr && c * 128 + lane * 4 + e < left) mask |= 1u << (4 * c + e);  // strict '>'
-    }
-
-    // ---- rank the survivors: per 128-element chunk, lanes in index order -----
-    // ex: survivors of lower lanes in the same chunk, tot: survivors of the chunk,
-    // both packed 8 bits per chunk (at most 124 and 128).
-    uint32_t ex_lo = 0, ex_hi = 0, tot_lo = 0, tot_hi = 0, count = 0;
-#pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
-      const uint32_t cnt = __popc((mask >> (4 * c)) & 0xfu);
-      const uint32_t b0 = __ballot_sync(0xffffffffu, cnt & 1u);
-      const uint32_t b1 = __ballot_sync(0xffffffffu, cnt & 2u);
-      const uint32_t b2 = __ballot_sync(0xffffffffu, cnt & 4u);
-      const uint32_t ex = __popc(b0 & lt) + 2 * __popc(b1 & lt) + 4 * __popc(b2 & lt);
-      const uint32_t tot = __popc(b0) + 2 * __popc(b1) + 4 * __popc(b2);
-      if (c < 4) { ex_lo |= ex << (8 * c); tot_lo |= tot << (8 * c); }
-      else { ex_hi |= ex << (8 * (c - 4)); tot_hi |= tot << (8 * (c - 4)); }
-      count += tot;
-    }
-#define CX_EX(c) ((((c) < 4 ? ex_lo : ex_hi) >> (8 * ((c)&3))) & 0xffu)
-#define CX_TOT(c) ((((c) < 4 ? tot_lo : tot_hi) >> (8 * ((c)&3))) & 0xffu)
-
-    // ---- reserve room in the pair list -----------------------------------------
-    // The pair list is cut into nregions equal regions with one counter each, and
-    // neighbouring sub-tiles use different regions: atomics on one address are
-    // serialised by the L2, a single counter would cap the kernel's throughput.
-    const uint32_t region = sub & (p.nregions - 1);
-    uint32_t base = 0;
-    if (count) {
-      if (lane == 0) base = atomicAdd(&p.ctr->region[region][0], count);
-      base = __shfl_sync(0xffffffffu, base, 0);
-    }
-    const uint32_t emit = base >= p.region_size ? 0u : min(count, p.region_size - base);  // pairs that fit
-    base += region * p.region_size;
-    if (lane < p.tg.count) {
-      uint2 entry;
-      entry.x = emit ? base : 0u;
-      entry.y = emit;
-      reinterpret_cast<uint2*>(p.tg.ep[lane].table)[sub] = entry;
-    }
-
-    // ---- stage in shared memory, store coalesced to every target -----------------
-    const int32_t lane_idx0 = (int32_t)sub_base + lane * 4;
-    if (count <= kStage) {
-      uint32_t off = 0;
-#pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        uint32_t pos = off + CX_EX(c);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          if (mask & (1u << (4 * c + e))) {
-            CxPair pr;
-            pr.idx = lane_idx0 + c * 128 + e;
-            pr.val = __float_as_uint(v[c][e]);
-            stage[pos++] = pr;
-          }
-        }
-        off += CX_TOT(c);
-      }
-      __syncwarp();
-      for (uint32_t i = lane; i < emit; i += 32) {
-        const CxPair pr = stage[i];
-        for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].pairs[base + i] = pr;
-      }
-      __syncwarp();
-    } else {
-      uint32_t off = 0;
-#pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        uint32_t pos = CX_EX(c);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          if (mask & (1u << (4 * c + e))) {
-            CxPair pr;
-            pr.idx = lane_idx0 + c * 128 + e;
-            pr.val = __float_as_uint(v[c][e]);
-            stage[pos++] = pr;
-          }
-        }
-        __syncwarp();
-        const uint32_t tot = CX_TOT(c);
-        const uint32_t lim = emit > off ? min(emit - off, tot) : 0u;
-        for (uint32_t i = lane; i < lim; i += 32) {
-          const CxPair pr = stage[i];
-          for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].pairs[base + off + i] = pr;
-        }
-        __syncwarp();
-        off += tot;
-      }
-    }
-
-    // ---- residual: zero what was emitted, keep the rest ------------------------------
-    if (HAS_R) {
-      uint32_t off = 0;
-#pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        const uint32_t m = (mask >> (4 * c)) & 0xfu;
-        uint32_t pos = off + CX_EX(c);
-        off += CX_TOT(c);
-        if (!HAS_G && m == 0) continue;  // nothing changed in this vector
-        const int64_t i0 = sub_base + c * 128 + lane * 4;
-        float out[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const bool sel = m & (1u << e);
-          out[e] = (sel && pos < emit) ? 0.f : v[c][e];
-          pos += sel ? 1u : 0u;
-        }
-        if (VEC && i0 + 3 < p.n) {
-          cx::store4(r + i0, out);
-        } else {
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            if (i0 + e < p.n) r[i0 + e] = out[e];
-        }
-      }
-    }
-#undef CX_EX
-#undef CX_TOT
+    if (sub < nfull) compress_subtile<T, HAS_G, HAS_R, true>(p, sub, lane, thr, g, r, stage);
+    else compress_subtile_guarded<T, HAS_G, HAS_R>(p, sub, lane, thr, g, r, stage);
   }
 
   // ---- completion: the CTA that arrives last publishes -------------------------------
@@ -246,13 +243,12 @@ __global__ void __launch_bounds__(kThreads, CX_COMPRESS_MIN_BLOCKS) compress_ker
   if (tid == 0) {
     const uint32_t prev = atomicAdd(&p.ctr->done, 1u);
     s_last = (prev == gridDim.x - 1) ? 1u : 0u;
+    s_found = 0;
+    s_nnz = 0;
   }
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  __shared__ uint32_t s_found, s_nnz;
-  if (tid == 0) { s_found = 0; s_nnz = 0; }
-  __syncthreads();
   if ((uint32_t)tid < p.nregions) {
     const uint32_t f = *reinterpret_cast<volatile uint32_t*>(&p.ctr->region[tid][0]);
     atomicAdd(&s_found, f);
@@ -304,19 +300,11 @@ __global__ void compress_empty_kernel(const CompressParams p) {
   }
 }
 
-template <typename T, bool HAS_G, bool HAS_R>
-void launch_typed(const CompressParams& p, bool vec, int grid, cudaStream_t s) {
-  if (vec)
-    compress_kernel<T, HAS_G, HAS_R, true><<<grid, kThreads, 0, s>>>(p);
-  else
-    compress_kernel<T, HAS_G, HAS_R, false><<<grid, kThreads, 0, s>>>(p);
-}
-
 template <typename T>
-void launch_mode(const CompressParams& p, bool vec, int grid, cudaStream_t s) {
-  if (p.g && p.r) launch_typed<T, true, true>(p, vec, grid, s);
-  else if (p.r) launch_typed<T, false, true>(p, vec, grid, s);
-  else launch_typed<T, true, false>(p, vec, grid, s);
+void launch_mode(const CompressParams& p, int grid, cudaStream_t s) {
+  if (p.g && p.r) compress_kernel<T, true, true><<<grid, kThreads, 0, s>>>(p);
+  else if (p.r) compress_kernel<T, false, true><<<grid, kThreads, 0, s>>>(p);
+  else compress_kernel<T, true, false><<<grid, kThreads, 0, s>>>(p);
 }
 
 }  // namespace
@@ -353,15 +341,15 @@ int cx_compress_cuda(int gdtype, const void* g, float* r, int64_t n, const float
     return cx_check_launch("compress_empty_kernel");
   }
   const size_t esz = gdtype == CX_F32 ? 4 : 2;
-  const bool vec = (!r || (reinterpret_cast<uintptr_t>(r) & 15) == 0) &&
-                   (!g || (reinterpret_cast<uintptr_t>(g) & (4 * esz - 1)) == 0);
+  p.vec = (!r || (reinterpret_cast<uintptr_t>(r) & 15) == 0) &&
+          (!g || (reinterpret_cast<uintptr_t>(g) & (4 * esz - 1)) == 0);
   int grid = cx_sm_count() * CX_COMPRESS_MIN_BLOCKS;
   const int need = (int)((p.nsub + kWarps - 1) / kWarps);
   if (grid > need) grid = need;
   switch (gdtype) {
-    case CX_F32: launch_mode<float>(p, vec, grid, s); break;
-    case CX_BF16: launch_mode<__nv_bfloat16>(p, vec, grid, s); break;
-    case CX_F16: launch_mode<__half>(p, vec, grid, s); break;
+    case CX_F32: launch_mode<float>(p, grid, s); break;
+    case CX_BF16: launch_mode<__nv_bfloat16>(p, grid, s); break;
+    case CX_F16: launch_mode<__half>(p, grid, s); break;
     default: return cx_set_error("cx_compress: unsupported dtype on CUDA", 0);
   }
   cx_note_launch();
