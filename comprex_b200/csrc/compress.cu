@@ -34,7 +34,7 @@
 namespace {
 
 #ifndef CX_COMPRESS_MIN_BLOCKS
-#define CX_COMPRESS_MIN_BLOCKS 4  // CTAs per SM the register budget is tuned for
+#define CX_COMPRESS_MIN_BLOCKS 3  // CTAs per SM the register budget is tuned for (measured best of 2..5)
 #endif
 
 constexpr int kThreads = 256;
