@@ -157,9 +157,11 @@ __device__ __forceinline__ void update4(const ApplyParams& p, int64_t i, const f
     } else {  // AdamW
       mv[e] = a.beta1 * mv[e] + (1.f - a.beta1) * g;
       vv[e] = a.beta2 * vv[e] + (1.f - a.beta2) * g * g;
-      const float mh = mv[e] / a.bc1;
-      const float vh = vv[e] / a.bc2;
-      wv[e] = wv[e] * (1.f - a.lr * a.wd) - a.lr * mh / (sqrtf(vh) + a.eps);
+      // reciprocals instead of divisions: one correctly rounded 1/x per element, the
+      // bias corrections' reciprocals are loop invariants; same arithmetic as the host twin
+      const float mh = mv[e] * __frcp_rn(a.bc1);
+      const float vh = vv[e] * __frcp_rn(a.bc2);
+      wv[e] = wv[e] * (1.f - a.lr * a.wd) - a.lr * mh * __frcp_rn(sqrtf(vh) + a.eps);
     }
   }
   if (vec) {

@@ -270,8 +270,8 @@ int cx_apply_host(const CxSources* src, int64_t n, const CxApplyArgs* a, uint32_
         const float mv = a->beta1 * a->m[i] + (1.f - a->beta1) * g;
         const float vv = a->beta2 * a->v[i] + (1.f - a->beta2) * g * g;
         a->m[i] = mv; a->v[i] = vv;
-        const float mh = mv / a->bc1, vh = vv / a->bc2;
-        wv = wv * (1.f - a->lr * a->wd) - a->lr * mh / (sqrtf(vh) + a->eps);
+        const float mh = mv * (1.f / a->bc1), vh = vv * (1.f / a->bc2);
+        wv = wv * (1.f - a->lr * a->wd) - a->lr * mh * (1.f / (sqrtf(vh) + a->eps));
       }
       w[i] = wv;
       if (a->shadow) store_elem(sdt, a->shadow, i, wv);

@@ -345,11 +345,14 @@ class GaspiEnvironment:
         return (len(self._segments), self._segments[-1]["used"] if self._segments else 0)
 
     def heap_release(self, mark) -> None:
-        """Give back everything allocated since ``mark`` (stack discipline)."""
+        """Give back everything allocated since ``mark`` (stack discipline, collective).
+
+        All ranks first finish their queued work: a peer may still be storing into the
+        blocks that are about to be zeroed and handed out again."""
         nseg, used = mark
-        self.flush()
+        self.barrier()
         while len(self._segments) > max(nseg, 1):
-            self._free_segment(self._segments.pop())
+            self._free_segment(self._segments.pop(), collective=True)
         if self._segments and nseg >= 1:
             seg = self._segments[nseg - 1]
             lo, hi = used, seg["used"]
@@ -362,7 +365,7 @@ class GaspiEnvironment:
             seg["used"] = 0
         self.barrier()
 
-    def _free_segment(self, seg: dict) -> None:
+    def _free_segment(self, seg: dict, collective: bool = False) -> None:
         keep = seg["keep"]
         if keep is None:
             return
@@ -372,6 +375,8 @@ class GaspiEnvironment:
         elif kind == "ipc":
             for p in keep[2]:
                 self.lib.cx_cuda_ipc_close(p)
+            if collective and self.group is not None:
+                dist.barrier(group=self.group)   # every importer has unmapped before the owner frees
             self.lib.cx_cuda_free(keep[1])
         elif kind == "shm":
             for p in seg["bases"]:
