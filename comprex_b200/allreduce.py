@@ -80,6 +80,25 @@ class _AllreduceBase:
         self._status = self._env.new_status(type(self).__name__)
         self._counters = self._env.scratch(64)
 
+    # Target / source descriptors depend only on the parity of the step: they are built
+    # once and reused, a call then only refreshes the sequence numbers.
+    def _cached_targets(self, key, build):
+        cache = self.__dict__.setdefault("_desc_cache", {})
+        tg = cache.get(key)
+        if tg is None:
+            tg = cache[key] = P.make_targets(build())
+        return tg
+
+    def _cached_sources(self, key, build, seq):
+        cache = self.__dict__.setdefault("_desc_cache", {})
+        src = cache.get(key)
+        if src is None:
+            eps = build()
+            src = cache[key] = P.make_sources(eps, [seq] * len(eps))
+        for i in range(src.count):
+            src.seq[i] = seq
+        return src
+
     def _prep(self, vector):
         if self.size is None:
             raise ComprexError("setup_connections was not called")
@@ -205,12 +224,14 @@ class BigRingAllreduce(_AllreduceBase):
 
         def send():
             if nr > 1:
-                tg = P.make_targets([self._slots[me][par].endpoint(env, r) for r in range(nr) if r != me])
+                tg = self._cached_targets(("tg", par), lambda: [self._slots[me][par].endpoint(env, r)
+                                                                 for r in range(nr) if r != me])
                 P.dense_send(env, t, None, self.size, seq, tg, self._counters)
 
         def reduce():
             if nr > 1:
-                src = P.make_sources([self._slots[j][par].endpoint(env) for j in arrival], [seq] * len(arrival))
+                src = self._cached_sources(("src", par), lambda: [self._slots[j][par].endpoint(env) for j in arrival],
+                                           seq)
                 P.dense_reduce(env, t, t, self.size, src, self._status)
         return [send, reduce]
 
@@ -292,7 +313,7 @@ class Comprex_BigRingAllreduce(_ComprexAllreduceBase):
     def _send_targets(self, par):
         env, me = self._env, self._env.rank
         dests = [r for r in range(env.ranks) if r != me or self.consistent]
-        return P.make_targets([self._slots[me][par].endpoint(env, r) for r in dests])
+        return self._cached_targets(("tg", par), lambda: [self._slots[me][par].endpoint(env, r) for r in dests])
 
     def _plan_common(self, t, g, fixed_thr, rounds=1, recv_args=None):
         env = self._env
@@ -315,7 +336,8 @@ class Comprex_BigRingAllreduce(_ComprexAllreduceBase):
                 order = self._order()
                 if not order:
                     return
-                src = P.make_sources([self._slots[j][par].endpoint(env) for j in order], [seq] * len(order))
+                src = self._cached_sources(("src", par), lambda: [self._slots[j][par].endpoint(env) for j in order],
+                                           seq)
                 if recv_args is not None:
                     # fused averaging + parameter update instead of a dense result; ``True``
                     # means "whatever the owner sets in _recv_args_now before this phase runs"
