@@ -19,7 +19,9 @@ the timed region.  ``gpu_launches`` counts this library's kernel launches inside
 the device-timed region (rank 0).  Clocks are sampled with nvidia-smi during the
 timed region.
 
-``--impl reference`` reports why the reference cannot run here.
+``--impl reference`` reports why the reference cannot run here.  ``--impl dense`` runs the
+comparison arm on the same model and data: stock DistributedDataParallel (dense NCCL allreduce)
+with the stock torch optimizer.
 """
 import argparse
 import json
@@ -32,7 +34,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-REFERENCE_UNAVAILABLE = ("reference is not installable offline: /root/reference has no setup.py/pyproject.toml "
+REFERENCE_UNAVAILABLE = ("reference is not installable offline: its tree has no setup.py/pyproject.toml "
                          "(pip: 'Neither setup.py nor pyproject.toml found'), and it needs GPI-2, GaspiCxx and "
                          "TensorFlow 2.3, none of which are on this image")
 
@@ -42,7 +44,7 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "dense"])
     ap.add_argument("--model", default="resnet50", choices=["resnet50", "gpt2", "lenet"])
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch (default: the named config)")
     ap.add_argument("--ratio", type=float, default=None)
@@ -132,7 +134,7 @@ def main():
         batch = args.batch or 128
         ratio = args.ratio or 0.01
         model = resnet50().to(dev).to(torch.bfloat16).to(memory_format=torch.channels_last)
-        opt_kw = dict(lr=0.1, momentum=0.9, rule="sgd", weight_decay=0.0)
+        opt_kw = dict(lr=0.01, momentum=0.9, rule="sgd", weight_decay=0.0)
 
         def host_batch(g):
             return (torch.randn(batch, 3, 224, 224, generator=g).to(torch.bfloat16)
@@ -177,8 +179,25 @@ def main():
     broadcast_parameters(model, env, 0)
     # slots sized for 2x the expected survivors (what does not fit stays in the residual)
     size_factor = max(4.0 * ratio, 1e-3) + 1e-4
-    opt = ComprexOptimizer(model.parameters(), env, compression_ratio=ratio, size_factor=size_factor,
-                           bucket_cap_mb=args.bucket_mb, overlap=not args.no_overlap, **opt_kw)
+    dense = args.impl == "dense"
+    if dense:
+        # comparison arm: stock DistributedDataParallel (dense NCCL allreduce, 25 MB buckets) and
+        # the stock fused torch optimizer on the same model, data and step structure
+        from torch.nn.parallel import DistributedDataParallel as DDP
+        if args.model == "gpt2":
+            opt = torch.optim.AdamW(model.parameters(), lr=opt_kw["lr"], betas=opt_kw["betas"],
+                                    weight_decay=opt_kw["weight_decay"], fused=True)
+        else:
+            opt = torch.optim.SGD(model.parameters(), lr=opt_kw["lr"], momentum=opt_kw.get("momentum", 0.0))
+        if world > 1:
+            ddp = DDP(model, device_ids=[local], bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True)
+            def loss_fn(x, y, _m=ddp):   # route the forward through the DDP wrapper
+                if args.model == "gpt2":
+                    return _m(x, y)
+                return F.cross_entropy(_m(x).float() if args.model == "resnet50" else _m(x), y)
+    else:
+        opt = ComprexOptimizer(model.parameters(), env, compression_ratio=ratio, size_factor=size_factor,
+                               bucket_cap_mb=args.bucket_mb, overlap=not args.no_overlap, **opt_kw)
 
     gen = torch.Generator().manual_seed(100 + rank)
     host = [host_batch(gen) for _ in range(4)]
@@ -251,11 +270,12 @@ def main():
         e2e = {"value": round(batch * world * args.steps / sec, 2), "unit": "samples/s",
                "h2d_bytes_per_step": hx.numel() * hx.element_size() + hy.numel() * hy.element_size(),
                "d2h_bytes_per_step": 4, "ms_per_step": round(sec * 1e3 / args.steps, 3)}
-    stats = opt.stats()
+    stats = {} if dense else opt.stats()
     if rank == 0:
         cfg.update({"parallelism": f"dp{world}", "per_gpu_batch": batch, "params": nparams,
                     "compression_ratio": ratio, "bucket_mb": args.bucket_mb, "overlap": not args.no_overlap,
-                    "allreduce": "comprex_bigring (direct NVLink peer stores, replica-consistent)",
+                    "allreduce": ("dense NCCL allreduce (DistributedDataParallel), stock torch optimizer" if dense else
+                                  "comprex_bigring (direct NVLink peer stores, replica-consistent)"),
                     "cache": "inputs_larger_than_L2 (activations + weights per step exceed 126 MB)",
                     "first_bucket_nnz": stats.get("nnz"), "first_bucket_n": stats.get("n"), "final_loss": final_loss})
         print(json.dumps({
@@ -263,7 +283,7 @@ def main():
             "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
             "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp32" if args.model == "lenet" else "bf16", "data": "synthetic",
-            "impl": "ours", "config": cfg, "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches)}))
+            "impl": "dense_nccl_ddp" if dense else "ours", "config": cfg, "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches)}))
     env.close()
     if world > 1:
         dist.destroy_process_group()

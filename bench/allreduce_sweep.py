@@ -8,7 +8,7 @@ every repetition, an L2 flush between repetitions, and the MAX over ranks of
 every repetition before the median is taken.
 
     torchrun --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 bench/allreduce_sweep.py \
-        --out gpurun_out/sweep_p8.jsonl
+        --out results/sweep_p8.jsonl
 
 Every row carries the dense ``torch.distributed.all_reduce`` (NCCL) time of the
 same tensor, the speed-up against it, the fraction of the vector that was sent,

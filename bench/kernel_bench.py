@@ -15,7 +15,7 @@ ops) or reads/writes the dense state once (dense ops).  Fractions are "of
 measured": the copy bandwidth in MEASURED_PEAKS.json at the repository root
 when present (6.65 TB/s otherwise, "of fallback").
 
-    python bench/kernel_bench.py --out gpurun_out/kernel_bench.jsonl
+    python bench/kernel_bench.py --out results/kernel_bench.jsonl
 """
 import argparse
 import json

@@ -3,7 +3,7 @@ examples/comprex_speed.cpp: ``writeRemote`` + ``readRemote_add`` each way, sizes
 1e5 ... 5e8 bytes, top-k 10 % / 1 % / 0.1 %, bandwidth ``2*n*4/t``), dense GaspiEx and
 compressed Comprex, device-timed with CUDA events, max over the two ranks.
 
-    torchrun --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 bench/p2p_pingpong.py --out gpurun_out/p2p.jsonl
+    torchrun --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 bench/p2p_pingpong.py --out results/p2p.jsonl
 """
 import argparse
 import json

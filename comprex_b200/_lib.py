@@ -61,6 +61,22 @@ class ApplyArgs(C.Structure):
                 ("bc1", C.c_float), ("bc2", C.c_float), ("momentum", C.c_float), ("pad2", C.c_float)]
 
 
+OPK_THRESHOLD, OPK_COMPRESS, OPK_APPLY, OPK_DENSE_SEND, OPK_DENSE_REDUCE = 1, 2, 3, 4, 5
+
+
+class Op(C.Structure):
+    """One launch of a pre-built launch sequence (CxOp in csrc/cx_common.h)."""
+    _fields_ = [("kind", C.c_int32), ("dev", C.c_int32), ("dtype", C.c_int32), ("has_ranges", C.c_int32),
+                ("g", C.c_void_p), ("r", C.c_void_p), ("n", C.c_int64),
+                ("ratio", C.c_float), ("default_subsamples", C.c_int32), ("subsample_factor", C.c_float),
+                ("scale", C.c_float), ("thr", C.c_void_p), ("cap", C.c_uint32), ("src_rank", C.c_uint32),
+                ("workspace", C.c_void_p), ("ws_bytes", C.c_int64), ("stats", C.c_void_p),
+                ("out", C.c_void_p), ("own", C.c_void_p), ("status", C.c_void_p), ("timeout_ns", C.c_uint64),
+                ("has_push", C.c_int32), ("pad", C.c_int32),
+                ("starts", C.c_int64 * MAX_PEERS), ("lens", C.c_int64 * MAX_PEERS),
+                ("tg", Targets), ("src", Sources), ("apply", ApplyArgs)]
+
+
 assert C.sizeof(Header) == 64 and C.sizeof(Stats) == 32
 
 _lock = threading.Lock()
@@ -88,6 +104,8 @@ def _declare(lib) -> None:
         "cx_dense_send": (i32, [i32, i32, vp, vp, i64, u64, P(Targets), P(i64), P(i64), vp, u32, vp]),
         "cx_dense_reduce": (i32, [i32, i32, vp, vp, i64, P(Sources), f32, P(Targets), u64, P(i64), P(i64),
                                   vp, u32, vp, u64, vp]),
+        "cx_run_ops": (i32, [P(Op), i32, u64, vp]),
+        "cx_sizeof": (i64, [i32]),
         "cx_axpy": (i32, [i32, i32, vp, i32, vp, f32, i64, vp]),
         "cx_fill_zero": (i32, [i32, vp, i64, vp]),
         "cx_rle_compress_host": (i64, [vp, vp, i64, f32, vp, i64]),
@@ -136,6 +154,10 @@ def load():
                     f"native library {path} is missing and could not be built: {exc}") from exc
         lib = C.CDLL(path)
         _declare(lib)
+        for what, mirror in enumerate((Op, Sources, Targets, ApplyArgs, None, Header)):
+            if mirror is not None and lib.cx_sizeof(what) != C.sizeof(mirror):
+                raise ComprexError(f"{path} does not match this binding ({mirror.__name__} is "
+                                   f"{lib.cx_sizeof(what)} bytes there, {C.sizeof(mirror)} here): rebuild it")
         _lib = lib
     return _lib
 

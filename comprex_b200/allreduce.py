@@ -57,6 +57,19 @@ def _cap_for(n: int, size_factor: float) -> int:
     return max(int(n * 4 * size_factor - 8) // 8, 1)
 
 
+class _OpSeq:
+    """A launch sequence built once (an array of CxOp) and run with one native call per step."""
+
+    def __init__(self, env, ops):
+        self.env = env
+        self.arr = (_lib.Op * len(ops))(*ops)
+        self.count = len(ops)
+
+    def run(self, seq: int) -> None:
+        env = self.env
+        _lib.check(env.lib.cx_run_ops(self.arr, self.count, seq, _lib.stream_ptr(env.device)), "cx_run_ops")
+
+
 class _AllreduceBase:
     compressed = False
 
@@ -350,6 +363,63 @@ class Comprex_BigRingAllreduce(_ComprexAllreduceBase):
 
     def _plan_apply(self, t, recv_args=None):
         return self._plan_common(t, t, None, recv_args=recv_args)
+
+    # ---- pre-built launch sequences: one native call for the send half, one for the receive half
+    def _seqs(self, par):
+        cache = self.__dict__.setdefault("_seq_cache", {})
+        got = cache.get(par)
+        if got is None:
+            env, comp = self._env, self._comp
+            thr, cmp_, app = _lib.Op(), _lib.Op(), _lib.Op()
+            thr.kind, cmp_.kind, app.kind = _lib.OPK_THRESHOLD, _lib.OPK_COMPRESS, _lib.OPK_APPLY
+            for op in (thr, cmp_, app):
+                op.dev, op.n = env.dev, self.size
+            thr.r = cmp_.r = self.rests.data_ptr()
+            thr.thr = cmp_.thr = comp.thr.data_ptr()
+            thr.default_subsamples, thr.subsample_factor = self._subsamples, self._sample_factor
+            cmp_.cap, cmp_.src_rank = self.cap, env.rank
+            cmp_.workspace, cmp_.ws_bytes, cmp_.stats = comp.workspace.data_ptr(), comp.ws_bytes, comp.stats.dev_ptr
+            cmp_.tg = self._send_targets(par)
+            order = self._order()
+            app.src = P.make_sources([self._slots[j][par].endpoint(env) for j in order], [0] * len(order))
+            app.status, app.timeout_ns = self._status.dev_ptr, env.timeout_ns
+            got = cache[par] = (_OpSeq(env, [thr, cmp_]), _OpSeq(env, [app]))
+        return got
+
+    def send_fast(self, g: torch.Tensor):
+        """Threshold + compress of ``g`` with one native call; returns (seq, parity) for recv_fast."""
+        self._step += 1
+        seq, par = self._step, self._step & 1
+        if self._env.ranks == 1 and not self.consistent:
+            return seq, par
+        send, _ = self._seqs(par)
+        code, ptr = _lib.dtype_code(g.dtype), g.data_ptr()
+        thr, cmp_ = send.arr[0], send.arr[1]
+        thr.g = cmp_.g = ptr
+        thr.dtype = cmp_.dtype = code
+        thr.ratio = self.compression_ratio
+        send.run(seq)
+        return seq, par
+
+    def recv_fast(self, seq: int, par: int, args) -> None:
+        """Wait for all payloads of step ``seq`` and apply them with ``args`` (one native call)."""
+        _, recv = self._seqs(par)
+        if recv.arr[0].src.count == 0:
+            return
+        recv.arr[0].apply = args
+        recv.run(seq)
+
+    def apply(self, vector):
+        if self._env._world is not None:      # virtual ranks are driven phase by phase
+            return super().apply(vector)
+        t, orig = self._prep(vector)
+        seq, par = self.send_fast(t)
+        self.recv_fast(seq, par, P.args_set(t) if self.consistent else P.args_add(t))
+        self._env.maybe_check()
+        write_back(t, orig)
+        return vector
+
+    __call__ = apply
 
     def _plan_flush(self, t):
         """Every rank sends its whole residual; ``vector`` gains the peers' (and, when

@@ -217,6 +217,53 @@ int cx_shm_unlink(const char* name);
 void* cx_host_alloc(int64_t bytes);
 int cx_host_free(void* p);
 
+/* ---- op lists ------------------------------------------------------------
+ * A collective is a short, fixed sequence of the launches above.  The caller
+ * describes it once as an array of CxOp and afterwards runs the whole
+ * sequence with one call per step; only the sequence number (and, when the
+ * user's buffer moved, a few pointers) change between steps. */
+#define CX_OPK_THRESHOLD 1
+#define CX_OPK_COMPRESS 2
+#define CX_OPK_APPLY 3
+#define CX_OPK_DENSE_SEND 4
+#define CX_OPK_DENSE_REDUCE 5
+
+typedef struct CxOp {
+  int32_t kind;
+  int32_t dev;
+  int32_t dtype;               /* element type of g (threshold, compress) or of the dense vector */
+  int32_t has_ranges;          /* dense send / gather: starts and lens are valid */
+  const void* g;               /* input vector (may be NULL for compress_update) */
+  float* r;                    /* residual (may be NULL) */
+  int64_t n;
+  float ratio;                 /* threshold */
+  int32_t default_subsamples;
+  float subsample_factor;
+  float scale;                 /* dense reduce */
+  float* thr;                  /* device cell: written by threshold, read by compress */
+  uint32_t cap;
+  uint32_t src_rank;
+  void* workspace;             /* compress scratch / dense counters */
+  int64_t ws_bytes;
+  CxStats* stats;
+  void* out;                   /* dense reduce destination */
+  const void* own;             /* dense reduce: first operand (may be NULL) */
+  uint32_t* status;
+  uint64_t timeout_ns;
+  int32_t has_push;
+  int32_t pad;
+  int64_t starts[CX_MAX_PEERS];
+  int64_t lens[CX_MAX_PEERS];
+  CxTargets tg;                /* compress / dense send targets, dense reduce push targets */
+  CxSources src;               /* apply / dense reduce sources; their seq is set per call */
+  CxApplyArgs apply;
+} CxOp;
+
+/* Runs ops[0..count) in order on `stream`; every notification written or waited
+ * for uses sequence number `seq`.  Stops at the first failing launch. */
+int cx_run_ops(CxOp* ops, int count, uint64_t seq, void* stream);
+int64_t cx_sizeof(int what); /* 0 CxOp, 1 CxSources, 2 CxTargets, 3 CxApplyArgs, 4 CxWorkCounters, 5 CxHeader */
+
 /* bounded wait on a header from the host (status in the return value) */
 int cx_host_wait_seq(const CxHeader* hdr, uint64_t seq, uint64_t timeout_ns);
 

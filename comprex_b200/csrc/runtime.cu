@@ -131,6 +131,55 @@ int cx_axpy(int dev, int ydtype, void* y, int xdtype, const void* x, float a, in
                             : cx_axpy_host(ydtype, y, xdtype, x, a, n);
 }
 
+/* struct sizes, so that the binding can verify its mirror of the layouts at load time */
+int64_t cx_sizeof(int what) {
+  switch (what) {
+    case 0: return (int64_t)sizeof(CxOp);
+    case 1: return (int64_t)sizeof(CxSources);
+    case 2: return (int64_t)sizeof(CxTargets);
+    case 3: return (int64_t)sizeof(CxApplyArgs);
+    case 4: return (int64_t)sizeof(CxWorkCounters);
+    case 5: return (int64_t)sizeof(CxHeader);
+    default: return -1;
+  }
+}
+
+int cx_run_ops(CxOp* ops, int count, uint64_t seq, void* stream) {
+  for (int i = 0; i < count; ++i) {
+    CxOp& o = ops[i];
+    int rc = 0;
+    switch (o.kind) {
+      case CX_OPK_THRESHOLD:
+        rc = cx_threshold_topk(o.dev, o.dtype, o.g, o.r, o.n, o.ratio, o.default_subsamples,
+                               o.subsample_factor, o.thr, stream);
+        break;
+      case CX_OPK_COMPRESS:
+        rc = cx_compress(o.dev, o.dtype, o.g, o.r, o.n, o.thr, o.cap, seq, &o.tg, o.workspace,
+                         o.ws_bytes, o.stats, o.src_rank, stream);
+        break;
+      case CX_OPK_APPLY:
+        for (int j = 0; j < o.src.count; ++j) o.src.seq[j] = seq;
+        rc = cx_apply(o.dev, &o.src, o.n, &o.apply, o.status, o.timeout_ns, stream);
+        break;
+      case CX_OPK_DENSE_SEND:
+        rc = cx_dense_send(o.dev, o.dtype, o.g, o.r, o.n, seq, &o.tg, o.has_ranges ? o.starts : nullptr,
+                           o.has_ranges ? o.lens : nullptr, o.workspace, o.src_rank, stream);
+        break;
+      case CX_OPK_DENSE_REDUCE:
+        for (int j = 0; j < o.src.count; ++j) o.src.seq[j] = seq;
+        rc = cx_dense_reduce(o.dev, o.dtype, o.out, o.own, o.n, &o.src, o.scale,
+                             o.has_push ? &o.tg : nullptr, seq, o.has_ranges ? o.starts : nullptr,
+                             o.has_ranges ? o.lens : nullptr, o.workspace, o.src_rank, o.status,
+                             o.timeout_ns, stream);
+        break;
+      default:
+        return cx_set_error("cx_run_ops: unknown op kind", 0);
+    }
+    if (rc) return rc;
+  }
+  return 0;
+}
+
 int cx_fill_zero(int dev, void* p, int64_t bytes, void* stream) {
   if (dev == CX_DEV_CUDA) {
     const cudaError_t e = cudaMemsetAsync(p, 0, (size_t)bytes, reinterpret_cast<cudaStream_t>(stream));

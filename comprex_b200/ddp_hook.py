@@ -112,8 +112,8 @@ def comprex_hook(state: ComprexHookState, bucket: dist.GradBucket) -> torch.futu
 
     def run():
         if red.compressed:
-            for phase in red._plan_apply(buf, recv_args=P.args_set(buf, scale)):
-                phase()
+            seq, par = red.send_fast(buf)
+            red.recv_fast(seq, par, P.args_set(buf, scale))
         else:
             for phase in red._plan_apply(buf):
                 phase()

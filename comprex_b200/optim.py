@@ -47,7 +47,7 @@ _TYPES = {
 
 
 class _Bucket:
-    __slots__ = ("start", "end", "params", "grad_views", "ar", "ready", "sent")
+    __slots__ = ("start", "end", "params", "grad_views", "ar", "ready", "sent", "seq", "par")
 
     def __init__(self, start):
         self.start, self.end = start, start
@@ -212,8 +212,7 @@ class ComprexOptimizer(torch.optim.Optimizer):
         lr, mu, _ = self._hyper()
         x = self._fold(b, lr, mu)
         ar = b.ar
-        ar._pending_plan = ar._plan_apply(x, recv_args=True)
-        ar._pending_plan[0]()
+        b.seq, b.par = ar.send_fast(x)
         b.sent = True
 
     def _on_grad(self, p) -> None:
@@ -265,8 +264,7 @@ class ComprexOptimizer(torch.optim.Optimizer):
                 if not b.sent:
                     self._send(b)
             for b in self._buckets:          # then receive: all peers' payloads are on their way
-                b.ar._recv_args_now = self._recv_args(b, lr, mu, wd)
-                b.ar._pending_plan[1]()
+                b.ar.recv_fast(b.seq, b.par, self._recv_args(b, lr, mu, wd))
                 b.sent, b.ready = False, 0
         if use_side:
             torch.cuda.current_stream(self._env.device).wait_stream(comm)
