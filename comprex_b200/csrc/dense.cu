@@ -34,6 +34,27 @@ struct SendParams {
   CxWorkCounters* ctr;
 };
 
+// Grid-stride copy of nbytes with 16-byte accesses and four loads in flight per thread.
+// Both pointers must be 16-byte aligned.  VOLATILE_SRC: the source was written by a
+// peer GPU during this kernel's lifetime, read it through L2.
+template <bool VOLATILE_SRC>
+__device__ __forceinline__ void copy_bytes16(char* dst, const char* src, int64_t nbytes, int64_t gtid,
+                                             int64_t gsz) {
+  const int64_t nv = nbytes / 16;
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+  uint4* d = reinterpret_cast<uint4*>(dst);
+  int64_t q = gtid;
+  for (; q + 3 * gsz < nv; q += 4 * gsz) {
+    uint4 a, b, c, e;
+    if (VOLATILE_SRC) { a = __ldcg(s + q); b = __ldcg(s + q + gsz); c = __ldcg(s + q + 2 * gsz); e = __ldcg(s + q + 3 * gsz); }
+    else { a = s[q]; b = s[q + gsz]; c = s[q + 2 * gsz]; e = s[q + 3 * gsz]; }
+    d[q] = a; d[q + gsz] = b; d[q + 2 * gsz] = c; d[q + 3 * gsz] = e;
+  }
+  for (; q < nv; q += gsz) d[q] = VOLATILE_SRC ? __ldcg(s + q) : s[q];
+  for (int64_t b = nv * 16 + gtid; b < nbytes; b += gsz)
+    dst[b] = VOLATILE_SRC ? __ldcg(src + b) : src[b];
+}
+
 template <typename T>
 __device__ __forceinline__ void publish_dense(const CxTargets& tg, int k, int64_t n, uint64_t seq,
                                               uint32_t src_rank, uint32_t dtype) {
@@ -87,6 +108,11 @@ __global__ void __launch_bounds__(kThreads) dense_send_kernel(const SendParams p
       const T* src = g + p.rg.start[k];
       T* dst = reinterpret_cast<T*>(p.tg.ep[k].pairs);
       const int64_t len = p.rg.len[k];
+      if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+        copy_bytes16<false>(reinterpret_cast<char*>(dst), reinterpret_cast<const char*>(src),
+                            len * (int64_t)sizeof(T), gtid, gsz);
+        continue;
+      }
       const bool vec = (reinterpret_cast<uintptr_t>(src) & (4 * sizeof(T) - 1)) == 0;
       const int64_t nv = (len + 3) / 4;
       for (int64_t q = gtid; q < nv; q += gsz) {
@@ -200,6 +226,11 @@ __global__ void __launch_bounds__(kThreads) dense_reduce_kernel(const ReducePara
       const T* slot = reinterpret_cast<const T*>(p.src.ep[j].pairs);
       T* dst = out + p.rg.start[j];
       const int64_t len = p.rg.len[j];
+      if (p.scale == 1.f && ((reinterpret_cast<uintptr_t>(slot) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+        copy_bytes16<true>(reinterpret_cast<char*>(dst), reinterpret_cast<const char*>(slot),
+                           len * (int64_t)sizeof(T), gtid, gsz);
+        continue;
+      }
       const bool vec = (reinterpret_cast<uintptr_t>(dst) & (4 * sizeof(T) - 1)) == 0;
       const int64_t nv = (len + 3) / 4;
       for (int64_t q = gtid; q < nv; q += gsz) {
@@ -323,7 +354,7 @@ int cx_dense_send_cuda(int dtype, const void* g, float* r, int64_t n, uint64_t s
       if ((lens[k] + 3) / 4 > work) work = (lens[k] + 3) / 4;
     }
   }
-  const int grid = grid_for(work, 4);
+  const int grid = grid_for(work, 8);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   switch (dtype) {
     case CX_F32:
@@ -370,7 +401,8 @@ int cx_dense_reduce_cuda(int dtype, void* out, const void* own, int64_t n, const
     }
   }
   // every CTA waits on the notifications first: stay within one co-resident wave
-  const int grid = grid_for(work, 4);
+  // (40 registers x 256 threads: six CTAs per SM)
+  const int grid = grid_for(work, 6);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   switch (dtype) {
     case CX_F32: dense_reduce_kernel<float><<<grid, kThreads, 0, s>>>(p); break;

@@ -4,8 +4,8 @@ Sweeps the reference's settings: dense ``ring`` and ``bigring``, then ``comprex_
 ``comprex_bigring`` at top-k 1 % and 0.1 %, momentum 0.9, learning rate ``0.01 * ranks``,
 batch 64 per rank, ``size_factor`` 3, initial weights broadcast from rank 0.  MNIST is read
 from ``--data`` (a directory with ``mnist.npz``) when given; without it a synthetic
-28x28x1 data set of the same shape is used (uniform inputs, labels from a fixed random
-class templates buried in noise, so that there is something to learn).
+28x28x1 data set of the same shape is used (ten fixed random class templates buried in
+uniform noise, so that there is something to learn).
 
     torchrun --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 examples/lenet_train.py --epochs 2
 """
@@ -37,7 +37,7 @@ def load_data(path, n_train, n_test, device):
     # ten fixed random templates, one per class, buried in uniform noise
     templates = torch.rand(10, 1, 28, 28, generator=g)
     y = torch.randint(0, 10, (n_train + n_test,), generator=g)
-    x = 0.3 * templates[y] + 0.7 * torch.rand(n_train + n_test, 1, 28, 28, generator=g)
+    x = 0.6 * templates[y] + 0.4 * torch.rand(n_train + n_test, 1, 28, 28, generator=g)
     x, y = x.to(device), y.to(device)
     return x[:n_train], y[:n_train], x[n_train:], y[n_train:]
 
