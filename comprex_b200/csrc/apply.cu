@@ -72,113 +72,47 @@ __device__ __forceinline__ bool wait_sources(const ApplyParams& p, uint32_t* s_n
   return bad == 0;
 }
 
-// One touched element: out (+)= scale * sum, or the SGD step on the fp32 master.
-template <typename TO>
-__device__ __forceinline__ void touch(const ApplyParams& p, int32_t idx, float sum, float scale) {
-  const float val = scale * sum;
-  if (p.a.op == CX_OP_SGD) {
-    float* w = reinterpret_cast<float*>(p.a.out);
-    const float nw = w[idx] + val;
-    w[idx] = nw;
-    if (p.a.shadow) reinterpret_cast<TO*>(p.a.shadow)[idx] = cx::Elem<TO>::from_f(nw);
-  } else {
-    TO* o = reinterpret_cast<TO*>(p.a.out);
-    o[idx] = cx::Elem<TO>::from_f(cx::Elem<TO>::to_f(o[idx]) + val);
-  }
-}
-
-// Sparse ops.  Per sub-tile: (A) the pairs of all sources are loaded together and summed in
-// source order into the warp's shared-memory accumulator, (B) every touched element is
-// updated once with its sum (the first visitor takes the sum with an exchange and leaves
-// zero behind, so the accumulator is clean again).  Three dependent memory round trips per
-// sub-tile (table, pairs, destination) instead of one per source.
 template <typename TO>
 __global__ void __launch_bounds__(kThreads) apply_sparse_kernel(const ApplyParams p) {
   __shared__ uint32_t s_nnz[CX_MAX_PEERS];
-  __shared__ __align__(16) float s_acc[kWarps][CX_SUBTILE];
   if (!wait_sources(p, s_nnz)) return;
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const uint32_t nwarps = gridDim.x * kWarps;
   const float scale = p.a.op == CX_OP_SGD ? -p.a.scale : p.a.scale;
-  float* acc = s_acc[warp];
-#pragma unroll
-  for (int q = 0; q < CX_SUBTILE / 128; ++q)
-    *reinterpret_cast<float4*>(acc + q * 128 + lane * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-  __syncwarp();
   uint32_t bad = 0;
   for (uint32_t sub = blockIdx.x * kWarps + warp; sub < p.nsub; sub += nwarps) {
     const uint32_t lo = sub * CX_SUBTILE;
-    uint32_t a = 0, cnt = 0;
+    uint32_t a = 0, b = 0;
     if (lane < p.src.count) {
       const uint2 entry = __ldcg(reinterpret_cast<const uint2*>(p.src.ep[lane].table) + sub);
-      const uint32_t b = min(entry.x + min(entry.y, (uint32_t)CX_SUBTILE), p.src.cap[lane]);  // never beyond the slot
-      a = min(entry.x, b);
-      cnt = b - a;
+      a = entry.x;
+      b = min(entry.x + min(entry.y, (uint32_t)CX_SUBTILE), p.src.cap[lane]);  // never beyond the slot
+      a = min(a, b);
     }
-    uint32_t maxcnt = cnt;
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) maxcnt = max(maxcnt, __shfl_xor_sync(0xffffffffu, maxcnt, d));
-    if (maxcnt == 0) continue;
-    if (maxcnt <= 32) {
-      // (A) one pair per lane and source, all loads in flight together
-      CxPair pr[CX_MAX_PEERS];
-#pragma unroll
-      for (int j = 0; j < CX_MAX_PEERS; ++j) {
-        const uint32_t aj = __shfl_sync(0xffffffffu, a, j);
-        const uint32_t cj = __shfl_sync(0xffffffffu, cnt, j);
-        pr[j].idx = -1;
-        pr[j].val = 0;
-        if (j < p.src.count && (uint32_t)lane < cj) pr[j] = ld_pair(p.src.ep[j].pairs + aj + lane);
-      }
-#pragma unroll
-      for (int j = 0; j < CX_MAX_PEERS; ++j) {
-        if (j < p.src.count) {   // uniform
-          const uint32_t d = (uint32_t)pr[j].idx - lo;
-          if (pr[j].idx >= 0) {
-            if (d < CX_SUBTILE && (int64_t)pr[j].idx < p.n) acc[d] += __uint_as_float(pr[j].val);
-            else { bad = CX_ST_BAD_INDEX; pr[j].idx = -1; }
+    for (int j = 0; j < p.src.count; ++j) {
+      const uint32_t aj = __shfl_sync(0xffffffffu, a, j);
+      const uint32_t bj = __shfl_sync(0xffffffffu, b, j);
+      const CxPair* pairs = p.src.ep[j].pairs;
+      for (uint32_t i = aj + lane; i < bj; i += 32) {
+        const CxPair pr = ld_pair(pairs + i);
+        const uint32_t d = (uint32_t)pr.idx - lo;
+        if (d < CX_SUBTILE && (int64_t)pr.idx < p.n) {
+          const float val = scale * __uint_as_float(pr.val);
+          if (p.a.op == CX_OP_SGD) {
+            float* w = reinterpret_cast<float*>(p.a.out);
+            const float nw = w[pr.idx] + val;
+            w[pr.idx] = nw;
+            if (p.a.shadow) reinterpret_cast<TO*>(p.a.shadow)[pr.idx] = cx::Elem<TO>::from_f(nw);
+          } else {
+            TO* o = reinterpret_cast<TO*>(p.a.out);
+            o[pr.idx] = cx::Elem<TO>::from_f(cx::Elem<TO>::to_f(o[pr.idx]) + val);
           }
-          __syncwarp();   // the next source may address the same element from another lane
+        } else {
+          bad = CX_ST_BAD_INDEX;
         }
       }
-      // (B) every touched element once
-#pragma unroll
-      for (int j = 0; j < CX_MAX_PEERS; ++j) {
-        if (j < p.src.count && pr[j].idx >= 0) {
-          const float sum = atomicExch(&acc[(uint32_t)pr[j].idx - lo], 0.f);
-          if (sum != 0.f) touch<TO>(p, pr[j].idx, sum, scale);
-        }
-      }
-      __syncwarp();
-    } else {
-      // dense payloads: same two passes, source after source
-      for (int j = 0; j < p.src.count; ++j) {
-        const uint32_t aj = __shfl_sync(0xffffffffu, a, j);
-        const uint32_t cj = __shfl_sync(0xffffffffu, cnt, j);
-        const CxPair* pairs = p.src.ep[j].pairs + aj;
-        for (uint32_t i = lane; i < cj; i += 32) {
-          const CxPair q = ld_pair(pairs + i);
-          const uint32_t d = (uint32_t)q.idx - lo;
-          if (d < CX_SUBTILE && (int64_t)q.idx < p.n) acc[d] += __uint_as_float(q.val);
-          else bad = CX_ST_BAD_INDEX;
-        }
-        __syncwarp();
-      }
-      for (int j = 0; j < p.src.count; ++j) {
-        const uint32_t aj = __shfl_sync(0xffffffffu, a, j);
-        const uint32_t cj = __shfl_sync(0xffffffffu, cnt, j);
-        const CxPair* pairs = p.src.ep[j].pairs + aj;
-        for (uint32_t i = lane; i < cj; i += 32) {
-          const CxPair q = ld_pair(pairs + i);
-          const uint32_t d = (uint32_t)q.idx - lo;
-          if (d < CX_SUBTILE && (int64_t)q.idx < p.n) {
-            const float sum = atomicExch(&acc[d], 0.f);
-            if (sum != 0.f) touch<TO>(p, q.idx, sum, scale);
-          }
-        }
-      }
-      __syncwarp();
+      __syncwarp();  // the next source may address the same elements from other lanes
     }
   }
   if (bad && p.status) *p.status = *p.status | bad;

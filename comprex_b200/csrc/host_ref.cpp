@@ -234,7 +234,7 @@ int cx_apply_host(const CxSources* src, int64_t n, const CxApplyArgs* a, uint32_
   for (uint32_t sub = 0; sub < nsub; ++sub) {
     const int64_t lo = (int64_t)sub * CX_SUBTILE;
     const int64_t hi = std::min<int64_t>(lo + CX_SUBTILE, n);
-    memset(acc, 0, sizeof(acc));
+    if (!sparse) memset(acc, 0, sizeof(acc));
     for (int j = 0; j < src->count; ++j) {
       const uint32_t e_start = src->ep[j].table[2 * sub];
       const uint32_t e_count = std::min<uint32_t>(src->ep[j].table[2 * sub + 1], CX_SUBTILE);
@@ -245,23 +245,17 @@ int cx_apply_host(const CxSources* src, int64_t n, const CxApplyArgs* a, uint32_
         float val;
         memcpy(&val, &pr.val, 4);
         if (pr.idx < lo || pr.idx >= hi) { bad |= CX_ST_BAD_INDEX; continue; }
-        acc[pr.idx - lo] += val;   // sources in order, like the kernels
-      }
-    }
-    if (sparse) {   // only the touched elements change, each once with its sum
-      for (int64_t i = lo; i < hi; ++i) {
-        const float sum = acc[i - lo];
-        if (sum == 0.f) continue;
+        if (!sparse) { acc[pr.idx - lo] += val; continue; }
         if (a->op == CX_OP_SGD) {
-          const float nw = w[i] + (-a->scale) * sum;
-          w[i] = nw;
-          if (a->shadow) store_elem(sdt, a->shadow, i, nw);
+          const float nw = w[pr.idx] + (-a->scale) * val;
+          w[pr.idx] = nw;
+          if (a->shadow) store_elem(sdt, a->shadow, pr.idx, nw);
         } else {
-          store_elem(a->out_dtype, a->out, i, load_elem(a->out_dtype, a->out, i) + a->scale * sum);
+          store_elem(a->out_dtype, a->out, pr.idx, load_elem(a->out_dtype, a->out, pr.idx) + a->scale * val);
         }
       }
-      continue;
     }
+    if (sparse) continue;
     for (int64_t i = lo; i < hi; ++i) {
       const float g = a->scale * acc[i - lo];
       if (a->op == CX_OP_SET) { store_elem(a->out_dtype, a->out, i, g); continue; }

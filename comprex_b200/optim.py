@@ -185,10 +185,10 @@ class ComprexOptimizer(torch.optim.Optimizer):
         """Clip per tensor and build the vector that is exchanged for one bucket."""
         if self.pre_clipnorm is not None:
             clip = float(self.pre_clipnorm)
-            norms = torch._foreach_norm(b.grad_views)
-            # tf.clip_by_norm: g * clip / max(norm, clip)
-            coefs = [(clip / torch.clamp(nrm.float(), min=clip)).to(self._grad.dtype) for nrm in norms]
-            torch._foreach_mul_(b.grad_views, coefs)
+            norms = torch.stack(torch._foreach_norm(b.grad_views)).float()
+            # tf.clip_by_norm: g * clip / max(norm, clip); one small kernel chain for all tensors
+            coefs = (clip / norms.clamp_(min=clip)).to(self._grad.dtype)
+            torch._foreach_mul_(b.grad_views, list(coefs.unbind()))
         g = self._grad[b.start:b.end]
         u = self._update[b.start:b.end]
         if self.rule == "sgd" and self.local_momentum:

@@ -193,10 +193,9 @@ def test_apply_add_and_set(world, n, out_dtype):
     base = torch.randn(n).to(out_dtype)
     out = base.clone().to(dev)
     P.apply_sparse(e0, src, n, P.args_add(out, 0.5), st)
-    acc = torch.zeros(n)
-    for d in dense:   # same order, same rounding as the kernel: the sources are summed first
-        acc += d
-    want = torch.where(acc != 0, (base.float() + 0.5 * acc).to(out_dtype), base)
+    want = base.clone()
+    for d in dense:   # same order, same rounding as the kernel: one source after the other
+        want = (want.float() + 0.5 * d).to(out_dtype)
     assert torch.equal(out.cpu(), want)
     out2 = torch.full((n,), 7.0, dtype=out_dtype, device=dev)
     P.apply_sparse(e0, src, n, P.args_set(out2, 0.25), st)
