@@ -106,6 +106,7 @@ def _declare(lib) -> None:
                                   vp, u32, vp, u64, vp]),
         "cx_run_ops": (i32, [P(Op), i32, u64, vp]),
         "cx_sizeof": (i64, [i32]),
+        "cx_fold": (i32, [i32, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp, f32, f32, f32, vp]),
         "cx_axpy": (i32, [i32, i32, vp, i32, vp, f32, i64, vp]),
         "cx_fill_zero": (i32, [i32, vp, i64, vp]),
         "cx_rle_compress_host": (i64, [vp, vp, i64, f32, vp, i64]),

@@ -185,6 +185,15 @@ int cx_dense_reduce(int dev, int dtype, void* out, const void* own, int64_t n,
                     const int64_t* lens, void* counters, uint32_t src_rank,
                     uint32_t* status, uint64_t timeout_ns, void* stream);
 
+/* Optimizer fold (keras/comprex_optimizer.py:101-115): per-tensor L2 clip to `clip`
+ * (<= 0: off) and u = mu*u + lr*coef*g, read straight from the gradient tensors
+ * (seg_ptr, one pointer per tensor) into the flat fp32 vector u.  The item arrays
+ * describe the tensors in pieces of at most 65536 elements; all arrays live on `dev`. */
+int cx_fold(int dev, int gdtype, const void* const* seg_ptr, const int64_t* item_off,
+            const int64_t* item_rel, const int32_t* item_len, const int32_t* item_seg,
+            const int32_t* seg_first, int nitems, float* u, float* partial, float clip,
+            float mu, float lr, void* stream);
+
 /* small elementwise helpers of the engines and the optimizer */
 int cx_axpy(int dev, int ydtype, void* y, int xdtype, const void* x, float a,
             int64_t n, void* stream); /* y += a*x */

@@ -451,3 +451,36 @@ extern "C" int cx_rle_decode_host(const void* in, int64_t in_bytes, float* out, 
   if (i != n) return cx_set_error("cx_rle_decode: runs do not cover the vector", 0);
   return 0;
 }
+
+// ---- gradient fold (see fold.cu) -------------------------------------------------------
+int cx_fold_host(int gdtype, const void* const* seg_ptr, const int64_t* item_off,
+                 const int64_t* item_rel, const int32_t* item_len, const int32_t* item_seg,
+                 const int32_t* seg_first, int nitems, float* u, float* partial, float clip,
+                 float mu, float lr) {
+  if (!dtype_ok(gdtype)) return cx_set_error("cx_fold: unsupported dtype", 0);
+  if (clip > 0.f)
+    for (int it = 0; it < nitems; ++it) {
+      float acc = 0.f;
+      for (int i = 0; i < item_len[it]; ++i) {
+        const float x = load_elem(gdtype, seg_ptr[item_seg[it]], item_rel[it] + i);
+        acc += x * x;
+      }
+      partial[it] = acc;
+    }
+  for (int it = 0; it < nitems; ++it) {
+    const int seg = item_seg[it];
+    float coef = 1.f;
+    if (clip > 0.f) {
+      float ss = 0.f;
+      for (int i = seg_first[seg]; i < seg_first[seg + 1]; ++i) ss += partial[i];
+      coef = clip / fmaxf(sqrtf(ss), clip);
+    }
+    const float a = lr * coef;
+    float* dst = u + item_off[it];
+    for (int i = 0; i < item_len[it]; ++i) {
+      const float y = mu != 0.f ? dst[i] : 0.f;
+      dst[i] = mu * y + a * load_elem(gdtype, seg_ptr[seg], item_rel[it] + i);
+    }
+  }
+  return 0;
+}

@@ -41,6 +41,10 @@ int cx_dense_reduce_cuda(int, void*, const void*, int64_t, const CxSources*, flo
 int cx_dense_reduce_host(int, void*, const void*, int64_t, const CxSources*, float, const CxTargets*,
                          uint64_t, const int64_t*, const int64_t*, uint32_t, uint32_t*, uint64_t);
 int cx_axpy_cuda(int, void*, int, const void*, float, int64_t, void*);
+int cx_fold_cuda(int, const void* const*, const int64_t*, const int64_t*, const int32_t*, const int32_t*,
+                 const int32_t*, int, float*, float*, float, float, float, void*);
+int cx_fold_host(int, const void* const*, const int64_t*, const int64_t*, const int32_t*, const int32_t*,
+                 const int32_t*, int, float*, float*, float, float, float);
 int cx_axpy_host(int, void*, int, const void*, float, int64_t);
 
 // ---- errors and accounting -------------------------------------------------------
@@ -129,6 +133,17 @@ int cx_dense_reduce(int dev, int dtype, void* out, const void* own, int64_t n, c
 int cx_axpy(int dev, int ydtype, void* y, int xdtype, const void* x, float a, int64_t n, void* stream) {
   return dev == CX_DEV_CUDA ? cx_axpy_cuda(ydtype, y, xdtype, x, a, n, stream)
                             : cx_axpy_host(ydtype, y, xdtype, x, a, n);
+}
+
+int cx_fold(int dev, int gdtype, const void* const* seg_ptr, const int64_t* item_off,
+            const int64_t* item_rel, const int32_t* item_len, const int32_t* item_seg,
+            const int32_t* seg_first, int nitems, float* u, float* partial, float clip, float mu,
+            float lr, void* stream) {
+  return dev == CX_DEV_CUDA
+             ? cx_fold_cuda(gdtype, seg_ptr, item_off, item_rel, item_len, item_seg, seg_first, nitems, u,
+                            partial, clip, mu, lr, stream)
+             : cx_fold_host(gdtype, seg_ptr, item_off, item_rel, item_len, item_seg, seg_first, nitems, u,
+                            partial, clip, mu, lr);
 }
 
 /* struct sizes, so that the binding can verify its mirror of the layouts at load time */

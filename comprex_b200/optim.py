@@ -6,17 +6,20 @@ momentum buffer scaled by the learning rate (``mom = m*mom + lr*g``),
 concatenates everything into one blob, allreduces the blob with one of six
 collectives (default ``comprex_bigring``), divides by the number of ranks and
 applies ``var = (1-wd)*var - update``.  This class keeps those semantics for
-PyTorch and maps the exchange onto three kernel launches per bucket:
+PyTorch and maps a step onto five kernel launches per bucket:
 
-1. threshold estimate of ``residual + update`` (device resident),
-2. fused ``residual += update`` / select / store pairs into every peer's slot,
-3. fused wait / scatter-add in rank order / average / parameter update, which
+1. per-tensor sums of squares and 2. clip + momentum fold, read straight from
+   the gradient tensors autograd produced into the flat fp32 update vector,
+3. threshold estimate of ``residual + update`` (device resident),
+4. fused ``residual += update`` / select / store pairs into every peer's slot,
+5. fused wait / scatter-add in rank order / average / parameter update, which
    also refreshes the low-precision copy of the weights when the model is held
    in bf16 or fp16.
 
 The parameters live in one flat fp32 master buffer (the model's tensors are
-views of it, or of its low-precision shadow) and gradients accumulate directly
-into one flat buffer, so no concatenation or slicing copy happens.  The flat
+views of it, or of its low-precision shadow, in their own memory order, so
+channels-last weights stay channels-last); there is no flat gradient buffer,
+no concatenation and no slicing copy.  The flat
 buffers are laid out in reverse parameter order and cut into buckets of
 ``bucket_cap_mb``; with ``overlap=True`` a bucket's steps 1-2 are launched on a
 side stream from a post-accumulate-grad hook as soon as its last gradient is
@@ -47,12 +50,77 @@ _TYPES = {
 
 
 class _Bucket:
-    __slots__ = ("start", "end", "params", "grad_views", "ar", "ready", "sent", "seq", "par")
+    __slots__ = ("start", "end", "params", "offsets", "ar", "ready", "sent", "seq", "par", "fold")
 
     def __init__(self, start):
         self.start, self.end = start, start
-        self.params, self.grad_views = [], []
-        self.ar, self.ready, self.sent = None, 0, False
+        self.params, self.offsets = [], []
+        self.ar, self.ready, self.sent, self.fold = None, 0, False, None
+
+
+_ITEM = 65536     # elements per fold work item
+_ALIGN = 64       # tensors start on 128-byte (bf16) / 256-byte (fp32) boundaries of the flat buffers
+
+
+def _dense_layout(p: torch.Tensor) -> bool:
+    """True when p's elements occupy numel consecutive slots (any permutation, e.g. channels-last)."""
+    if p.is_contiguous():
+        return True
+    size, stride = p.size(), p.stride()
+    expect = 1
+    for dim in sorted(range(p.dim()), key=lambda d: stride[d]):
+        if size[dim] == 1:
+            continue
+        if stride[dim] != expect:
+            return False
+        expect *= size[dim]
+    return True
+
+
+def _same_layout(a: torch.Tensor, b: torch.Tensor) -> bool:
+    return all(x == y for n, x, y in zip(a.size(), a.stride(), b.stride()) if n > 1)
+
+
+class _FoldTable:
+    """Static description of a bucket's tensors for the fold kernels plus the per-step
+    table of gradient pointers (staged through a small ring of pinned buffers)."""
+
+    def __init__(self, env, bucket):
+        dev = env.device
+        off, rel, ln, seg, first = [], [], [], [], [0]
+        for si, (p, o) in enumerate(zip(bucket.params, bucket.offsets)):
+            k = p.numel()
+            for r in range(0, max(k, 1), _ITEM):
+                off.append(o - bucket.start + r)
+                rel.append(r)
+                ln.append(min(_ITEM, k - r))
+                seg.append(si)
+            first.append(len(off))
+        self.nitems, self.nseg = len(off), len(bucket.params)
+        self.item_off = torch.tensor(off, dtype=torch.int64, device=dev)
+        self.item_rel = torch.tensor(rel, dtype=torch.int64, device=dev)
+        self.item_len = torch.tensor(ln, dtype=torch.int32, device=dev)
+        self.item_seg = torch.tensor(seg, dtype=torch.int32, device=dev)
+        self.seg_first = torch.tensor(first, dtype=torch.int32, device=dev)
+        self.partial = torch.zeros(self.nitems, dtype=torch.float32, device=dev)
+        self.ptrs = torch.zeros(self.nseg, dtype=torch.int64, device=dev)
+        self.cuda = dev.type == "cuda"
+        if self.cuda:
+            self.ring = [(torch.zeros(self.nseg, dtype=torch.int64).pin_memory(), torch.cuda.Event()) for _ in range(4)]
+            self.turn = 0
+
+    def stage(self, values) -> None:
+        """Upload this step's gradient pointers (async on the current stream)."""
+        if not self.cuda:
+            self.ptrs.copy_(torch.tensor(values, dtype=torch.int64))
+            return
+        host, ev = self.ring[self.turn]
+        self.turn = (self.turn + 1) % len(self.ring)
+        ev.synchronize()                      # the copy that last used this buffer has finished
+        host.copy_(torch.tensor(values, dtype=torch.int64))
+        self.ptrs.copy_(host, non_blocking=True)
+        ev.record()
+
 
 
 class ComprexOptimizer(torch.optim.Optimizer):
@@ -106,26 +174,30 @@ class ComprexOptimizer(torch.optim.Optimizer):
                 self._buckets.append(b)
             self._offsets.append(off)
             b.params.append(p)
-            off += (p.numel() + 3) // 4 * 4                 # 16-byte aligned tensors
+            b.offsets.append(off)
+            off += (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
             b.end = off
         self.blob_size = n = off
         dev = env.device
+        self._dtype = dt
         self._master = torch.zeros(n, dtype=torch.float32, device=dev)
         self._shadow = torch.zeros(n, dtype=dt, device=dev) if dt != torch.float32 else None
-        self._grad = torch.zeros(n, dtype=dt, device=dev)
         store = self._shadow if self._shadow is not None else self._master
         self._bucket_of = {}
-        bi = 0
-        for p, o in zip(self._params, self._offsets):
-            k = p.numel()
-            self._master[o:o + k].copy_(p.detach().reshape(-1))
-            store[o:o + k].copy_(p.detach().reshape(-1))
-            p.data = store[o:o + k].view_as(p)
-            p.grad = self._grad[o:o + k].view_as(p)
-            while o >= self._buckets[bi].end:
-                bi += 1
-            self._buckets[bi].grad_views.append(self._grad[o:o + k])
-            self._bucket_of[p] = self._buckets[bi]
+        for b in self._buckets:
+            for p, o in zip(b.params, b.offsets):
+                k = p.numel()
+                src = p.detach()
+                if not _dense_layout(src):
+                    src = src.contiguous()
+                # the flat buffers keep the tensor's own memory order (e.g. channels-last weights)
+                self._master[o:o + k].as_strided(src.size(), src.stride()).copy_(src)
+                view = store[o:o + k].as_strided(src.size(), src.stride())
+                view.copy_(src)
+                p.data = view
+                p.grad = None
+                self._bucket_of[p] = b
+        self._zeros = torch.zeros(max(p.numel() for p in plist), dtype=dt, device=dev)
         self._update = torch.zeros(n, dtype=torch.float32, device=dev)   # momentum_var / exchanged vector
         self._m = torch.zeros(n, dtype=torch.float32, device=dev) if rule == "adamw" or not local_momentum else None
         self._v = torch.zeros(n, dtype=torch.float32, device=dev) if rule == "adamw" else None
@@ -172,31 +244,41 @@ class ComprexOptimizer(torch.optim.Optimizer):
             self._buckets[0].ar = self.comprex_allreducers[0] = self.create_allreduce_op(self.allreduce_type, self.blob_size)
         self._armed = True
 
-    def zero_grad(self, set_to_none: bool = False) -> None:
-        """Zero the flat gradient buffer; the per-parameter views stay attached."""
-        self._grad.zero_()
-        es = self._grad.element_size()
-        for p, o in zip(self._params, self._offsets):
-            if p.grad is None or p.grad.data_ptr() != self._grad.data_ptr() + o * es:
-                p.grad = self._grad[o:o + p.numel()].view_as(p)
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        """Drop the gradients (autograd then writes fresh tensors, which the fold kernels read
+        in place; no flat gradient buffer and no accumulate kernels are involved)."""
+        for p in self._params:
+            if set_to_none:
+                p.grad = None
+            elif p.grad is not None:
+                p.grad.zero_()
 
     # ---- the step ---------------------------------------------------------------------------------
     def _fold(self, b: _Bucket, lr: float, mu: float) -> torch.Tensor:
-        """Clip per tensor and build the vector that is exchanged for one bucket."""
-        if self.pre_clipnorm is not None:
-            clip = float(self.pre_clipnorm)
-            norms = torch.stack(torch._foreach_norm(b.grad_views)).float()
-            # tf.clip_by_norm: g * clip / max(norm, clip); one small kernel chain for all tensors
-            coefs = (clip / norms.clamp_(min=clip)).to(self._grad.dtype)
-            torch._foreach_mul_(b.grad_views, list(coefs.unbind()))
-        g = self._grad[b.start:b.end]
+        """Clip per tensor and build the vector that is exchanged for one bucket: two launches
+        that read the gradient tensors where autograd left them."""
+        if b.fold is None:
+            b.fold = _FoldTable(self._env, b)
+        ft, ptrs = b.fold, []
+        for p in b.params:
+            g = p.grad
+            if g is None:
+                ptrs.append(self._zeros.data_ptr())
+                continue
+            if g.dtype != self._dtype or not _same_layout(g, p):
+                g = torch.empty_strided(p.size(), p.stride(), dtype=self._dtype, device=p.device).copy_(g)  # rare
+                p.grad = g
+            ptrs.append(g.data_ptr())
+        ft.stage(ptrs)
         u = self._update[b.start:b.end]
-        if self.rule == "sgd" and self.local_momentum:
-            u.mul_(mu * self.momentum_correction).add_(g, alpha=lr)
-            return u
-        if g.dtype == torch.float32:
-            return g
-        u.copy_(g)
+        local = self.rule == "sgd" and self.local_momentum
+        env = self._env
+        _lib.check(env.lib.cx_fold(env.dev, _lib.dtype_code(self._dtype), ft.ptrs.data_ptr(), ft.item_off.data_ptr(),
+                                   ft.item_rel.data_ptr(), ft.item_len.data_ptr(), ft.item_seg.data_ptr(),
+                                   ft.seg_first.data_ptr(), ft.nitems, u.data_ptr(), ft.partial.data_ptr(),
+                                   float(self.pre_clipnorm) if self.pre_clipnorm is not None else 0.0,
+                                   mu * self.momentum_correction if local else 0.0, lr if local else 1.0,
+                                   _lib.stream_ptr(env.device)), "cx_fold")
         return u
 
     def _hyper(self):
@@ -215,10 +297,27 @@ class ComprexOptimizer(torch.optim.Optimizer):
         b.seq, b.par = ar.send_fast(x)
         b.sent = True
 
+    def no_sync(self):
+        """Context for gradient accumulation with ``overlap=True``: backward passes inside it
+        only accumulate; the buckets go out during the first backward pass after it (or in
+        ``step``)."""
+        import contextlib
+
+        @contextlib.contextmanager
+        def ctx():
+            armed, self._armed = self._armed, False
+            try:
+                yield
+            finally:
+                self._armed = armed
+        return ctx()
+
     def _on_grad(self, p) -> None:
+        if not self._armed:
+            return
         b = self._bucket_of[p]
         b.ready += 1
-        if not self._armed or b.ready < len(b.params) or b.sent:
+        if b.ready < len(b.params) or b.sent:
             return
         comm = self._comm_stream()
         comm.wait_stream(torch.cuda.current_stream(self._env.device))

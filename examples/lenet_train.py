@@ -75,7 +75,7 @@ def main():
             with torch.no_grad():
                 acc = float((model(xte).argmax(1) == yte).float().mean())
             if rank == 0:
-                print(f"{kind} ratio {ratio:g} epoch {epoch + 1}: loss {float(loss):.4f} test accuracy {acc:.4f} "
+                print(f"{kind} ratio {ratio:g} epoch {epoch + 1}: loss {loss.item():.4f} test accuracy {acc:.4f} "
                       f"time {time.time() - t0:.1f} s", flush=True)
         env.barrier()
     env.close()

@@ -24,7 +24,7 @@ def _const_grad_model(device, seed=0):
 def _set_grads(opt, params, cs):
     opt.zero_grad()
     for p, c in zip(params, cs):
-        p.grad.add_(c)
+        p.grad = c.clone()
 
 
 @pytest.mark.parametrize("buckets", [None, 0.004])
@@ -54,6 +54,40 @@ def test_sgd_rule_matches_reference_after_flush(device, buckets, local_momentum)
             torch.testing.assert_close(p.detach(), ref, rtol=1e-4, atol=1e-4)
     else:
         assert all(torch.isfinite(p).all() for p in params)
+    env.close()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fold_clips_per_tensor_and_keeps_memory_format(device, dtype):
+    """The fold kernels against clip_by_norm + momentum in plain fp32, on tensors that are
+    larger than one work item, channels-last, unaligned in length, or without a gradient."""
+    env = cx.GaspiEnvironment(8 << 20, device=device)
+    torch.manual_seed(3)
+    conv = torch.randn(96, 24, 3, 3, device=device).to(memory_format=torch.channels_last)
+    shapes = [torch.randn(70001, device=device), conv, torch.randn(7, device=device), torch.randn(33, 5, device=device)]
+    params = [torch.nn.Parameter(t.to(dtype)) for t in shapes]
+    w0 = [p.detach().float().clone() for p in params]
+    lr, mu, clip = 0.05, 0.9, 2.0
+    opt = ComprexOptimizer(params, env, lr=lr, momentum=mu, compression_ratio=1.0, size_factor=1.0, pre_clipnorm=clip)
+    assert params[1].is_contiguous(memory_format=torch.channels_last) and not params[1].is_contiguous()
+    for p, w in zip(params, w0):
+        torch.testing.assert_close(p.detach().float(), w)
+    gs = [(torch.randn_like(p.float()) * s).to(dtype) for p, s in zip(params, (0.001, 1.0, 3.0, 0.2))]
+    gs[1] = gs[1].contiguous(memory_format=torch.channels_last)
+    mom = [torch.zeros_like(w) for w in w0]
+    for step in range(3):
+        opt.zero_grad()
+        for i, (p, g) in enumerate(zip(params, gs)):
+            if not (step == 1 and i == 3):          # one step without a gradient for the last tensor
+                p.grad = g.clone()
+        b = opt._buckets[0]
+        u = opt._fold(b, lr, mu).clone()
+        for i, (g, o) in enumerate(zip(gs, b.offsets[::-1])):
+            gf = g.float() if not (step == 1 and i == 3) else torch.zeros_like(g.float())
+            mom[i] = mu * mom[i] + lr * gf * (clip / max(float(gf.norm()), clip))
+        for p, o, i in zip(b.params, b.offsets, range(len(params) - 1, -1, -1)):
+            got = u[o:o + p.numel()].as_strided(p.size(), p.stride())
+            torch.testing.assert_close(got, mom[i], rtol=2e-5, atol=1e-7)
     env.close()
 
 
