@@ -33,6 +33,7 @@ one device.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -129,11 +130,38 @@ class _AllreduceBase:
         return vector
 
     def apply(self, vector):
-        """In-place allreduce of ``vector``; returns it (allreduce.py:159-166)."""
+        """In-place allreduce of ``vector``; returns it (allreduce.py:159-166).
+
+        Between real ranks the launches of a call depend only on the vector's address and
+        the parity of the step, so they are recorded once as an array of CxOp and replayed
+        with one native call per step.  Virtual ranks (``LoopbackWorld``) run phase by phase."""
         t, orig = self._prep(vector)
-        return self._run(self._plan_apply(t), t, orig, vector)
+        env = self._env
+        if env._world is not None or not self._replay:
+            return self._run(self._plan_apply(t), t, orig, vector)
+        cache = self.__dict__.setdefault("_replay_cache", {})
+        key = (t.data_ptr(), t.dtype, (self._step + 1) & 1)
+        ops = cache.get(key)
+        if ops is None:
+            if len(cache) >= 64:
+                cache.clear()
+            env._rec = rec = []
+            try:
+                for phase in self._plan_apply(t):     # advances the step itself
+                    phase()
+            finally:
+                env._rec = None
+            ops = cache[key] = _OpSeq(env, rec) if rec else False
+        else:
+            self._step += 1
+        if ops:
+            ops.run(self._step)
+        env.maybe_check()
+        write_back(t, orig)
+        return vector
 
     __call__ = apply
+    _replay = True
 
 
 # =====================================================================================
@@ -222,14 +250,32 @@ class RingAllreduce(_AllreduceBase):
 
 
 class BigRingAllreduce(_AllreduceBase):
-    """Every rank receives every other rank's whole vector (src/allreduce.tpp:542-601), one-shot."""
+    """Every rank receives every other rank's whole vector (src/allreduce.tpp:542-601), one-shot.
 
-    def setup_connections(self, size, tag=0, dtype=torch.float32):
+    One-shot moves (P-1) n elements out of every GPU.  Through a switch that gives every
+    pair full bandwidth this is the lowest-latency schedule for small vectors and the
+    wrong one for large vectors, so above ``two_shot_bytes`` (default 8 MiB, environment
+    variable ``COMPREX_TWO_SHOT_BYTES``; never with two ranks, where both schedules move
+    the same bytes) the call runs the reduce-scatter + allgather schedule of
+    ``RingAllreduce``: 2 (P-1)/P n elements, every rank ends with the same bits."""
+
+    def setup_connections(self, size, tag=0, dtype=torch.float32, two_shot_bytes=None):
         self._setup_common(size, dtype)
         env, nb = self._env, size * torch.empty(0, dtype=dtype).element_size()
+        if two_shot_bytes is None:
+            two_shot_bytes = int(os.environ.get("COMPREX_TWO_SHOT_BYTES", 8 << 20))
+        self._two_shot = None
+        if env.ranks > 2 and nb > two_shot_bytes:
+            self._two_shot = RingAllreduce(self.gaspi_env)
+            self._two_shot.setup_connections(size, tag, dtype)
+            return
         self._slots = [[P.DenseSlot.create(env, nb) for _ in range(2)] for _ in range(env.ranks)]
 
     def _plan_apply(self, t):
+        if self._two_shot is not None:
+            self._two_shot._step = self._step          # one step counter: sequence numbers and parity agree
+            self._step += 1
+            return self._two_shot._plan_apply(t)
         env, me, nr = self._env, self._env.rank, self._env.ranks
         self._step += 1
         seq, par = self._step, self._step & 1
@@ -268,6 +314,7 @@ class _ComprexAllreduceBase(_AllreduceBase):
         """Change top-k for later calls.  The ring-specific sampling parameters are
         kept (the reference silently falls back to the defaults here)."""
         self.compression_ratio = float(compression_ratio)
+        self.__dict__.pop("_replay_cache", None)      # the ratio is part of the recorded launches
 
     def reset(self):
         for r in self._residuals():

@@ -91,6 +91,29 @@ def _ptr(t: torch.Tensor | None) -> int:
     return 0 if t is None else t.data_ptr()
 
 
+def _recording(env) -> bool:
+    """True while a launch sequence is being recorded instead of launched (see
+    ``allreduce._AllreduceBase.apply``): the wrappers below then append a CxOp to
+    ``env._rec`` and launch nothing."""
+    return getattr(env, "_rec", None) is not None
+
+
+def _new_op(env, kind: int, dtype: int, n: int):
+    op = _lib.Op()
+    op.kind, op.dev, op.dtype, op.n = kind, env.dev, dtype, n
+    return op
+
+
+def _set_ranges(op, ranges) -> None:
+    if ranges is None:
+        return
+    if len(ranges) > _lib.MAX_PEERS:
+        raise ComprexError("too many ranges")
+    op.has_ranges = 1
+    for i, (a, k) in enumerate(ranges):
+        op.starts[i], op.lens[i] = a, k
+
+
 def _flat(t: torch.Tensor, what: str) -> torch.Tensor:
     if not t.is_contiguous():
         raise ComprexError(f"{what} must be contiguous")
@@ -113,12 +136,20 @@ class Compressor:
         self.stats = env.new_stats()
 
     def set_threshold(self, value: float) -> None:
+        if _recording(self.env):
+            raise ComprexError("a constant threshold cannot be part of a recorded launch sequence")
         self.thr.fill_(float(value))
 
     def threshold_topk(self, g, r, n: int, ratio: float, default_subsamples: int = 1000,
                        subsample_factor: float = 10.0) -> None:
         env = self.env
         gd = _lib.dtype_code(g.dtype) if g is not None else _lib.F32
+        if _recording(env):
+            op = _new_op(env, _lib.OPK_THRESHOLD, gd, n)
+            op.g, op.r, op.thr, op.ratio = _ptr(g), _ptr(r), self.thr.data_ptr(), ratio
+            op.default_subsamples, op.subsample_factor = int(default_subsamples), float(subsample_factor)
+            env._rec.append(op)
+            return
         _lib.check(env.lib.cx_threshold_topk(env.dev, gd, _ptr(g), _ptr(r), n, ratio, int(default_subsamples),
                                              float(subsample_factor), self.thr.data_ptr(),
                                              _lib.stream_ptr(env.device)), "cx_threshold_topk")
@@ -131,6 +162,12 @@ class Compressor:
         gd = _lib.dtype_code(g.dtype) if g is not None else _lib.F32
         if r is not None and r.dtype != torch.float32:
             raise ComprexError("the residual must be float32")
+        if _recording(env):
+            op = _new_op(env, _lib.OPK_COMPRESS, gd, n)
+            op.g, op.r, op.thr, op.cap, op.src_rank = _ptr(g), _ptr(r), self.thr.data_ptr(), cap, env.rank
+            op.workspace, op.ws_bytes, op.stats, op.tg = self.workspace.data_ptr(), self.ws_bytes, self.stats.dev_ptr, targets
+            env._rec.append(op)
+            return
         _lib.check(env.lib.cx_compress(env.dev, gd, _ptr(g), _ptr(r), n, self.thr.data_ptr(), cap, seq,
                                        C.byref(targets), self.workspace.data_ptr(), self.ws_bytes,
                                        self.stats.dev_ptr, env.rank, _lib.stream_ptr(env.device)),
@@ -143,6 +180,11 @@ class Compressor:
 
 
 def apply_sparse(env: GaspiEnvironment, sources: Sources, n: int, args: ApplyArgs, status) -> None:
+    if _recording(env):
+        op = _new_op(env, _lib.OPK_APPLY, _lib.F32, n)
+        op.src, op.apply, op.status, op.timeout_ns = sources, args, status.dev_ptr, env.timeout_ns
+        env._rec.append(op)
+        return
     _lib.check(env.lib.cx_apply(env.dev, C.byref(sources), n, C.byref(args), status.dev_ptr,
                                 env.timeout_ns, _lib.stream_ptr(env.device)), "cx_apply")
 
@@ -192,6 +234,12 @@ def _ranges(ranges):
 
 def dense_send(env: GaspiEnvironment, g: torch.Tensor, r, n: int, seq: int, targets: Targets,
                counters: torch.Tensor, ranges=None) -> None:
+    if _recording(env):
+        op = _new_op(env, _lib.OPK_DENSE_SEND, _lib.dtype_code(g.dtype), n)
+        op.g, op.r, op.tg, op.workspace, op.src_rank = g.data_ptr(), _ptr(r), targets, counters.data_ptr(), env.rank
+        _set_ranges(op, ranges)
+        env._rec.append(op)
+        return
     starts, lens = _ranges(ranges)
     _lib.check(env.lib.cx_dense_send(env.dev, _lib.dtype_code(g.dtype), g.data_ptr(), _ptr(r), n, seq,
                                      C.byref(targets), starts, lens, counters.data_ptr(), env.rank,
@@ -201,6 +249,15 @@ def dense_send(env: GaspiEnvironment, g: torch.Tensor, r, n: int, seq: int, targ
 def dense_reduce(env: GaspiEnvironment, out: torch.Tensor, own, n: int, sources: Sources, status,
                  scale: float = 1.0, push: Targets | None = None, push_seq: int = 0,
                  counters: torch.Tensor | None = None, ranges=None) -> None:
+    if _recording(env):
+        op = _new_op(env, _lib.OPK_DENSE_REDUCE, _lib.dtype_code(out.dtype), n)
+        op.out, op.own, op.src, op.scale = out.data_ptr(), _ptr(own), sources, scale
+        op.workspace, op.src_rank, op.status, op.timeout_ns = _ptr(counters), env.rank, status.dev_ptr, env.timeout_ns
+        if push is not None:
+            op.has_push, op.tg = 1, push
+        _set_ranges(op, ranges)
+        env._rec.append(op)
+        return
     starts, lens = _ranges(ranges)
     _lib.check(env.lib.cx_dense_reduce(env.dev, _lib.dtype_code(out.dtype), out.data_ptr(), _ptr(own), n,
                                        C.byref(sources), scale, C.byref(push) if push is not None else None,

@@ -176,6 +176,47 @@ def scenario_allreduce_variants(rank, world, device):
     return True
 
 
+def scenario_replay_and_two_shot(rank, world, device):
+    """Six calls on one buffer: the launch sequence is recorded twice (one per parity) and
+    replayed afterwards; the large-vector schedule of the dense BigRing gives the same sum."""
+    import comprex_b200 as cx
+    env = cx.GaspiEnvironment(32 << 20, device=device, timeout_ms=20000)
+    n = 30011
+    cases = [(cx.AllToOneAllreduce, dict(chiefRank=world - 1)), (cx.RingAllreduce, {}), (cx.BigRingAllreduce, {}),
+             (cx.BigRingAllreduce, dict(two_shot_bytes=1024))]
+    for cls, kw in cases:
+        ar = cls(env)
+        ar.setup_connections(n, 1, **kw)
+        if "two_shot_bytes" in kw:
+            assert (ar._two_shot is not None) == (world > 2)
+        buf = torch.empty(n, device=device)
+        for step in range(6):
+            vs = [torch.randn(n, generator=torch.Generator().manual_seed(7 * step + r)) for r in range(world)]
+            buf.copy_(vs[rank])
+            ar.apply(buf)
+            assert (buf.double().cpu() - sum(v.double() for v in vs)).abs().max().item() < 1e-5
+        assert len(ar._replay_cache) == 2
+        got = [None] * world
+        dist.all_gather_object(got, buf.cpu())
+        if cls is not cx.BigRingAllreduce or ar._two_shot is not None:   # one-shot sums in arrival order
+            assert all(torch.equal(g, got[0]) for g in got)
+    # compressed ring on one buffer: what was sent plus what is held back adds up after a flush
+    ar = cx.Comprex_RingAllreduce(env)
+    ar.setup_connections(n, 1, compression_ratio=0.05, size_factor=3.0)
+    buf = torch.empty(n, device=device)
+    for step in range(6):
+        buf.fill_(1.0)
+        ar.apply(buf)
+    assert len(ar._replay_cache) == 2
+    ar.set_compression_ratio(0.1)
+    assert "_replay_cache" not in ar.__dict__
+    buf.fill_(1.0)
+    ar.apply(buf)
+    env.barrier()
+    env.close()
+    return True
+
+
 def scenario_missing_sender(rank, world, device):
     """Rank 1 skips its send: rank 0's wait must give up with TIMEOUT, not hang; then recover."""
     import comprex_b200 as cx
@@ -250,6 +291,11 @@ def test_allreduce_variants_cpu_ranks(world):
     run_ranks(world, "scenario_allreduce_variants")
 
 
+@pytest.mark.parametrize("world", [2, 3])
+def test_replay_and_two_shot_cpu_ranks(world):
+    assert all(run_ranks(world, "scenario_replay_and_two_shot"))
+
+
 def test_missing_sender_times_out_cpu():
     assert run_ranks(2, "scenario_missing_sender")[0] is True
 
@@ -272,6 +318,12 @@ def test_config1_two_gpus():
 @pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
 def test_allreduce_variants_gpus():
     run_ranks(min(_gpus(), 4), "scenario_allreduce_variants", backend="nccl")
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_replay_and_two_shot_gpus():
+    assert all(run_ranks(min(_gpus(), 4), "scenario_replay_and_two_shot", backend="nccl"))
 
 
 @pytest.mark.gpu
