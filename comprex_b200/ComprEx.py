@@ -19,7 +19,6 @@ from __future__ import annotations
 
 import ctypes as C
 
-import numpy as np
 import torch
 
 from . import _lib
@@ -173,9 +172,11 @@ class CompressorRLE(_Compressor):
 
     The byte layout follows the reference (``n | nnz | values | nRuns |
     firstIsYes | runs``) but values are stored at their packed position, which
-    the reference's codec gets wrong for thresholds above zero.  The codec runs
-    on the host; engines on a GPU stage the payload through pinned memory, so
-    it is meant for interface parity and tests, not for the training path.
+    the reference's codec gets wrong for thresholds above zero.  Engines use the
+    fused codec of ``csrc/rle.cu`` (count / scan / emit kernels that store the
+    payload straight into the receiver's slot, bounded wait + run check + expand on
+    the other side); ``encode`` / ``decode`` below are the host codec on byte strings,
+    the oracle of the tests.
     """
     kind = "rle"
 
@@ -220,7 +221,8 @@ class Comprex:
         self.send_sizeBytes = bool(send_sizeBytes)
         self.cap = max(int(self.size * 4 * self.size_factor - 8) // 8, 1)
         self._slots = [P.SparseSlot.create(env, self.size, self.cap) for _ in range(self._nslots())]
-        self._dense = None  # CompressorNone / RLE payloads, created on demand
+        self._dense = None  # CompressorNone payloads, created on demand
+        self._rle = None    # CompressorRLE slots and scratch, created on demand
         self._comp = P.Compressor(env, self.size)
         self._counters = env.scratch(64)
         self._status = env.new_status(type(self).__name__)
@@ -243,10 +245,15 @@ class Comprex:
 
     def setCompressor(self, compressor) -> None:
         comp = compressor.get().clone()
-        if comp.kind != "pairs" and self._dense is None:
+        if comp.kind == "none" and self._dense is None:
             from .GaspiEx import GaspiEx
-            # dense / RLE payloads travel through a dense slot big enough for the worst case
-            self._dense = GaspiEx(self._env, 2 * self.size + 8)
+            self._dense = GaspiEx(self._env, self.size)      # dense payloads travel through a dense slot
+            if self._dest is not None:
+                self._dense.connectTx(self._dest)
+            if self._src is not None:
+                self._dense.connectRx(self._src)
+        if comp.kind == "rle" and self._rle is None:
+            self._rle = P.RleCodec(self._env, self.size)     # worst-case sized slots (collective allocation)
         self.compressor = comp
 
     def getSize(self) -> int:
@@ -357,20 +364,16 @@ class Comprex:
                          self._dense._counters)
             self._env.maybe_check()
             return
-        if fixed_thr is None:
-            if isinstance(thr_obj, ThresholdTopK):
-                if r is not None and g is not None:
-                    thr_obj.prepare_with(r, g)
-                else:
-                    thr_obj.prepare(g if g is not None else r)
-            fixed_thr = thr_obj.getThreshold()
-        payload = CompressorRLE.encode(g, r, fixed_thr)
-        # raw bytes ride through the dense slot as 32-bit words (the copy is bit-exact)
-        words = torch.zeros(2 * self.size + 8, dtype=torch.int32)
-        raw = np.frombuffer(payload + b"\0" * (-len(payload) % 4), dtype=np.int32)
-        words[0] = len(payload)
-        words[1:1 + raw.size] = torch.from_numpy(raw.copy())
-        self._dense.writeRemote(words.view(torch.float32).to(self._env.device))
+        if fixed_thr is not None:
+            self._comp.set_threshold(fixed_thr)
+        else:
+            thr_obj._launch(self._comp, g, r, self.size)
+        seq = self._tx_seq.get(self._dest, 0) + 1
+        self._tx_seq[self._dest] = seq
+        if g is not None and g.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+            g = g.to(torch.float32)
+        self._rle.send(g, r, self._comp.thr, seq, self._dest)
+        self._env.maybe_check()
 
     def _send(self, g, r, thr_obj, fixed_thr=None) -> None:
         if self.compressor.kind == "pairs":
@@ -418,11 +421,15 @@ class Comprex:
             else:
                 self._dense.readRemote_vec(t, self.size)
             return
-        words = self._dense.readRemote()
-        self._env.flush()
-        w = words.cpu().view(torch.int32).numpy()
-        payload = w[1:].tobytes()[: int(w[0])]
-        CompressorRLE.decode(payload, t, add)
+        seq = self._rx_seq.get(self._src, 0) + 1
+        self._rx_seq[self._src] = seq
+        if t.dtype == torch.float32:
+            self._rle.recv(t, seq, add, self._status)
+        else:
+            tmp = t.to(torch.float32)
+            self._rle.recv(tmp, seq, add, self._status)
+            t.copy_(tmp)
+        self._env.maybe_check()
 
     def readRemote(self, vector=None):
         """Wait and decompress (overwrite).  Returns a new tensor without ``vector``."""

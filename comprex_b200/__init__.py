@@ -13,5 +13,6 @@ from .ComprEx import (Comprex, FastComprex, ThresholdNone, ThresholdConst, Thres
                       CompressorNone, CompressorRLE, CompressorIndexPairs)
 from .allreduce import (AllToOneAllreduce, RingAllreduce, BigRingAllreduce,  # noqa: F401
                         Comprex_AllToOneAllreduce, Comprex_RingAllreduce, Comprex_BigRingAllreduce)
+from .utils import ComprexConfig  # noqa: F401
 
 __version__ = "0.1.0"

@@ -111,6 +111,10 @@ def _declare(lib) -> None:
         "cx_fill_zero": (i32, [i32, vp, i64, vp]),
         "cx_rle_compress_host": (i64, [vp, vp, i64, f32, vp, i64]),
         "cx_rle_decode_host": (i32, [vp, i64, vp, i64, i32]),
+        "cx_rle_slot_bytes": (i64, [i64]),
+        "cx_rle_workspace_bytes": (i64, [i64]),
+        "cx_rle_send": (i32, [i32, i32, vp, vp, i64, vp, i64, u64, P(Targets), vp, i64, u32, vp]),
+        "cx_rle_recv": (i32, [i32, P(Endpoint), u64, vp, i64, i32, i64, vp, i64, vp, u64, vp]),
         "cx_cuda_device_count": (i32, []),
         "cx_cuda_set_device": (i32, [i32]),
         "cx_cuda_malloc": (vp, [i64]),

@@ -91,6 +91,39 @@ def build(verbose: bool = False, force: bool = False, ptxas_v: bool = False) -> 
     return LIB
 
 
+def build_selftest(sanitizer: str = "address,undefined", verbose: bool = False) -> Path:
+    """Build the host back end together with its self-test under a sanitizer
+    (``address,undefined`` or ``thread``); returns the executable."""
+    OBJDIR.mkdir(exist_ok=True)
+    exe = OBJDIR / ("host_selftest_" + sanitizer.replace(",", "_"))
+    srcs = [CSRC / "selftest" / "host_selftest.cpp", CSRC / "host_ref.cpp"]
+    if not _stale(exe, srcs + list(CSRC.glob("*.h")) + [Path(__file__)]):
+        return exe
+    # not every g++ ships the sanitizer runtimes: take the first one that links
+    tried = []
+    for cxx in dict.fromkeys([os.environ.get("CXX") or "g++", "/usr/bin/g++", "g++", "clang++"]):
+        if not shutil.which(cxx):
+            continue
+        cmd = ([cxx, "-O1", "-g", "-std=c++17", "-ffp-contract=off", "-Wall", "-fno-omit-frame-pointer",
+                f"-fsanitize={sanitizer}", "-fno-sanitize-recover=all"]
+               + [str(x) for x in srcs] + ["-o", str(exe), "-lpthread", "-lrt"])
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode == 0:
+            return exe
+        tried.append(f"{cxx}:\n{res.stdout}\n{res.stderr}")
+    raise RuntimeError("building the self-test failed:\n" + "\n".join(tried))
+
+
 if __name__ == "__main__":
+    if "--selftest" in sys.argv:
+        for san, args in (("address,undefined", []), ("thread", ["--protocol"])):
+            exe = build_selftest(san, verbose=True)
+            print(exe, flush=True)
+            sys.exit_code = subprocess.run([str(exe)] + args).returncode
+            if sys.exit_code:
+                sys.exit(sys.exit_code)
+        sys.exit(0)
     path = build(verbose=True, force="--force" in sys.argv, ptxas_v="--ptxas" in sys.argv)
     print(path)

@@ -204,6 +204,20 @@ int64_t cx_rle_compress_host(const float* g, float* r, int64_t n, float thr,
                              void* out, int64_t out_bytes);
 int cx_rle_decode_host(const void* in, int64_t in_bytes, float* out, int64_t n,
                        int add);
+/* RLE fused with the transfer: the payload (same byte layout as the host codec) is stored
+ * into every target's slot and released with `seq`; the receiver waits (bounded), checks the
+ * runs and expands.  thr points to device memory on CUDA.  slot_bytes is the payload room of
+ * a slot (>= cx_rle_slot_bytes(n)); the workspace (>= cx_rle_workspace_bytes(n), zeroed once)
+ * is rank-local scratch.  A payload that fails a check sets CX_ST_BAD_HEADER and leaves `out`
+ * as it was. */
+int64_t cx_rle_slot_bytes(int64_t n);
+int64_t cx_rle_workspace_bytes(int64_t n);
+int cx_rle_send(int dev, int gdtype, const void* g, float* r, int64_t n, const float* thr,
+                int64_t slot_bytes, uint64_t seq, const CxTargets* tg, void* workspace,
+                int64_t ws_bytes, uint32_t src_rank, void* stream);
+int cx_rle_recv(int dev, const CxEndpoint* src, uint64_t expect_seq, float* out, int64_t n,
+                int add, int64_t slot_bytes, void* workspace, int64_t ws_bytes,
+                uint32_t* status, uint64_t timeout_ns, void* stream);
 
 /* ---- runtime: heaps ---------------------------------------------------- */
 int cx_cuda_device_count(void);

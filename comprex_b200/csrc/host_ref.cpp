@@ -20,9 +20,23 @@
 #include "cx_common.h"
 
 int cx_set_error(const char* where, int cuda_err);
+// The float arithmetic below is the reference's (src/threshold.hxx:182-205); both back ends
+// take the sample count, the stride and the rank from it.
 extern "C" void cx_threshold_plan(int64_t n, float ratio, int default_subsamples,
                                   float subsample_factor, int32_t* samples, int32_t* use_all,
-                                  float* stepsize, int32_t* topk_pos);
+                                  float* stepsize, int32_t* topk_pos) {
+  int subs = default_subsamples;
+  if (ratio > 0.f) {
+    const float req = subsample_factor / ratio;
+    if (req > (float)default_subsamples) subs = req >= 2147483520.f ? 2147483520 : (int)req;
+  }
+  if (subs < 1) subs = 1;
+  int64_t size;
+  if (n < subs) { size = n; *use_all = 1; *stepsize = 1.f; }
+  else { size = subs; *use_all = 0; *stepsize = (float)n / (float)subs; }
+  *samples = (int32_t)size;
+  *topk_pos = (int32_t)(ceilf((float)size * ratio) - 1);
+}
 
 namespace {
 
@@ -416,10 +430,11 @@ extern "C" int64_t cx_rle_compress_host(const float* g, float* r, int64_t n, flo
   char* p = reinterpret_cast<char*>(out);
   const int32_t hdr[2] = {(int32_t)n, (int32_t)vals.size()};
   memcpy(p, hdr, 8); p += 8;
-  memcpy(p, vals.data(), 4 * vals.size()); p += 4 * vals.size();
+  if (!vals.empty()) memcpy(p, vals.data(), 4 * vals.size());
+  p += 4 * vals.size();
   const int32_t rh[2] = {(int32_t)runs.size(), first_yes};
   memcpy(p, rh, 8); p += 8;
-  memcpy(p, runs.data(), 4 * runs.size());
+  if (!runs.empty()) memcpy(p, runs.data(), 4 * runs.size());
   return need;
 }
 
@@ -449,6 +464,72 @@ extern "C" int cx_rle_decode_host(const void* in, int64_t in_bytes, float* out, 
     yes = !yes;
   }
   if (i != n) return cx_set_error("cx_rle_decode: runs do not cover the vector", 0);
+  return 0;
+}
+
+// RLE through a slot: the sender encodes and stores into every target, the receiver waits,
+// checks and decodes from its own slot (same protocol as the kernels in rle.cu).
+int cx_rle_send_host(int gdtype, const void* g, float* r, int64_t n, const float* thr,
+                     int64_t slot_bytes, uint64_t seq, const CxTargets* tg, uint32_t src_rank) {
+  if (!g && !r) return cx_set_error("cx_rle_send: g and r are both NULL", 0);
+  if (g && !dtype_ok(gdtype)) return cx_set_error("cx_rle_send: unsupported dtype", 0);
+  if (slot_bytes < 16 + 8 * n) return cx_set_error("cx_rle_send: slot smaller than the worst case", 0);
+  std::vector<float> gf;
+  const float* gp = reinterpret_cast<const float*>(g);
+  if (g && gdtype != CX_F32) {
+    gf.resize((size_t)n);
+    for (int64_t i = 0; i < n; ++i) gf[(size_t)i] = load_elem(gdtype, g, i);
+    gp = gf.data();
+  }
+  std::vector<char> buf((size_t)(16 + 8 * n));
+  const int64_t used = cx_rle_compress_host(gp, r, n, *thr, buf.data(), (int64_t)buf.size());
+  if (used < 0) return 1;
+  int32_t nnz;
+  memcpy(&nnz, buf.data() + 4, 4);
+  for (int k = 0; k < tg->count; ++k) {
+    memcpy(tg->ep[k].pairs, buf.data(), (size_t)used);
+    CxHeader* h = tg->ep[k].hdr;
+    h->bytes = (uint64_t)used; h->n = (uint32_t)n; h->nnz = (uint32_t)nnz; h->nnz_found = (uint32_t)nnz;
+    h->kind = CX_KIND_RLE; h->threshold = *thr; h->nsub = 0; h->src_rank = src_rank; h->dtype = CX_F32;
+    publish(h, seq);
+  }
+  return 0;
+}
+
+int cx_rle_recv_host(const CxEndpoint* src, uint64_t expect_seq, float* out, int64_t n, int add,
+                     int64_t slot_bytes, uint32_t* status, uint64_t timeout_ns) {
+  uint32_t bad = 0;
+  if (!wait_seq(src->hdr, expect_seq, timeout_ns)) bad = CX_ST_TIMEOUT;
+  else if (src->hdr->kind != CX_KIND_RLE || (int64_t)src->hdr->n != n ||
+           (int64_t)src->hdr->bytes > slot_bytes || src->hdr->bytes < 16) bad = CX_ST_BAD_HEADER;
+  if (!bad) {
+    // check the runs before anything is written: a corrupt payload leaves `out` untouched
+    const char* p = reinterpret_cast<const char*>(src->pairs);
+    const int64_t bytes = (int64_t)src->hdr->bytes;
+    int32_t hdr[2], rh[2] = {0, 0};
+    memcpy(hdr, p, 8);
+    const int64_t nnz = hdr[1];
+    bool ok = hdr[0] == n && nnz >= 0 && 16 + 4 * nnz <= bytes;
+    if (ok) {
+      memcpy(rh, p + 8 + 4 * nnz, 8);
+      ok = rh[0] >= 0 && 16 + 4 * nnz + 4 * (int64_t)rh[0] <= bytes;
+    }
+    if (ok) {
+      const int32_t* runs = reinterpret_cast<const int32_t*>(p + 16 + 4 * nnz);
+      int64_t total = 0, ytotal = 0;
+      bool yes = rh[1] != 0;
+      for (int32_t q = 0; q < rh[0] && ok; ++q, yes = !yes) {
+        if (runs[q] < 0) ok = false;
+        total += runs[q];
+        if (yes) ytotal += runs[q];
+        if (total > n) ok = false;
+      }
+      ok = ok && total == n && ytotal == nnz;
+    }
+    if (!ok) bad = CX_ST_BAD_HEADER;
+    else if (cx_rle_decode_host(p, bytes, out, n, add)) bad = CX_ST_BAD_HEADER;
+  }
+  if (bad && status) *status |= bad;
   return 0;
 }
 

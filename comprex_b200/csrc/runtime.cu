@@ -41,6 +41,13 @@ int cx_dense_reduce_cuda(int, void*, const void*, int64_t, const CxSources*, flo
 int cx_dense_reduce_host(int, void*, const void*, int64_t, const CxSources*, float, const CxTargets*,
                          uint64_t, const int64_t*, const int64_t*, uint32_t, uint32_t*, uint64_t);
 int cx_axpy_cuda(int, void*, int, const void*, float, int64_t, void*);
+int cx_rle_send_cuda(int, const void*, float*, int64_t, const float*, int64_t, uint64_t, const CxTargets*,
+                     void*, int64_t, uint32_t, void*);
+int cx_rle_send_host(int, const void*, float*, int64_t, const float*, int64_t, uint64_t, const CxTargets*,
+                     uint32_t);
+int cx_rle_recv_cuda(const CxEndpoint*, uint64_t, float*, int64_t, int, int64_t, void*, int64_t, uint32_t*,
+                     uint64_t, void*);
+int cx_rle_recv_host(const CxEndpoint*, uint64_t, float*, int64_t, int, int64_t, uint32_t*, uint64_t);
 int cx_fold_cuda(int, const void* const*, const int64_t*, const int64_t*, const int32_t*, const int32_t*,
                  const int32_t*, int, float*, float*, float, float, float, void*);
 int cx_fold_host(int, const void* const*, const int64_t*, const int64_t*, const int32_t*, const int32_t*,
@@ -144,6 +151,23 @@ int cx_fold(int dev, int gdtype, const void* const* seg_ptr, const int64_t* item
                             partial, clip, mu, lr, stream)
              : cx_fold_host(gdtype, seg_ptr, item_off, item_rel, item_len, item_seg, seg_first, nitems, u,
                             partial, clip, mu, lr);
+}
+
+int cx_rle_send(int dev, int gdtype, const void* g, float* r, int64_t n, const float* thr,
+                int64_t slot_bytes, uint64_t seq, const CxTargets* tg, void* workspace,
+                int64_t ws_bytes, uint32_t src_rank, void* stream) {
+  return dev == CX_DEV_CUDA
+             ? cx_rle_send_cuda(gdtype, g, r, n, thr, slot_bytes, seq, tg, workspace, ws_bytes, src_rank, stream)
+             : cx_rle_send_host(gdtype, g, r, n, thr, slot_bytes, seq, tg, src_rank);
+}
+
+int cx_rle_recv(int dev, const CxEndpoint* src, uint64_t expect_seq, float* out, int64_t n, int add,
+                int64_t slot_bytes, void* workspace, int64_t ws_bytes, uint32_t* status,
+                uint64_t timeout_ns, void* stream) {
+  return dev == CX_DEV_CUDA
+             ? cx_rle_recv_cuda(src, expect_seq, out, n, add, slot_bytes, workspace, ws_bytes, status,
+                                timeout_ns, stream)
+             : cx_rle_recv_host(src, expect_seq, out, n, add, slot_bytes, status, timeout_ns);
 }
 
 /* struct sizes, so that the binding can verify its mirror of the layouts at load time */

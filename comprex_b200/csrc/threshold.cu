@@ -125,21 +125,10 @@ __global__ void __launch_bounds__(kThreads) threshold_kernel(const ThreshParams 
 }  // namespace
 
 // Host-side part of the rule, in the reference's float arithmetic.
+// sample count, stride and rank of the estimate (defined with the host back end)
 extern "C" void cx_threshold_plan(int64_t n, float ratio, int default_subsamples,
                                   float subsample_factor, int32_t* samples, int32_t* use_all,
-                                  float* stepsize, int32_t* topk_pos) {
-  int subs = default_subsamples;
-  if (ratio > 0.f) {
-    const float req = subsample_factor / ratio;
-    if (req > (float)default_subsamples) subs = req >= 2147483520.f ? 2147483520 : (int)req;
-  }
-  if (subs < 1) subs = 1;
-  int64_t size;
-  if (n < subs) { size = n; *use_all = 1; *stepsize = 1.f; }
-  else { size = subs; *use_all = 0; *stepsize = (float)n / (float)subs; }
-  *samples = (int32_t)size;
-  *topk_pos = (int32_t)(ceilf((float)size * ratio) - 1);
-}
+                                  float* stepsize, int32_t* topk_pos);
 
 int cx_threshold_topk_cuda(int gdtype, const void* g, const float* r, int64_t n, float ratio,
                            int default_subsamples, float subsample_factor, float* thr_out,

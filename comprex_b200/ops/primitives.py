@@ -179,6 +179,38 @@ class Compressor:
         return self.stats.read()
 
 
+class RleCodec:
+    """Slots and scratch of one run-length coded connection (csrc/rle.cu): two receive slots
+    sized for the worst case (collective allocation) plus one workspace per direction."""
+
+    def __init__(self, env: GaspiEnvironment, n: int):
+        self.env, self.n = env, n
+        self.slot_bytes = int(env.lib.cx_rle_slot_bytes(n))
+        self.ws_bytes = int(env.lib.cx_rle_workspace_bytes(n))
+        self.slots = [DenseSlot.create(env, self.slot_bytes) for _ in range(2)]
+        self.tx_ws = env.scratch(self.ws_bytes)
+        self.rx_ws = env.scratch(self.ws_bytes)
+
+    def send(self, g, r, thr_cell: torch.Tensor, seq: int, dest: int) -> None:
+        """Encode ``r + g`` at the threshold in ``thr_cell`` into rank ``dest``'s slot."""
+        env = self.env
+        gd = _lib.dtype_code(g.dtype) if g is not None else _lib.F32
+        tg = make_targets([self.slots[seq & 1].endpoint(env, dest)])
+        _lib.check(env.lib.cx_rle_send(env.dev, gd, _ptr(g), _ptr(r), self.n, thr_cell.data_ptr(), self.slot_bytes,
+                                       seq, C.byref(tg), self.tx_ws.data_ptr(), self.ws_bytes, env.rank,
+                                       _lib.stream_ptr(env.device)), "cx_rle_send")
+
+    def recv(self, out: torch.Tensor, seq: int, add: bool, status) -> None:
+        """Wait for payload ``seq`` in the local slot and expand it into the float32 ``out``."""
+        env = self.env
+        if out.dtype != torch.float32 or out.numel() != self.n:
+            raise ComprexError("RLE decode needs a float32 vector of the connection's size")
+        ep = self.slots[seq & 1].endpoint(env)
+        _lib.check(env.lib.cx_rle_recv(env.dev, C.byref(ep), seq, out.data_ptr(), self.n, int(add), self.slot_bytes,
+                                       self.rx_ws.data_ptr(), self.ws_bytes, status.dev_ptr, env.timeout_ns,
+                                       _lib.stream_ptr(env.device)), "cx_rle_recv")
+
+
 def apply_sparse(env: GaspiEnvironment, sources: Sources, n: int, args: ApplyArgs, status) -> None:
     if _recording(env):
         op = _new_op(env, _lib.OPK_APPLY, _lib.F32, n)

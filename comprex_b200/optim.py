@@ -41,6 +41,7 @@ import torch
 from . import _lib, allreduce as _ar
 from ._lib import ComprexError
 from .ops import primitives as P
+from .utils.trace import nvtx_range
 
 _TYPES = {
     "alltoone": _ar.AllToOneAllreduce, "comprex_alltoone": _ar.Comprex_AllToOneAllreduce,
@@ -292,9 +293,9 @@ class ComprexOptimizer(torch.optim.Optimizer):
 
     def _send(self, b: _Bucket) -> None:
         lr, mu, _ = self._hyper()
-        x = self._fold(b, lr, mu)
-        ar = b.ar
-        b.seq, b.par = ar.send_fast(x)
+        with nvtx_range("comprex.fold+send"):
+            x = self._fold(b, lr, mu)
+            b.seq, b.par = b.ar.send_fast(x)
         b.sent = True
 
     def no_sync(self):
@@ -363,7 +364,8 @@ class ComprexOptimizer(torch.optim.Optimizer):
                 if not b.sent:
                     self._send(b)
             for b in self._buckets:          # then receive: all peers' payloads are on their way
-                b.ar.recv_fast(b.seq, b.par, self._recv_args(b, lr, mu, wd))
+                with nvtx_range("comprex.recv+update"):
+                    b.ar.recv_fast(b.seq, b.par, self._recv_args(b, lr, mu, wd))
                 b.sent, b.ready = False, 0
         if use_side:
             torch.cuda.current_stream(self._env.device).wait_stream(comm)

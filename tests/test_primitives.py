@@ -360,6 +360,79 @@ def test_rle_roundtrip_and_residual():
     assert torch.equal(out, x)
 
 
+@pytest.mark.parametrize("n", [1, 7, 2047, 2048, 2049, 4096, 10007, 70001])
+@pytest.mark.parametrize("thr,density", [(0.0, 0.25), (0.8, 1.0), (3.5, 1.0), (100.0, 1.0)])
+def test_rle_fused_codec_matches_host_bytes(world, n, thr, density):
+    """Fused RLE send/receive (kernels on a GPU, host twin on the CPU): the bytes that land in
+    the receiver's slot equal the host codec's payload, the expansion equals the plain
+    restatement, the residual keeps what was not sent, and `add` accumulates."""
+    e0, e1 = world.envs
+    codecs = [P.RleCodec(e, n) for e in world.envs]
+    torch.manual_seed(n)
+    g = torch.randn(n) * (torch.rand(n) < density)
+    r0 = 0.3 * torch.randn(n) * (torch.rand(n) < density)
+    cell = torch.full((1,), thr, dtype=torch.float32, device=e0.device)
+    gd, r = g.to(e0.device), r0.clone().to(e0.device)
+    codecs[0].send(gd, r, cell, 1, 1)
+    status = e1.new_status("t")
+    out = torch.full((n,), 9.0, device=e1.device)
+    codecs[1].recv(out, 1, False, status)
+    e1.flush()
+    assert status.value == 0
+    v = g + r0
+    keep = (v.abs() >= thr) & ~((thr == 0.0) & (v == 0))
+    assert torch.equal(out.cpu(), torch.where(keep, v, torch.zeros(n)))
+    assert torch.equal(r.cpu(), torch.where(keep, torch.zeros(n), v))
+    rh = r0.clone()
+    expect = cx.CompressorRLE.encode(g, rh, thr)
+    ep = codecs[1].slots[1].endpoint(e1)
+    hdr = e1.read_header(ep.hdr)
+    assert (hdr.kind, hdr.n, hdr.bytes, hdr.nnz) == (_lib.KIND_RLE, n, len(expect), int(keep.sum()))
+    assert e1.read_bytes(ep.pairs, len(expect)) == expect
+    # second payload (other parity) accumulated on top
+    codecs[0].send(None, r, cell.zero_(), 2, 1)            # flush of the residual at threshold 0
+    acc = torch.ones(n, device=e1.device)
+    codecs[1].recv(acc, 2, True, status)
+    e1.flush()
+    assert status.value == 0
+    assert torch.equal(acc.cpu(), 1 + torch.where(keep, torch.zeros(n), v))
+    assert float(r.abs().sum()) == 0.0
+
+
+def test_rle_fused_receive_rejects_corrupt_runs(world):
+    """Host-side fault injection: run lengths that do not add up to n set BAD_HEADER and leave
+    the output untouched; a payload that never arrives times out with a status."""
+    e0, e1 = world.envs
+    n = 5000
+    codecs = [P.RleCodec(e, n) for e in world.envs]
+    g = torch.randn(n, generator=torch.Generator().manual_seed(0))
+    cell = torch.full((1,), 1.0, dtype=torch.float32, device=e0.device)
+    codecs[0].send(g.to(e0.device), None, cell, 1, 1)
+    e0.flush()
+    ep = codecs[1].slots[1].endpoint(e1)
+    hdr = e1.read_header(ep.hdr)
+    raw = bytearray(e1.read_bytes(ep.pairs, hdr.bytes))
+    runs_at = 16 + 4 * hdr.nnz
+    first = int.from_bytes(raw[runs_at:runs_at + 4], "little")
+    raw[runs_at:runs_at + 4] = (first + 1).to_bytes(4, "little")       # one element too many
+    t = torch.frombuffer(raw, dtype=torch.uint8)
+    if e1.dev == _lib.DEV_CUDA:
+        _lib.check(e1.lib.cx_cuda_memcpy(ep.pairs, t.data_ptr(), len(raw), 1, None), "memcpy")
+    else:
+        C.memmove(ep.pairs, t.data_ptr(), len(raw))
+    status = e1.new_status("t")
+    out = torch.full((n,), 9.0, device=e1.device)
+    codecs[1].recv(out, 1, False, status)
+    with pytest.raises(cx.ComprexError, match="BAD_HEADER"):
+        e1.flush()
+    assert torch.equal(out.cpu(), torch.full((n,), 9.0))
+    status2 = e1.new_status("t2")
+    codecs[1].recv(out, 2, False, status2)                 # nobody sent payload 2
+    with pytest.raises(cx.ComprexError, match="TIMEOUT"):
+        e1.flush()
+    assert torch.equal(out.cpu(), torch.full((n,), 9.0))
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("n", [1000, 4096, 100003, (1 << 22) + 5])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
