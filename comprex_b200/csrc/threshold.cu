@@ -10,7 +10,16 @@
 // and a 4-pass 8-bit radix select over one CTA finds the element of that rank.
 // The result stays in device memory, where the compress kernel reads it, so
 // no host round trip sits between the two.
+//
+// Gathering the sample is the expensive part for small top-k fractions (10 000
+// strided elements at 0.1 %: 20 000 separate 32-byte sectors, more than one SM's
+// load path moves in the time the rest of the kernel takes).  Above 2048 samples the
+// kernel therefore runs as a thread-block cluster of 8 CTAs: every CTA gathers one
+// eighth of the sample and stores the keys through distributed shared memory into
+// the first CTA, which then selects alone.
+#include <cooperative_groups.h>
 #include <math.h>
+#include <string.h>
 
 #include "cx_device.cuh"
 
@@ -45,33 +54,65 @@ __device__ __forceinline__ uint32_t sample_key(const ThreshParams& p, int i) {
   return __float_as_uint(fabsf(x));
 }
 
+constexpr int kGather = 4;  // loads of one thread that are in flight together
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads) threshold_kernel(const ThreshParams p) {
+  namespace cg = cooperative_groups;
   __shared__ uint32_t s_keys[kSmemKeys];
   __shared__ uint32_t s_hist[256];
   __shared__ uint32_t s_sel[2];  // chosen digit, remaining rank
   __shared__ uint32_t s_red[kThreads / 32];
+  __shared__ uint32_t s_cmax[8];  // per-CTA maxima of a cluster launch (first CTA's copy is used)
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int s = p.samples;
   const bool cached = s <= kSmemKeys;
   const int s_round = (s + kThreads - 1) / kThreads * kThreads;
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned ncta = cluster.num_blocks();      // 1 unless launched as a cluster (only when cached)
+  const unsigned crank = cluster.block_rank();
+  uint32_t* keys0 = ncta > 1 ? cluster.map_shared_rank(s_keys, 0) : s_keys;
 
-  // pass 0: gather the sample (and its maximum, for the sentinel case)
+  // pass 0: gather the sample (and its maximum, for the sentinel case); CTA c of a cluster
+  // takes the samples [c, c+1) * s / ncta
+  const int lo = (int)((int64_t)s * crank / ncta), hi = (int)((int64_t)s * (crank + 1) / ncta);
   uint32_t mx = 0;
-  for (int i = tid; i < s; i += kThreads) {
-    const uint32_t k = sample_key<T>(p, i);
-    if (cached) s_keys[i] = k;
-    mx = max(mx, k);
+  for (int i0 = lo + tid; i0 < hi; i0 += kGather * kThreads) {
+    uint32_t k[kGather];
+#pragma unroll
+    for (int u = 0; u < kGather; ++u) {
+      const int i = i0 + u * kThreads;
+      k[u] = i < hi ? sample_key<T>(p, i) : 0u;
+    }
+#pragma unroll
+    for (int u = 0; u < kGather; ++u) {
+      const int i = i0 + u * kThreads;
+      if (i < hi) {
+        if (cached) keys0[i] = k[u];
+        mx = max(mx, k[u]);
+      }
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+  if (lane == 0) s_red[tid >> 5] = mx;
+  __syncthreads();
+  if (tid == 0) {
+    uint32_t m = 0;
+    for (int w = 0; w < kThreads / 32; ++w) m = max(m, s_red[w]);
+    (ncta > 1 ? cluster.map_shared_rank(s_cmax, 0) : s_cmax)[crank] = m;
+  }
+  if (ncta > 1) {
+    cluster.sync();              // keys and maxima of all CTAs are in the first CTA's shared memory
+    if (crank != 0) return;      // (no CTA touches another CTA's shared memory after this point)
+  } else {
+    __syncthreads();
   }
   if (p.topk_pos <= 0) {
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, d));
-    if (lane == 0) s_red[tid >> 5] = mx;
-    __syncthreads();
     if (tid == 0) {
       uint32_t m = 0;
-      for (int w = 0; w < kThreads / 32; ++w) m = max(m, s_red[w]);
+      for (unsigned c = 0; c < ncta; ++c) m = max(m, s_cmax[c]);
       *p.thr_out = __uint_as_float(m) + 1.0f;
     }
     return;
@@ -140,12 +181,28 @@ int cx_threshold_topk_cuda(int gdtype, const void* g, const float* r, int64_t n,
                     &p.stepsize, &p.topk_pos);
   if (n <= 0) { p.samples = 0; p.topk_pos = 0; }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // a cluster of 8 CTAs gathers large samples (their keys must fit the first CTA's shared memory)
+  const unsigned ncta = (p.samples > 2048 && p.samples <= kSmemKeys) ? 8u : 1u;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(ncta, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = ncta;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e;
   switch (gdtype) {
-    case CX_F32: threshold_kernel<float><<<1, kThreads, 0, s>>>(p); break;
-    case CX_BF16: threshold_kernel<__nv_bfloat16><<<1, kThreads, 0, s>>>(p); break;
-    case CX_F16: threshold_kernel<__half><<<1, kThreads, 0, s>>>(p); break;
+    case CX_F32: e = cudaLaunchKernelEx(&cfg, threshold_kernel<float>, p); break;
+    case CX_BF16: e = cudaLaunchKernelEx(&cfg, threshold_kernel<__nv_bfloat16>, p); break;
+    case CX_F16: e = cudaLaunchKernelEx(&cfg, threshold_kernel<__half>, p); break;
     default: return cx_set_error("cx_threshold_topk: unsupported dtype on CUDA", 0);
   }
+  if (e != cudaSuccess) return cx_set_error("threshold_kernel launch", (int)e);
   cx_note_launch();
   return cx_check_launch("threshold_kernel");
 }

@@ -95,14 +95,18 @@ class StatusWord:
 
 
 class StatsBlock:
-    """CxStats of the last compress call of one compressor."""
+    """CxStats of the last compress call of one compressor.
 
-    def __init__(self, host_ptr: int, dev_ptr: int):
-        self.dev_ptr = dev_ptr
-        self._view = C.cast(host_ptr, C.POINTER(_lib.Stats))
+    The block lives in the memory of the device that runs the kernel (a write to mapped host
+    memory would put a PCIe round trip on the tail of every compress launch); ``read`` copies
+    it to the host."""
+
+    def __init__(self, device):
+        self._t = torch.zeros(C.sizeof(_lib.Stats), dtype=torch.uint8, device=device)
+        self.dev_ptr = self._t.data_ptr()
 
     def read(self) -> dict:
-        s = self._view[0]
+        s = _lib.Stats.from_buffer_copy(bytes(self._t.cpu().numpy().tobytes()))
         return {"n": int(s.n), "nnz": int(s.nnz), "nnz_found": int(s.nnz_found),
                 "status": int(s.status), "threshold": float(s.threshold)}
 
@@ -210,8 +214,7 @@ class GaspiEnvironment:
         return word
 
     def new_stats(self) -> StatsBlock:
-        host, dev = self._pinned_take(C.sizeof(_lib.Stats))
-        return StatsBlock(host, dev)
+        return StatsBlock(self.device)
 
     def check(self) -> None:
         """Turn status bits that kernels left behind into an exception."""
