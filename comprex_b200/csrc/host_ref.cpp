@@ -281,11 +281,14 @@ int cx_apply_host(const CxSources* src, int64_t n, const CxApplyArgs* a, uint32_
         a->m[i] = mv;
         wv = (1.f - a->wd) * wv - mv;
       } else {
-        const float mv = a->beta1 * a->m[i] + (1.f - a->beta1) * g;
-        const float vv = a->beta2 * a->v[i] + (1.f - a->beta2) * g * g;
+        // same operation order as the kernel (fused multiply-adds in the same places); the
+        // kernel's square root and reciprocal are the hardware approximations, so w agrees
+        // to a few ulp of the step, m and v bit for bit
+        const float mv = fmaf(a->beta1, a->m[i], (1.f - a->beta1) * g);
+        const float vv = fmaf(a->beta2, a->v[i], ((1.f - a->beta2) * g) * g);
         a->m[i] = mv; a->v[i] = vv;
         const float mh = mv * (1.f / a->bc1), vh = vv * (1.f / a->bc2);
-        wv = wv * (1.f - a->lr * a->wd) - a->lr * mh * (1.f / (sqrtf(vh) + a->eps));
+        wv = fmaf(-(a->lr * mh), 1.f / (sqrtf(vh) + a->eps), wv * (1.f - a->lr * a->wd));
       }
       w[i] = wv;
       if (a->shadow) store_elem(sdt, a->shadow, i, wv);
