@@ -4,7 +4,7 @@ For every (n, ratio, dtype) it times, with CUDA events on the launching stream
 after warm-up and with an L2 flush between iterations:
 
 * ``threshold``  - sampled top-k threshold estimate,
-* ``compress``   - fused residual add / select / ordered compaction / store into
+* ``compress``   - fused residual add / select / per-sub-tile compaction / store into
                    ``--targets`` slots (local memory stands in for peers),
 * ``apply_add``  - wait + scatter-add of ``--sources`` payloads,
 * ``apply_sgd`` / ``apply_adamw`` - the same fused with the parameter update.
@@ -14,6 +14,9 @@ target); apply reads the pairs and touches one 32-byte sector per pair (sparse
 ops) or reads/writes the dense state once (dense ops).  Fractions are "of
 measured": the copy bandwidth in MEASURED_PEAKS.json at the repository root
 when present (6.65 TB/s otherwise, "of fallback").
+
+Below about 2^24 elements the figures are bound by the host's launch path (one ctypes
+call per timed launch), not by the kernels.
 
     python bench/kernel_bench.py --out results/kernel_bench.jsonl
 """
