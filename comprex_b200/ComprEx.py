@@ -22,6 +22,7 @@ import ctypes as C
 import torch
 
 from . import _lib
+from .common import AbstractExchange
 from ._lib import ComprexError
 from .GaspiEx import to_device_vector, write_back
 from .ops import primitives as P
@@ -206,7 +207,7 @@ class CompressorRLE(_Compressor):
 # ---------------------------------------------------------------------------------
 # ComprEx
 # ---------------------------------------------------------------------------------
-class Comprex:
+class Comprex(AbstractExchange):
     """Compressed exchange with residual; mirrors ``ComprEx<T>`` and its Python class.
 
     ``size_factor`` sizes the receive slot like the reference does

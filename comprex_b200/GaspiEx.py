@@ -19,6 +19,7 @@ import numpy as np
 import torch
 
 from . import _lib
+from .common import AbstractExchange
 from ._lib import ComprexError
 from .ops import primitives as P
 
@@ -44,7 +45,7 @@ def write_back(t: torch.Tensor, original) -> None:
         np.copyto(original.reshape(-1), t.detach().cpu().numpy().astype(original.dtype, copy=False))
 
 
-class GaspiEx:
+class GaspiEx(AbstractExchange):
     def __init__(self, gaspi_env, size: int, dtype: torch.dtype = torch.float32):
         self._env = env = gaspi_env.get()
         self.size = int(size)

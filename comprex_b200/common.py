@@ -23,3 +23,28 @@ class Subscribable:
     def unsubscribe(self, obj) -> None:
         if obj in self._subscribers:
             self._subscribers.remove(obj)
+
+
+class AbstractExchange:
+    """Interface of the point-to-point engines (src/AbstractExchange.hxx:7-23): what
+    ``GaspiEx`` and ``Comprex`` / ``FastComprex`` have in common, so that code can be written
+    against either."""
+
+    def writeRemote(self, vector):
+        raise NotImplementedError
+
+    def readRemote(self, vector=None):
+        raise NotImplementedError
+
+    def readRemote_add(self, vector):
+        raise NotImplementedError
+
+    def connectTx(self, targRank: int, tag: int = 0):
+        raise NotImplementedError
+
+    def connectRx(self, srcRank: int, tag: int = 0):
+        raise NotImplementedError
+
+    def connectTo(self, srcRank: int, targRank: int, tag: int = 0):
+        """srcRank: receive from this rank; targRank: send to this rank."""
+        raise NotImplementedError
