@@ -41,7 +41,9 @@ def hbm_gbs():
         return 6650.0, "fallback"
 
 
-def time_op(fn, reps, warmup, flush, dev):
+def time_op(fn, reps, warmup, flush, dev, after=None, samples=None):
+    """Median and minimum over the repetitions of the MAX over ranks; ``after`` runs outside the
+    timed region of every repetition, ``samples`` receives the individual times."""
     out = []
     for i in range(warmup + reps):
         if flush is not None:
@@ -55,8 +57,12 @@ def time_op(fn, reps, warmup, flush, dev):
         torch.cuda.synchronize(dev)
         t = torch.tensor([a.elapsed_time(b) * 1e3], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if after is not None and i >= warmup:
+            after()
         if i >= warmup:
             out.append(float(t.item()))
+    if samples is not None:
+        samples.extend(out)
     return statistics.median(out), min(out)
 
 
@@ -73,6 +79,9 @@ def main():
                     help="largest size for the schedules that hold P full-size slots (dense BigRing, AllToOne)")
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--csv", default=None,
+                    help="also write the reference benchmark's table (examples/allreduce_speed.cpp:182-184): "
+                         "variant;size(MB);compression;time_mean(us);time_stddev(us);sparsity_mean;sparsity_stddev")
     args = ap.parse_args()
 
     cx.initGaspiCxx("nccl")
@@ -87,7 +96,7 @@ def main():
     def emit(row):
         rows.append(row)
         if rank == 0:
-            print(json.dumps(row), flush=True)
+            print(json.dumps({k: v for k, v in row.items() if k != "csv"}), flush=True)
 
     for lg in args.log2_sizes:
         n = 1 << lg
@@ -131,7 +140,10 @@ def main():
 
                     def copy_only():
                         buf.copy_(x)
-                    med, best = time_op(run, args.reps, args.warmup, flush, dev)
+                    times, sparsity = [], []
+                    med, best = time_op(run, args.reps, args.warmup, flush, dev, samples=times,
+                                        after=(lambda: sparsity.append(float((buf == 0).float().mean()))) if args.csv else None)
+                    res_sparsity = round(float((buf == 0).float().mean()), 4)   # of the last result
                     cmed, _ = time_op(copy_only, 3, 1, flush, dev)   # the input reset is not part of the allreduce
                     med, best = max(med - cmed, 0.01), max(best - cmed, 0.01)
                     env.flush()
@@ -142,18 +154,32 @@ def main():
                         st = ar.stats()
                         row["sent_fraction"] = round(st["nnz"] / max(st["n"], 1), 5)
                         row["overflow"] = bool(st["status"] & 4)
-                        row["result_sparsity"] = round(float((buf == 0).float().mean()), 4)
+                        row["result_sparsity"] = res_sparsity
                         if variant == "comprex_bigring":
                             hbm_b = 12.0 * n
                             link_b = (world - 1) * (8.0 * st["nnz"] + 8.0 * n / 1024)
                             roof_us = max(hbm_b / (peak * 1e3), link_b / (NVLINK_GBS * 1e3))
                             row["roofline_us"] = round(roof_us, 2)
                             row["frac_of_roofline_" + how] = round(roof_us / med, 3)
+                    if args.csv:
+                        ts = [max(t - cmed, 0.01) for t in times]
+                        row["csv"] = (variant, n * x.element_size() / 1e6, ratio, statistics.mean(ts),
+                                      statistics.pstdev(ts), statistics.mean(sparsity), statistics.pstdev(sparsity))
                     emit(row)
                     del ar, buf
                     env.heap_release(mark)
             del x, work
             torch.cuda.empty_cache()
+    if args.csv and rank == 0:
+        os.makedirs(os.path.dirname(os.path.abspath(args.csv)), exist_ok=True)
+        with open(args.csv, "w") as f:
+            f.write("variant;size(MB);compression;time_mean(us);time_stddev(us);sparsity_mean;sparsity_stddev\n")
+            for row in rows:
+                if "csv" in row:
+                    v = row["csv"]
+                    f.write(f"{v[0]};{v[1]:.6g};{v[2]:g};{v[3]:.2f};{v[4]:.2f};{v[5]:.5f};{v[6]:.5f}\n")
+    for row in rows:
+        row.pop("csv", None)
     if args.out and rank == 0:
         os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
         with open(args.out, "w") as f:

@@ -511,7 +511,9 @@ class Comprex_RingAllreduce(_ComprexAllreduceBase):
     def _plan_ring(self, t, flush, rounds=1):
         env, me, nr = self._env, self._env.rank, self._env.ranks
         mine = (me + 1) % nr
-        others = [c for c in range(nr) if c != mine]
+        # chunk order starts behind this rank's own chunk: at any moment every rank addresses a
+        # different owner instead of all ranks storing into the same receiver
+        others = [(mine + k) % nr for k in range(1, nr)]
         peers = [r for r in range(nr) if r != me]
         phases = []
         for rnd in range(rounds):

@@ -103,8 +103,19 @@ __global__ void __launch_bounds__(kThreads) dense_send_kernel(const SendParams p
       }
     }
   } else {
-    // target k receives elements [start_k, start_k + len_k)
-    for (int k = 0; k < p.tg.count; ++k) {
+    // target k receives elements [start_k, start_k + len_k).  The CTAs are dealt out to the
+    // targets (CTA b serves target b mod count) so that all destinations are written at the
+    // same time: when every rank runs this kernel, a loop "target 0 first" would aim all of
+    // them at the same receiver, whose NVLink ingress then serialises the whole phase.
+    const int cnt = p.tg.count;
+    const bool dealt = cnt > 0 && (int)gridDim.x >= cnt;
+    const int k0 = dealt ? (int)(blockIdx.x % cnt) : 0;
+    const int k1 = dealt ? k0 + 1 : cnt;
+    const int64_t my_ctas = dealt ? ((int64_t)gridDim.x - k0 + cnt - 1) / cnt : gridDim.x;
+    const int64_t tid_k = dealt ? (int64_t)(blockIdx.x / cnt) * kThreads + threadIdx.x : gtid;
+    const int64_t sz_k = my_ctas * kThreads;
+    for (int k = k0; k < k1; ++k) {
+      const int64_t gtid = tid_k, gsz = sz_k;   // this target's share of the grid
       const T* src = g + p.rg.start[k];
       T* dst = reinterpret_cast<T*>(p.tg.ep[k].pairs);
       const int64_t len = p.rg.len[k];
