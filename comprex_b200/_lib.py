@@ -72,7 +72,7 @@ class Op(C.Structure):
                 ("scale", C.c_float), ("thr", C.c_void_p), ("cap", C.c_uint32), ("src_rank", C.c_uint32),
                 ("workspace", C.c_void_p), ("ws_bytes", C.c_int64), ("stats", C.c_void_p),
                 ("out", C.c_void_p), ("own", C.c_void_p), ("status", C.c_void_p), ("timeout_ns", C.c_uint64),
-                ("has_push", C.c_int32), ("pad", C.c_int32),
+                ("has_push", C.c_int32), ("lane", C.c_int32),
                 ("starts", C.c_int64 * MAX_PEERS), ("lens", C.c_int64 * MAX_PEERS),
                 ("tg", Targets), ("src", Sources), ("apply", ApplyArgs)]
 

@@ -496,6 +496,9 @@ class Comprex_RingAllreduce(_ComprexAllreduceBase):
         self._rs = [[P.SparseSlot.create(env, nmax, self.cap) for _ in range(2)] for _ in range(env.ranks)]
         self._ag = [[P.SparseSlot.create(env, nmax, self.cap) for _ in range(2)] for _ in range(env.ranks)]
         self._comp = P.Compressor(env, nmax)
+        # one compressor (scratch, threshold cell) per chunk: the per-chunk compressions of the
+        # reduce-scatter are independent and run concurrently when the call is replayed
+        self._chunk_comps = [P.Compressor(env, nmax) for _ in range(env.ranks)]
         self.rests = torch.zeros(size, dtype=torch.float32, device=env.device)
         self.owner_rests = torch.zeros(nmax, dtype=torch.float32, device=env.device) if owner_residual else None
 
@@ -521,15 +524,17 @@ class Comprex_RingAllreduce(_ComprexAllreduceBase):
             seq, par = self._step, self._step & 1
 
             def scatter(seq=seq, par=par):
-                for c in others:
+                for k, c in enumerate(others):
                     n = self.segment_sizes[c]
                     g, r = (None if flush else self._view(t, c)), self._view(self.rests, c)
-                    if flush:
-                        self._comp.set_threshold(0.0)
-                    else:
-                        self._comp.threshold_topk(g, r, n, self.compression_ratio, self._subsamples, self._sample_factor)
-                    self._comp.compress(g, r, n, self.cap, seq,
-                                        P.make_targets([self._rs[me][par].endpoint(env, self._owner(c))]))
+                    comp = self._chunk_comps[c]
+                    with P.lane(env, k + 1):
+                        if flush:
+                            comp.set_threshold(0.0)
+                        else:
+                            comp.threshold_topk(g, r, n, self.compression_ratio, self._subsamples, self._sample_factor)
+                        comp.compress(g, r, n, self.cap, seq,
+                                      P.make_targets([self._rs[me][par].endpoint(env, self._owner(c))]))
 
             def reduce(seq=seq, par=par, last=(rnd == rounds - 1)):
                 if nr == 1:
@@ -552,10 +557,11 @@ class Comprex_RingAllreduce(_ComprexAllreduceBase):
             def gather(seq=seq, par=par, last=(rnd == rounds - 1)):
                 if flush and not last:
                     return
-                for j in peers:
+                for k, j in enumerate(peers):
                     c = (j + 1) % nr
                     src = P.make_sources([self._ag[j][par].endpoint(env)], [seq])
-                    P.apply_sparse(env, src, self.segment_sizes[c], P.args_set(self._view(t, c)), self._status)
+                    with P.lane(env, k + 1):     # the chunks are disjoint: decode them side by side
+                        P.apply_sparse(env, src, self.segment_sizes[c], P.args_set(self._view(t, c)), self._status)
             phases += [scatter, reduce, gather]
         return phases
 

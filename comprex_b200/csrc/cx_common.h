@@ -274,7 +274,7 @@ typedef struct CxOp {
   uint32_t* status;
   uint64_t timeout_ns;
   int32_t has_push;
-  int32_t pad;
+  int32_t lane;                /* 0: the caller's stream; k > 0: side stream k (see cx_run_ops) */
   int64_t starts[CX_MAX_PEERS];
   int64_t lens[CX_MAX_PEERS];
   CxTargets tg;                /* compress / dense send targets, dense reduce push targets */
@@ -282,8 +282,14 @@ typedef struct CxOp {
   CxApplyArgs apply;
 } CxOp;
 
-/* Runs ops[0..count) in order on `stream`; every notification written or waited
- * for uses sequence number `seq`.  Stops at the first failing launch. */
+/* Runs ops[0..count) on `stream`; every notification written or waited for uses sequence
+ * number `seq`.  Stops at the first failing launch.
+ * Ops with lane 0 run on `stream` in order.  Ops with lane k > 0 (CUDA only, k <= CX_MAX_LANES)
+ * run on an internal side stream k, in order among themselves and concurrently with the other
+ * lanes: a side stream starts behind everything queued on `stream` before its first op, and the
+ * next lane-0 op (or the end of the list) waits for all side streams.  Independent small
+ * launches (the per-chunk compressions of a ring) then overlap instead of queueing up. */
+#define CX_MAX_LANES 16
 int cx_run_ops(CxOp* ops, int count, uint64_t seq, void* stream);
 int64_t cx_sizeof(int what); /* 0 CxOp, 1 CxSources, 2 CxTargets, 3 CxApplyArgs, 4 CxWorkCounters, 5 CxHeader */
 

@@ -15,6 +15,7 @@
 #include <unistd.h>
 
 #include <atomic>
+#include <mutex>
 
 #include "cx_common.h"
 
@@ -183,39 +184,103 @@ int64_t cx_sizeof(int what) {
   }
 }
 
-int cx_run_ops(CxOp* ops, int count, uint64_t seq, void* stream) {
-  for (int i = 0; i < count; ++i) {
-    CxOp& o = ops[i];
-    int rc = 0;
-    switch (o.kind) {
-      case CX_OPK_THRESHOLD:
-        rc = cx_threshold_topk(o.dev, o.dtype, o.g, o.r, o.n, o.ratio, o.default_subsamples,
+// ---- launch sequences -------------------------------------------------------------------
+namespace {
+
+int run_one(CxOp& o, uint64_t seq, void* stream) {
+  switch (o.kind) {
+    case CX_OPK_THRESHOLD:
+      return cx_threshold_topk(o.dev, o.dtype, o.g, o.r, o.n, o.ratio, o.default_subsamples,
                                o.subsample_factor, o.thr, stream);
-        break;
-      case CX_OPK_COMPRESS:
-        rc = cx_compress(o.dev, o.dtype, o.g, o.r, o.n, o.thr, o.cap, seq, &o.tg, o.workspace,
+    case CX_OPK_COMPRESS:
+      return cx_compress(o.dev, o.dtype, o.g, o.r, o.n, o.thr, o.cap, seq, &o.tg, o.workspace,
                          o.ws_bytes, o.stats, o.src_rank, stream);
-        break;
-      case CX_OPK_APPLY:
-        for (int j = 0; j < o.src.count; ++j) o.src.seq[j] = seq;
-        rc = cx_apply(o.dev, &o.src, o.n, &o.apply, o.status, o.timeout_ns, stream);
-        break;
-      case CX_OPK_DENSE_SEND:
-        rc = cx_dense_send(o.dev, o.dtype, o.g, o.r, o.n, seq, &o.tg, o.has_ranges ? o.starts : nullptr,
+    case CX_OPK_APPLY:
+      for (int j = 0; j < o.src.count; ++j) o.src.seq[j] = seq;
+      return cx_apply(o.dev, &o.src, o.n, &o.apply, o.status, o.timeout_ns, stream);
+    case CX_OPK_DENSE_SEND:
+      return cx_dense_send(o.dev, o.dtype, o.g, o.r, o.n, seq, &o.tg, o.has_ranges ? o.starts : nullptr,
                            o.has_ranges ? o.lens : nullptr, o.workspace, o.src_rank, stream);
-        break;
-      case CX_OPK_DENSE_REDUCE:
-        for (int j = 0; j < o.src.count; ++j) o.src.seq[j] = seq;
-        rc = cx_dense_reduce(o.dev, o.dtype, o.out, o.own, o.n, &o.src, o.scale,
+    case CX_OPK_DENSE_REDUCE:
+      for (int j = 0; j < o.src.count; ++j) o.src.seq[j] = seq;
+      return cx_dense_reduce(o.dev, o.dtype, o.out, o.own, o.n, &o.src, o.scale,
                              o.has_push ? &o.tg : nullptr, seq, o.has_ranges ? o.starts : nullptr,
                              o.has_ranges ? o.lens : nullptr, o.workspace, o.src_rank, o.status,
                              o.timeout_ns, stream);
-        break;
-      default:
-        return cx_set_error("cx_run_ops: unknown op kind", 0);
-    }
-    if (rc) return rc;
+    default:
+      return cx_set_error("cx_run_ops: unknown op kind", 0);
   }
+}
+
+// side streams and their events, one set per device, created on first use
+struct Lanes {
+  cudaStream_t stream[CX_MAX_LANES + 1];
+  cudaEvent_t done[CX_MAX_LANES + 1];
+  cudaEvent_t fork;
+  bool ready;
+};
+Lanes g_lanes[64];
+std::mutex g_lanes_mutex;
+
+Lanes* lanes_for_current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_lanes_mutex);
+  Lanes& l = g_lanes[dev];
+  if (!l.ready) {
+    if (cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    for (int k = 1; k <= CX_MAX_LANES; ++k) {
+      if (cudaStreamCreateWithFlags(&l.stream[k], cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+      if (cudaEventCreateWithFlags(&l.done[k], cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    }
+    l.ready = true;
+  }
+  return &l;
+}
+
+}  // namespace
+
+int cx_run_ops(CxOp* ops, int count, uint64_t seq, void* stream) {
+  cudaStream_t main_stream = reinterpret_cast<cudaStream_t>(stream);
+  Lanes* lanes = nullptr;
+  uint32_t open_mask = 0;      // side lanes with work that `stream` has not waited for yet
+  bool forked = false;         // the fork event of the current region is recorded
+  auto join = [&]() -> int {
+    for (int k = 1; k <= CX_MAX_LANES; ++k) {
+      if (!((open_mask >> k) & 1u)) continue;
+      if (cudaEventRecord(lanes->done[k], lanes->stream[k]) != cudaSuccess ||
+          cudaStreamWaitEvent(main_stream, lanes->done[k], 0) != cudaSuccess)
+        return cx_set_error("cx_run_ops: joining a side stream", (int)cudaGetLastError());
+    }
+    open_mask = 0;
+    forked = false;
+    return 0;
+  };
+  for (int i = 0; i < count; ++i) {
+    CxOp& o = ops[i];
+    int rc;
+    if (o.lane > 0 && o.dev == CX_DEV_CUDA) {
+      if (o.lane > CX_MAX_LANES) return cx_set_error("cx_run_ops: lane out of range", 0);
+      if (!lanes && !(lanes = lanes_for_current_device()))
+        return cx_set_error("cx_run_ops: side streams", (int)cudaGetLastError());
+      if (!forked) {
+        if (cudaEventRecord(lanes->fork, main_stream) != cudaSuccess)
+          return cx_set_error("cx_run_ops: fork event", (int)cudaGetLastError());
+        forked = true;
+      }
+      if (!((open_mask >> o.lane) & 1u)) {
+        if (cudaStreamWaitEvent(lanes->stream[o.lane], lanes->fork, 0) != cudaSuccess)
+          return cx_set_error("cx_run_ops: forking a side stream", (int)cudaGetLastError());
+        open_mask |= 1u << o.lane;
+      }
+      rc = run_one(o, seq, lanes->stream[o.lane]);
+    } else {
+      if (open_mask && (rc = join())) return rc;
+      rc = run_one(o, seq, stream);
+    }
+    if (rc) { if (open_mask) join(); return rc; }
+  }
+  if (open_mask) return join();
   return 0;
 }
 

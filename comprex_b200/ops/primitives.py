@@ -101,7 +101,25 @@ def _recording(env) -> bool:
 def _new_op(env, kind: int, dtype: int, n: int):
     op = _lib.Op()
     op.kind, op.dev, op.dtype, op.n = kind, env.dev, dtype, n
+    op.lane = getattr(env, "_lane", 0)      # side stream of the recorded sequence (see ``lane``)
     return op
+
+
+class lane:
+    """``with lane(env, k):`` - launches recorded inside run on side stream ``k`` of the replayed
+    sequence (concurrently with the other lanes, joined before the next lane-0 launch).  Outside a
+    recording the launches simply go to the current stream."""
+
+    def __init__(self, env, k: int):
+        self.env, self.k = env, int(k)
+
+    def __enter__(self):
+        self.prev = getattr(self.env, "_lane", 0)
+        self.env._lane = self.k
+        return self
+
+    def __exit__(self, *exc):
+        self.env._lane = self.prev
 
 
 def _set_ranges(op, ranges) -> None:
