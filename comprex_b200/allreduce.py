@@ -91,8 +91,21 @@ class _AllreduceBase:
             raise ComprexError("connections are already set up")
         self.size = int(size)
         self.dtype = dtype
+        self._check_agreement()
         self._status = self._env.new_status(type(self).__name__)
         self._counters = self._env.scratch(64)
+
+    def _check_agreement(self) -> None:
+        """Collective: every rank must set up the same kind of allreduce for the same size (slot
+        layouts are derived from it; a mismatch would otherwise show up as BAD_HEADER later)."""
+        env = self._env
+        if env._world is not None or env.ranks == 1 or env.group is None:
+            return
+        mine = (type(self).__name__, self.size, str(self.dtype))
+        theirs = env._exchange(mine)
+        if any(t != mine for t in theirs):
+            raise ComprexError("allreduce set-up differs between ranks: " +
+                               ", ".join(f"rank {r}: {t}" for r, t in enumerate(theirs)))
 
     # Target / source descriptors depend only on the parity of the step: they are built
     # once and reused, a call then only refreshes the sequence numbers.

@@ -217,6 +217,71 @@ def scenario_replay_and_two_shot(rank, world, device):
     return True
 
 
+def scenario_allreduce_ops(rank, world, device):
+    """The six *AllreduceOp wrappers and the registered ops (mirror of test/TFallreduceOp.py):
+    set up once, apply in place, flush, compare with the closed form."""
+    import comprex_b200 as cx
+    from comprex_b200 import allreduceOp as O
+    from helpers import alt_ramp
+    env = cx.GaspiEnvironment(32 << 20, device=device, timeout_ms=20000)
+    n = 5003
+    vals = alt_ramp(n, device)
+    for cls, kw in [(O.AllToOneAllreduceOp, dict(chiefRank=0)), (O.RingAllreduceOp, {}), (O.BigRingAllreduceOp, {})]:
+        op = cls(env)
+        op.setup(n, 1, **kw)
+        op.setup(n - 1, 1, **kw)                       # a second, smaller set-up is ignored
+        try:
+            op.setup(n + 1, 1, **kw)
+            raise AssertionError("growing an op must fail")
+        except RuntimeError:
+            pass
+        t = vals.clone()
+        out = op(t)                                    # __call__ -> apply, in place
+        assert out is t and torch.equal(t, world * vals)
+        torch.ops.comprex.allreduce_apply(t, op.handle)    # the registered op itself
+        assert torch.equal(t, world * world * vals)
+    runs = 4
+    for cls, kw in [(O.Comprex_BigRingAllreduceOp, {}), (O.Comprex_RingAllreduceOp, {}),
+                    (O.Comprex_AllToOneAllreduceOp, dict(chiefRank=0))]:
+        op = cls(env)
+        op.setup(n, 1, compression_ratio=0.05, size_factor=3.0, **kw)
+        op.set_compression_ratio(0.02)
+        acc = vals.clone()
+        for _ in range(runs):
+            op.apply(acc if rank == 0 else vals.clone())
+        op.flush(acc if rank == 0 else torch.zeros(n, device=device))
+        env.barrier()
+        if rank == 0:
+            expect = (runs * (world - 1) + 1) * vals
+            if cls is O.Comprex_RingAllreduceOp:
+                c = 1 % world
+                a = op.allreduce
+                sl = slice(a.segment_starts[c], a.segment_starts[c] + a.segment_sizes[c])
+                assert torch.equal(acc[sl], expect[sl])
+            else:
+                assert torch.equal(acc, expect)
+    env.barrier()
+    env.close()
+    return True
+
+
+def scenario_mismatched_setup(rank, world, device):
+    """Ranks that disagree on the vector length learn it at set-up, on every rank."""
+    import comprex_b200 as cx
+    env = cx.GaspiEnvironment(8 << 20, device=device, timeout_ms=5000)
+    ar = cx.Comprex_BigRingAllreduce(env)
+    try:
+        ar.setup_connections(1000 + rank, 1, 0.01, 3.0)
+    except cx.ComprexError as e:
+        assert "differs between ranks" in str(e) and "1001" in str(e)
+        ok = True
+    else:
+        ok = False
+    env.barrier()
+    env.close()
+    return ok
+
+
 def scenario_missing_sender(rank, world, device):
     """Rank 1 skips its send: rank 0's wait must give up with TIMEOUT, not hang; then recover."""
     import comprex_b200 as cx
@@ -296,6 +361,14 @@ def test_replay_and_two_shot_cpu_ranks(world):
     assert all(run_ranks(world, "scenario_replay_and_two_shot"))
 
 
+def test_allreduce_ops_cpu_ranks():
+    assert all(run_ranks(2, "scenario_allreduce_ops"))
+
+
+def test_mismatched_setup_is_detected_cpu():
+    assert all(run_ranks(2, "scenario_mismatched_setup"))
+
+
 def test_missing_sender_times_out_cpu():
     assert run_ranks(2, "scenario_missing_sender")[0] is True
 
@@ -318,6 +391,12 @@ def test_config1_two_gpus():
 @pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
 def test_allreduce_variants_gpus():
     run_ranks(min(_gpus(), 4), "scenario_allreduce_variants", backend="nccl")
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_allreduce_ops_gpus():
+    assert all(run_ranks(2, "scenario_allreduce_ops", backend="nccl"))
 
 
 @pytest.mark.gpu
