@@ -212,14 +212,25 @@ def main():
         opt.step()
         return loss
 
-    def step_e2e(i):
-        hx, hy = host[i % len(host)]
-        x, y = hx.to(dev, non_blocking=True), hy.to(dev, non_blocking=True)
-        opt.zero_grad()
-        loss = loss_fn(x, y)
-        loss.backward()
-        opt.step()
-        return float(loss.item())
+    def e2e_loop(nsteps):
+        """nsteps training steps fed from pinned host memory: the next batch's host-to-device copy
+        runs on a copy stream while this batch trains, and the loss of step k is read on the host
+        while step k+1 is queued (every step's copy and read-back happen inside this loop)."""
+        from comprex_b200.utils import AsyncScalar, DevicePrefetcher
+        feed = DevicePrefetcher((host[i % len(host)] for i in range(nsteps)), dev)
+        pending, last = None, 0.0
+        for x, y in feed:
+            opt.zero_grad()
+            loss = loss_fn(x, y)
+            loss.backward()
+            opt.step()
+            reader = AsyncScalar(loss)
+            if pending is not None:
+                last = pending.value()
+            pending = reader
+        if pending is not None:
+            last = pending.value()
+        return last
 
     def barrier():
         torch.cuda.synchronize()
@@ -258,12 +269,10 @@ def main():
 
     e2e = None
     if not args.skip_e2e:
-        for i in range(2):
-            step_e2e(i)
+        e2e_loop(2)
         barrier()
         t0 = time.perf_counter()
-        for i in range(args.steps):
-            step_e2e(i)
+        e2e_loop(args.steps)
         barrier()
         sec = max_over_ranks(time.perf_counter() - t0)
         hx, hy = host[0]

@@ -72,3 +72,23 @@ def test_timers_and_logging(tmp_path, device):
     assert log(loss=1.0, samples=8) is None
     rec = log(loss=0.5, samples=8)
     assert rec["step"] == 2 and rec["loss"] == 0.5 and rec["samples_per_s"] > 0
+
+
+def test_prefetcher_and_async_scalar(device):
+    from comprex_b200.utils import AsyncScalar, DevicePrefetcher
+    pin = device != "cpu" and torch.cuda.is_available()
+    host = [(torch.full((4, 3), float(i)), torch.tensor([i])) for i in range(5)]
+    if pin:
+        host = [(a.pin_memory(), b.pin_memory()) for a, b in host]
+    feed = DevicePrefetcher(host, device, depth=2)
+    seen, readers = [], []
+    for x, y in feed:
+        assert x.device.type == torch.device(device).type
+        readers.append(AsyncScalar(x.sum() + y.sum()))
+        seen.append(int(y.item()))
+    assert seen == [0, 1, 2, 3, 4]
+    assert [r.value() for r in readers] == [13.0 * i for i in range(5)]
+    single = list(DevicePrefetcher([torch.ones(2), torch.zeros(2)], device))
+    assert len(single) == 2 and float(single[0].sum()) == 2.0
+    if pin:
+        assert feed.h2d_bytes == 5 * (12 * 4 + 8)
