@@ -187,9 +187,16 @@ def dev_code(t: torch.Tensor) -> int:
     return DEV_CUDA if t.is_cuda else DEV_HOST
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr(device: torch.device) -> int:
+    """cudaStream_t of the current stream of ``device`` (0 on the host).  Called once per launch:
+    the raw-pointer query avoids building a ``torch.cuda.Stream`` object each time."""
     if device.type != "cuda":
         return 0
+    if _raw_stream is not None and device.index is not None:
+        return _raw_stream(device.index)
     return torch.cuda.current_stream(device).cuda_stream
 
 

@@ -105,13 +105,19 @@ class _FoldTable:
         self.seg_first = torch.tensor(first, dtype=torch.int32, device=dev)
         self.partial = torch.zeros(self.nitems, dtype=torch.float32, device=dev)
         self.ptrs = torch.zeros(self.nseg, dtype=torch.int64, device=dev)
+        self.last = None
         self.cuda = dev.type == "cuda"
         if self.cuda:
             self.ring = [(torch.zeros(self.nseg, dtype=torch.int64).pin_memory(), torch.cuda.Event()) for _ in range(4)]
             self.turn = 0
 
     def stage(self, values) -> None:
-        """Upload this step's gradient pointers (async on the current stream)."""
+        """Upload this step's gradient pointers (async on the current stream).  The caching
+        allocator usually hands autograd the same blocks every step: an unchanged table is
+        not uploaded again."""
+        if values == self.last:
+            return
+        self.last = list(values)
         if not self.cuda:
             self.ptrs.copy_(torch.tensor(values, dtype=torch.int64))
             return
@@ -205,7 +211,9 @@ class ComprexOptimizer(torch.optim.Optimizer):
         self.comprex_allreducers = {}
         self._xbuf = None
         self._comm = None
-        self.overlap = bool(overlap) and dev.type == "cuda"
+        # with a single bucket there is nothing to overlap with: its last gradient appears when
+        # backward ends, and the hooks and the side stream would only add latency
+        self.overlap = bool(overlap) and dev.type == "cuda" and len(self._buckets) > 1
         self._armed = False
         self._hooks = []
         if self.overlap:
@@ -266,7 +274,7 @@ class ComprexOptimizer(torch.optim.Optimizer):
             if g is None:
                 ptrs.append(self._zeros.data_ptr())
                 continue
-            if g.dtype != self._dtype or not _same_layout(g, p):
+            if g.dtype != self._dtype or (g.stride() != p.stride() and not _same_layout(g, p)):
                 g = torch.empty_strided(p.size(), p.stride(), dtype=self._dtype, device=p.device).copy_(g)  # rare
                 p.grad = g
             ptrs.append(g.data_ptr())
