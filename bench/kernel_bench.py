@@ -7,6 +7,8 @@ after warm-up and with an L2 flush between iterations:
 * ``compress``   - fused residual add / select / per-sub-tile compaction / store into
                    ``--targets`` slots (local memory stands in for peers),
 * ``apply_add``  - wait + scatter-add of ``--sources`` payloads,
+* ``apply_set``  - wait + dense result (sum of the payloads, zero elsewhere): the receive side of
+                   the replica-consistent allreduce,
 * ``apply_sgd`` / ``apply_adamw`` - the same fused with the parameter update.
 
 Algorithmic bytes: compress reads g and r and writes r (plus 8 B per pair and
@@ -110,6 +112,10 @@ def main():
                     src = P.make_sources([s.endpoint(env) for s in slots[: args.sources]], [1] * args.sources)
                     P.apply_sparse(env, src, n, P.args_add(out, 1.0 / 8), st)
 
+                def k_set():
+                    src = P.make_sources([s.endpoint(env) for s in slots[: args.sources]], [1] * args.sources)
+                    P.apply_sparse(env, src, n, P.args_set(out, 1.0 / 8), st)
+
                 def k_sgd():
                     src = P.make_sources([s.endpoint(env) for s in slots[: args.sources]], [1] * args.sources)
                     P.apply_sparse(env, src, n, P.args_update(_lib.OP_SGD, w, 1.0 / 8), st)
@@ -126,6 +132,7 @@ def main():
                     "threshold": (k_thr, 0),
                     "compress": (k_comp, n * (gb + 8) + 8 * nnz * args.targets),
                     "apply_add": (k_add, args.sources * nnz * (8 + 64)),
+                    "apply_set": (k_set, args.sources * nnz * 8 + 4 * n),
                     "apply_sgd": (k_sgd, args.sources * nnz * (8 + 64)),
                     "apply_adamw": (k_adamw, args.sources * nnz * 8 + 24 * n),
                 }
