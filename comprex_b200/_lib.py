@@ -105,6 +105,9 @@ def _declare(lib) -> None:
         "cx_dense_reduce": (i32, [i32, i32, vp, vp, i64, P(Sources), f32, P(Targets), u64, P(i64), P(i64),
                                   vp, u32, vp, u64, vp]),
         "cx_run_ops": (i32, [P(Op), i32, u64, vp]),
+        "cx_graph_build": (i32, [P(Op), i32, P(vp)]),
+        "cx_graph_launch": (i32, [vp, u64, vp]),
+        "cx_graph_free": (i32, [vp]),
         "cx_sizeof": (i64, [i32]),
         "cx_fold": (i32, [i32, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp, f32, f32, f32, vp]),
         "cx_axpy": (i32, [i32, i32, vp, i32, vp, f32, i64, vp]),

@@ -38,6 +38,7 @@ struct ApplyParams {
   uint32_t vec;  // every dense pointer is 16-byte aligned
   uint32_t* status;
   uint64_t timeout_ns;
+  const uint64_t* seq_cell;  // non-NULL inside a captured graph: the waits use its value
 };
 
 __device__ __forceinline__ CxPair ld_pair(const CxPair* p) {
@@ -58,7 +59,7 @@ __device__ __forceinline__ bool wait_sources(const ApplyParams& p, uint32_t* s_n
     const int j = threadIdx.x;
     const CxHeader* h = p.src.ep[j].hdr;
     uint32_t bad = 0;
-    if (!cx::wait_seq(&h->seq, p.src.seq[j], p.timeout_ns)) {
+    if (!cx::wait_seq(&h->seq, cx::seq_of(p.seq_cell, p.src.seq[j]), p.timeout_ns)) {
       bad = CX_ST_TIMEOUT;
     } else {
       const uint32_t kind = *reinterpret_cast<const volatile uint32_t*>(&h->kind);
@@ -608,7 +609,7 @@ int cx_apply_cuda(const CxSources* src, int64_t n, const CxApplyArgs* a, uint32_
   ApplyParams p;
   p.src = *src; p.a = *a; p.n = n;
   p.nsub = (uint32_t)((n + CX_SUBTILE - 1) / CX_SUBTILE);
-  p.status = status; p.timeout_ns = timeout_ns;
+  p.status = status; p.timeout_ns = timeout_ns; p.seq_cell = cx_seq_cell();
   const bool update = a->op != CX_OP_ADD && a->op != CX_OP_SET;
   if (update && a->op != CX_OP_SGD && !a->m) return cx_set_error("cx_apply: momentum buffer missing", 0);
   if (a->op == CX_OP_ADAMW && !a->v) return cx_set_error("cx_apply: second-moment buffer missing", 0);

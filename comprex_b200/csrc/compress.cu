@@ -53,6 +53,7 @@ struct CompressParams {
   uint32_t region_size;  // cap / nregions pairs each
   uint32_t vec;          // g and r are aligned for 16-byte (8-byte for 16-bit g) accesses
   uint64_t seq;
+  const uint64_t* seq_cell;  // non-NULL inside a captured graph: the sequence number lives there
   CxWorkCounters* ctr;
   CxStats* stats;
   uint32_t src_rank;
@@ -270,7 +271,7 @@ compress_kernel(const __grid_constant__ CompressParams p) {
     h->src_rank = p.src_rank;
     h->dtype = CX_F32;
     __threadfence_system();
-    cx::st_release_sys(&h->seq, p.seq);
+    cx::st_release_sys(&h->seq, cx::seq_of(p.seq_cell, p.seq));
   }
   if (tid == 0) {
     if (p.stats) {
@@ -292,7 +293,7 @@ __global__ void compress_empty_kernel(const CompressParams p) {
     h->bytes = 8; h->n = 0; h->nnz = 0; h->nnz_found = 0; h->kind = CX_KIND_PAIRS;
     h->threshold = *p.thr; h->nsub = 0; h->src_rank = p.src_rank; h->dtype = CX_F32;
     __threadfence_system();
-    cx::st_release_sys(&h->seq, p.seq);
+    cx::st_release_sys(&h->seq, cx::seq_of(p.seq_cell, p.seq));
   }
   if (tid == 0 && p.stats) {
     p.stats->n = 0; p.stats->nnz = 0; p.stats->nnz_found = 0; p.stats->status = 0;
@@ -331,6 +332,7 @@ int cx_compress_cuda(int gdtype, const void* g, float* r, int64_t n, const float
     p.nregions *= 2;
   p.region_size = cap / p.nregions;
   p.seq = seq;
+  p.seq_cell = cx_seq_cell();
   p.ctr = reinterpret_cast<CxWorkCounters*>(workspace);
   p.stats = stats; p.src_rank = src_rank;
   p.tg = *tg;

@@ -291,6 +291,12 @@ typedef struct CxOp {
  * launches (the per-chunk compressions of a ring) then overlap instead of queueing up. */
 #define CX_MAX_LANES 16
 int cx_run_ops(CxOp* ops, int count, uint64_t seq, void* stream);
+/* The same sequence captured as a CUDA graph (CUDA ops only): built once, then one small copy
+ * (the sequence number, into a device cell the kernels read) and one graph launch per replay.
+ * The ops' pointers and parameters are frozen at build time. */
+int cx_graph_build(CxOp* ops, int count, void** graph_out);
+int cx_graph_launch(void* graph, uint64_t seq, void* stream);
+int cx_graph_free(void* graph);
 int64_t cx_sizeof(int what); /* 0 CxOp, 1 CxSources, 2 CxTargets, 3 CxApplyArgs, 4 CxWorkCounters, 5 CxHeader */
 
 /* bounded wait on a header from the host (status in the return value) */

@@ -107,6 +107,16 @@ __device__ __forceinline__ void store4(__half* p, const float (&v)[4]) {
 
 }  // namespace cx
 
+// A launch that is part of a captured graph takes its sequence number from a device cell
+// (written in stream order before every graph launch) instead of from its parameters.
+namespace cx {
+__device__ __forceinline__ uint64_t seq_of(const uint64_t* cell, uint64_t by_value) {
+  return cell ? *reinterpret_cast<const volatile uint64_t*>(cell) : by_value;
+}
+}  // namespace cx
+// the cell for launches issued by this thread right now (NULL outside a graph capture)
+const uint64_t* cx_seq_cell();
+
 // host-side launch bookkeeping shared by the .cu files
 void cx_note_launch();
 int cx_set_error(const char* where, int cuda_err);

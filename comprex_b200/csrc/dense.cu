@@ -26,6 +26,7 @@ struct SendParams {
   float* r;
   int64_t n;
   uint64_t seq;
+  const uint64_t* seq_cell;  // non-NULL inside a captured graph
   CxTargets tg;
   Ranges rg;
   int32_t has_ranges;
@@ -145,7 +146,7 @@ __global__ void __launch_bounds__(kThreads) dense_send_kernel(const SendParams p
   if (!s_last) return;
   __threadfence();
   if ((int)threadIdx.x < p.tg.count)
-    publish_dense<T>(p.tg, threadIdx.x, p.has_ranges ? p.rg.len[threadIdx.x] : p.n, p.seq,
+    publish_dense<T>(p.tg, threadIdx.x, p.has_ranges ? p.rg.len[threadIdx.x] : p.n, cx::seq_of(p.seq_cell, p.seq),
                      p.src_rank, p.dtype);
   if (threadIdx.x == 0) p.ctr->done = 0;
 }
@@ -159,6 +160,7 @@ struct ReduceParams {
   int32_t has_push;
   CxTargets push;
   uint64_t push_seq;
+  const uint64_t* seq_cell;  // non-NULL inside a captured graph: waits and the push use its value
   uint32_t src_rank;
   uint32_t dtype;
   CxWorkCounters* ctr;
@@ -169,14 +171,14 @@ struct ReduceParams {
 };
 
 __device__ __forceinline__ bool wait_dense(const CxSources& src, uint64_t timeout_ns,
-                                           uint32_t* status, uint32_t dtype) {
+                                           uint32_t* status, uint32_t dtype, const uint64_t* seq_cell) {
   __shared__ uint32_t s_bad;
   if (threadIdx.x == 0) s_bad = 0;
   __syncthreads();
   if ((int)threadIdx.x < src.count) {
     const CxHeader* h = src.ep[threadIdx.x].hdr;
     uint32_t bad = 0;
-    if (!cx::wait_seq(&h->seq, src.seq[threadIdx.x], timeout_ns)) bad = CX_ST_TIMEOUT;
+    if (!cx::wait_seq(&h->seq, cx::seq_of(seq_cell, src.seq[threadIdx.x]), timeout_ns)) bad = CX_ST_TIMEOUT;
     else if (*reinterpret_cast<const volatile uint32_t*>(&h->kind) != CX_KIND_DENSE ||
              *reinterpret_cast<const volatile uint32_t*>(&h->dtype) != dtype)
       bad = CX_ST_BAD_HEADER;
@@ -227,7 +229,7 @@ __device__ __forceinline__ float ldcg1<__half>(const __half* p) {
 template <typename T>
 __global__ void __launch_bounds__(kThreads) dense_reduce_kernel(const ReduceParams p) {
   __shared__ uint32_t s_last;
-  if (!wait_dense(p.src, p.timeout_ns, p.status, p.dtype)) return;
+  if (!wait_dense(p.src, p.timeout_ns, p.status, p.dtype, p.seq_cell)) return;
   T* out = reinterpret_cast<T*>(p.out);
   const T* own = reinterpret_cast<const T*>(p.own);
   const int64_t gtid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
@@ -310,7 +312,7 @@ __global__ void __launch_bounds__(kThreads) dense_reduce_kernel(const ReducePara
   if (!s_last) return;
   __threadfence();
   if ((int)threadIdx.x < p.push.count)
-    publish_dense<T>(p.push, threadIdx.x, p.n, p.push_seq, p.src_rank, p.dtype);
+    publish_dense<T>(p.push, threadIdx.x, p.n, cx::seq_of(p.seq_cell, p.push_seq), p.src_rank, p.dtype);
   if (threadIdx.x == 0) p.ctr->done = 0;
 }
 
@@ -351,7 +353,7 @@ int cx_dense_send_cuda(int dtype, const void* g, float* r, int64_t n, uint64_t s
   if (tg->count < 0 || tg->count > CX_MAX_PEERS) return cx_set_error("cx_dense_send: bad target count", 0);
   if (n < 0 || n > 0x7fffffffLL) return cx_set_error("cx_dense_send: n out of range", 0);
   SendParams p;
-  p.g = g; p.r = r; p.n = n; p.seq = seq; p.tg = *tg; p.src_rank = src_rank; p.dtype = dtype;
+  p.g = g; p.r = r; p.n = n; p.seq = seq; p.seq_cell = cx_seq_cell(); p.tg = *tg; p.src_rank = src_rank; p.dtype = dtype;
   p.ctr = reinterpret_cast<CxWorkCounters*>(counters);
   p.has_ranges = starts != nullptr;
   int64_t work = (n + 3) / 4;
@@ -396,7 +398,7 @@ int cx_dense_reduce_cuda(int dtype, void* out, const void* own, int64_t n, const
   p.out = out; p.own = own; p.n = n; p.src = *src; p.scale = scale;
   p.has_push = push && push->count > 0;
   if (p.has_push) p.push = *push; else p.push.count = 0;
-  p.push_seq = push_seq; p.src_rank = src_rank; p.dtype = dtype;
+  p.push_seq = push_seq; p.seq_cell = cx_seq_cell(); p.src_rank = src_rank; p.dtype = dtype;
   p.ctr = reinterpret_cast<CxWorkCounters*>(counters);
   p.status = status; p.timeout_ns = timeout_ns;
   p.gather = starts != nullptr;

@@ -67,6 +67,8 @@ int cx_set_error(const char* where, int cuda_err) {
   return cuda_err ? -cuda_err : -1;
 }
 void cx_note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+static thread_local const uint64_t* g_seq_cell = nullptr;
+const uint64_t* cx_seq_cell() { return g_seq_cell; }
 int cx_check_launch(const char* where) {
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : cx_set_error(where, (int)e);
@@ -281,6 +283,82 @@ int cx_run_ops(CxOp* ops, int count, uint64_t seq, void* stream) {
     if (rc) { if (open_mask) join(); return rc; }
   }
   if (open_mask) return join();
+  return 0;
+}
+
+// ---- a launch sequence as a CUDA graph -------------------------------------------------
+// The sequence is captured once (side-stream lanes become branches of the graph) with every
+// kernel reading its sequence number from a device cell; a replay is one 8-byte copy into the
+// cell plus one graph launch, instead of one runtime call per kernel.
+struct CxGraph {
+  cudaGraph_t graph;
+  cudaGraphExec_t exec;
+  uint64_t* cell;      // device memory
+  int kernels;         // launches per replay (for the launch counter)
+  int device;
+};
+
+int cx_graph_build(CxOp* ops, int count, void** out) {
+  *out = nullptr;
+  if (count <= 0) return cx_set_error("cx_graph_build: empty sequence", 0);
+  for (int i = 0; i < count; ++i)
+    if (ops[i].dev != CX_DEV_CUDA) return cx_set_error("cx_graph_build: host ops cannot be captured", 0);
+  CxGraph* g = new CxGraph();
+  g->graph = nullptr; g->exec = nullptr; g->cell = nullptr; g->kernels = 0; g->device = 0;
+  cudaStream_t cap = nullptr;
+  cudaError_t e = cudaGetDevice(&g->device);
+  if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&g->cell), sizeof(uint64_t));
+  if (e == cudaSuccess) e = cudaMemset(g->cell, 0, sizeof(uint64_t));
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking);
+  if (e != cudaSuccess || !lanes_for_current_device()) {   // side streams exist before the capture starts
+    if (g->cell) cudaFree(g->cell);
+    if (cap) cudaStreamDestroy(cap);
+    delete g;
+    return cx_set_error("cx_graph_build: set-up", (int)e);
+  }
+  const uint64_t before = g_launches.load();
+  e = cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal);
+  int rc = 0;
+  if (e == cudaSuccess) {
+    g_seq_cell = g->cell;
+    rc = cx_run_ops(ops, count, 0, cap);
+    g_seq_cell = nullptr;
+    const cudaError_t e2 = cudaStreamEndCapture(cap, &g->graph);   // always ends the capture
+    if (rc == 0 && e2 != cudaSuccess) e = e2;
+  }
+  g->kernels = (int)(g_launches.load() - before);
+  g_launches.store(before);                                        // nothing ran yet
+  if (e == cudaSuccess && rc == 0) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
+  cudaStreamDestroy(cap);
+  if (e != cudaSuccess || rc != 0) {
+    if (g->graph) cudaGraphDestroy(g->graph);
+    cudaFree(g->cell);
+    delete g;
+    cudaGetLastError();
+    return rc ? rc : cx_set_error("cx_graph_build: capture", (int)e);
+  }
+  *out = g;
+  return 0;
+}
+
+int cx_graph_launch(void* graph, uint64_t seq, void* stream) {
+  CxGraph* g = reinterpret_cast<CxGraph*>(graph);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // pageable source: the runtime stages the 8 bytes before it returns, so `seq` may go away
+  cudaError_t e = cudaMemcpyAsync(g->cell, &seq, sizeof(seq), cudaMemcpyHostToDevice, s);
+  if (e == cudaSuccess) e = cudaGraphLaunch(g->exec, s);
+  if (e != cudaSuccess) return cx_set_error("cx_graph_launch", (int)e);
+  g_launches.fetch_add((uint64_t)g->kernels, std::memory_order_relaxed);
+  return 0;
+}
+
+int cx_graph_free(void* graph) {
+  CxGraph* g = reinterpret_cast<CxGraph*>(graph);
+  if (!g) return 0;
+  if (g->exec) cudaGraphExecDestroy(g->exec);
+  if (g->graph) cudaGraphDestroy(g->graph);
+  if (g->cell) cudaFree(g->cell);
+  delete g;
   return 0;
 }
 

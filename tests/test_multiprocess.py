@@ -56,24 +56,28 @@ def _entry(rank, world, port, backend, fn_name, q, args):
 
 
 def run_ranks(world, fn_name, backend="gloo", args=(), timeout=240):
+    """Run a scenario on ``world`` spawned ranks.  The first rank that reports an error ends the
+    wait (its peers may be blocked in a collective with it) and its traceback is the failure."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_entry, args=(r, world, port, backend, fn_name, q, args)) for r in range(world)]
     for p in procs:
         p.start()
-    results = {}
+    results, failure = {}, None
     try:
         for _ in range(world):
             rank, status, payload = q.get(timeout=timeout)
             results[rank] = (status, payload)
+            if status != "ok":
+                failure = f"rank {rank} failed:\n{payload}"
+                break
     finally:
         for p in procs:
-            p.join(timeout=30)
+            p.join(timeout=5 if failure else 30)
             if p.is_alive():
                 p.terminate()
-    for rank, (status, payload) in sorted(results.items()):
-        assert status == "ok", f"rank {rank} failed:\n{payload}"
+    assert failure is None, failure
     return [results[r][1] for r in range(world)]
 
 
@@ -285,10 +289,14 @@ def scenario_mismatched_setup(rank, world, device):
 def scenario_missing_sender(rank, world, device):
     """Rank 1 skips its send: rank 0's wait must give up with TIMEOUT, not hang; then recover."""
     import comprex_b200 as cx
-    env = cx.GaspiEnvironment(8 << 20, device=device, timeout_ms=300)
+    env = cx.GaspiEnvironment(8 << 20, device=device, timeout_ms=1000)
     ex = cx.GaspiEx(env, 1000)
     ex.connectTo((rank - 1) % world, (rank + 1) % world, 0)
     v = torch.full((1000,), float(rank + 1), device=device)
+    warm = torch.zeros(8, device=device)
+    warm.add_(1)                     # context, allocator and first-launch costs are paid here,
+    env.flush()                      # not inside the one-second wait below
+    dist.barrier()
     raised = False
     if rank == 0:
         ex.writeRemote(v)
