@@ -283,6 +283,56 @@ def test_apply_bulk_copy_kernel_matches_register_kernel(monkeypatch, n, op, stag
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("graph", [False, True])
+def test_recorded_sequence_with_lanes_and_graph(world, graph):
+    """Six independent threshold + compress pairs on side-stream lanes, joined by one apply:
+    recorded once, replayed three times (as an op list, and on a GPU as a CUDA graph whose
+    kernels take the sequence number from a device cell); equals the direct launches."""
+    from comprex_b200.allreduce import _OpSeq
+    e0, e1 = world.envs
+    dev, nchunk, k = world.device, 3000, 6
+    torch.manual_seed(11)
+    g = torch.randn(k * nchunk).to(dev)
+    slots = [[P.SparseSlot.create(e, nchunk, nchunk) for e in world.envs] for _ in range(k)]
+    comps = [P.Compressor(e0, nchunk) for _ in range(k)]
+    outs = [torch.zeros(nchunk, device=dev) for _ in range(k)]
+    rests = [torch.zeros(k * nchunk, device=dev) for _ in range(2)]
+    st = e1.new_status("t")
+
+    def launches(r, seq):
+        for c in range(k):
+            view, rv = g[c * nchunk:(c + 1) * nchunk], r[c * nchunk:(c + 1) * nchunk]
+            with P.lane(e0, c + 1):
+                comps[c].threshold_topk(view, rv, nchunk, 0.05)
+                comps[c].compress(view, rv, nchunk, nchunk, seq, P.make_targets([slots[c][1].endpoint(e0, 1)]))
+        for c in range(k):
+            with P.lane(e0, c + 1):
+                P.apply_sparse(e0, P.make_sources([slots[c][1].endpoint(e0, 1)], [seq]), nchunk,
+                               P.args_add(outs[c]), st)
+
+    e0._rec = rec = []
+    try:
+        launches(rests[0], 0)
+    finally:
+        e0._rec = None
+    assert len(rec) == 3 * k and {op.lane for op in rec} == set(range(1, k + 1))
+    seq_obj = _OpSeq(e0, rec, graph=graph)
+    assert (seq_obj.graph is not None) == (graph and e0.dev == _lib.DEV_CUDA)
+    for step in (1, 2, 3):
+        seq_obj.run(step)
+    e0.flush()
+    got = torch.cat(outs).cpu()
+    for o in outs:
+        o.zero_()
+    for step in (4, 5, 6):                      # the same launches issued directly
+        launches(rests[1], step)
+    e0.flush()
+    assert st.value == 0
+    assert torch.equal(torch.cat(outs).cpu(), got)
+    assert torch.equal(rests[0].cpu(), rests[1].cpu())
+    assert float(got.abs().sum()) > 0
+
+
 def test_apply_timeout_sets_status_and_leaves_output(world):
     """A notification that never arrives: the wait gives up, the output is untouched."""
     e0 = world.envs[0]
