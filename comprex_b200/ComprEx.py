@@ -187,6 +187,8 @@ class CompressorRLE(_Compressor):
         g = vec.detach().to("cpu", torch.float32).contiguous() if vec is not None else None
         r = rests.detach().to("cpu", torch.float32).contiguous() if rests is not None else None
         n = (g if g is not None else r).numel()
+        if n == 0:                                  # an empty tensor has no address to hand over
+            return (0).to_bytes(4, "little") * 4    # n | nnz | nRuns | firstIsYes
         buf = (C.c_char * (16 + 8 * n + 16))()
         used = lib.cx_rle_compress_host(g.data_ptr() if g is not None else 0, r.data_ptr() if r is not None else 0,
                                         n, float(thr), buf, len(buf))
