@@ -28,7 +28,10 @@ applies only what was transmitted, so replicas stay bit-identical),
 
 ``apply`` is split into phases (``_plan_apply``) so that a
 :class:`~comprex_b200.parallel.env.LoopbackWorld` can run P virtual ranks on
-one device.
+one device.  Between real ranks the launches of a call are recorded once per
+parity of the step and replayed with one native call, from six launches on as
+a CUDA graph; independent launches (the per-chunk work of the compressed Ring)
+run on side-stream lanes.
 """
 from __future__ import annotations
 

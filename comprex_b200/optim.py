@@ -21,7 +21,7 @@ views of it, or of its low-precision shadow, in their own memory order, so
 channels-last weights stay channels-last); there is no flat gradient buffer,
 no concatenation and no slicing copy.  The flat
 buffers are laid out in reverse parameter order and cut into buckets of
-``bucket_cap_mb``; with ``overlap=True`` a bucket's steps 1-2 are launched on a
+``bucket_cap_mb``; with ``overlap=True`` (and more than one bucket) a bucket's steps 1-4 are launched on a
 side stream from a post-accumulate-grad hook as soon as its last gradient is
 produced, i.e. while backward is still running for earlier layers, and
 ``step()`` only launches the receive/update kernels.  Every rank, the sender
