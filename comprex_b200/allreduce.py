@@ -531,9 +531,12 @@ class Comprex_RingAllreduce(_ComprexAllreduceBase):
     """
 
     def setup_connections(self, size, tag=0, compression_ratio=0.01, size_factor=1.0, consistent=False,
-                          owner_residual=False):
+                          owner_residual=False, schedule="direct"):
+        if schedule not in ("direct", "hops"):
+            raise ComprexError("schedule must be 'direct' or 'hops'")
         self._setup_compressed(size, compression_ratio, size_factor, consistent)
         env = self._env
+        self.schedule = schedule
         self.owner_residual = bool(owner_residual)
         self.segment_sizes, self.segment_starts = _chunks(size, env.ranks)
         nmax = max(max(self.segment_sizes), 1)
@@ -546,9 +549,65 @@ class Comprex_RingAllreduce(_ComprexAllreduceBase):
         self._chunk_comps = [P.Compressor(env, nmax) for _ in range(env.ranks)]
         self.rests = torch.zeros(size, dtype=torch.float32, device=env.device)
         self.owner_rests = torch.zeros(nmax, dtype=torch.float32, device=env.device) if owner_residual else None
+        if schedule == "hops":
+            # the reference's neighbour-to-neighbour ring: one slot per hop and parity in each phase
+            hops = max(env.ranks - 1, 1)
+            self._hop_rs = [[P.SparseSlot.create(env, nmax, self.cap) for _ in range(2)] for _ in range(hops)]
+            self._hop_ag = [[P.SparseSlot.create(env, nmax, self.cap) for _ in range(2)] for _ in range(hops)]
+            self._replay = False     # the forwarding launches are not part of recorded sequences
 
     def _residuals(self):
         return [self.rests] + ([self.owner_rests] if self.owner_rests is not None else [])
+
+    def _plan_hops(self, t):
+        """The reference's schedule hop by hop (src/allreduce.tpp:420-457): P-1 reduce steps in
+        which every rank sends top-k of (chunk + that chunk's residual) to its right neighbour and
+        adds what arrives from the left, so partial sums are compressed again at every hop; then
+        the owner's top-k of the reduced chunk travels P-1 hops, forwarded unchanged.  On an
+        NVSwitch this costs 2(P-1) dependent exchanges where ``direct`` needs two; it is kept for
+        studies that need the reference's exact error behaviour."""
+        env, me, nr = self._env, self._env.rank, self._env.ranks
+        self._step += 1
+        seq, par = self._step, self._step & 1
+        if nr == 1:
+            return []
+        right = (me + 1) % nr
+        phases = []
+        for it in range(nr - 1):
+            sc, rc = (me - it) % nr, (me - it - 1) % nr
+
+            def send(it=it, sc=sc):
+                g, r, n = self._view(t, sc), self._view(self.rests, sc), self.segment_sizes[sc]
+                self._comp.threshold_topk(g, r, n, self.compression_ratio, self._subsamples, self._sample_factor)
+                self._comp.compress(g, r, n, self.cap, seq,
+                                    P.make_targets([self._hop_rs[it][par].endpoint(env, right)]))
+
+            def recv(it=it, rc=rc):
+                src = P.make_sources([self._hop_rs[it][par].endpoint(env)], [seq])
+                P.apply_sparse(env, src, self.segment_sizes[rc], P.args_add(self._view(t, rc)), self._status)
+            phases += [send, recv]
+
+        def gather_send():
+            c = (me + 1) % nr
+            n, mv = self.segment_sizes[c], self._view(t, c)
+            r = self.owner_rests[:n] if self.owner_rests is not None else None
+            self._comp.threshold_topk(mv, r, n, self.compression_ratio)
+            self._comp.compress(mv, r, n, self.cap, seq, P.make_targets([self._hop_ag[0][par].endpoint(env, right)]))
+        phases.append(gather_send)
+        for it in range(nr - 2):
+            def fwd(it=it, rc=(me - it) % nr):
+                ep = self._hop_ag[it][par].endpoint(env)
+                P.forward(env, ep, seq, P.make_targets([self._hop_ag[it + 1][par].endpoint(env, right)]), seq,
+                          self.cap, self._counters, self._status)
+                P.apply_sparse(env, P.make_sources([ep], [seq]), self.segment_sizes[rc],
+                               P.args_set(self._view(t, rc)), self._status)
+            phases.append(fwd)
+
+        def last(rc=(me + 2) % nr):
+            src = P.make_sources([self._hop_ag[nr - 2][par].endpoint(env)], [seq])
+            P.apply_sparse(env, src, self.segment_sizes[rc], P.args_set(self._view(t, rc)), self._status)
+        phases.append(last)
+        return phases
 
     def _owner(self, chunk):
         return (chunk - 1) % self._env.ranks
@@ -611,6 +670,8 @@ class Comprex_RingAllreduce(_ComprexAllreduceBase):
         return phases
 
     def _plan_apply(self, t):
+        if self.schedule == "hops":
+            return self._plan_hops(t)
         return self._plan_ring(t, flush=False)
 
     def _plan_flush(self, t):

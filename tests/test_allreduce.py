@@ -45,6 +45,7 @@ def test_dense_allreduce(world, cls, kw, dtype):
 
 
 @pytest.mark.parametrize("cls,kw", [(cx.Comprex_BigRingAllreduce, {}), (cx.Comprex_RingAllreduce, {}),
+                                    (cx.Comprex_RingAllreduce, dict(schedule="hops")),
                                     (cx.Comprex_AllToOneAllreduce, dict(chiefRank=0))])
 @pytest.mark.parametrize("n,ratio", [(50, 0.01), (1000, 0.01), (20011, 0.05)])
 def test_compressed_allreduce_conserves_sum(world, cls, kw, n, ratio):
@@ -71,6 +72,26 @@ def test_compressed_allreduce_conserves_sum(world, cls, kw, n, ratio):
     for a in ars:
         for r in a._residuals():
             assert float(r.abs().sum()) == 0.0
+
+
+def test_ring_schedules_agree_on_two_ranks(device):
+    """With two ranks the direct schedule is the hop-by-hop ring of the reference: same bits."""
+    results = []
+    for schedule in ("direct", "hops"):
+        w = cx.LoopbackWorld(2, device=device, timeout_ms=500)
+        ars = [cx.Comprex_RingAllreduce(e) for e in w.envs]
+        for a in ars:
+            a.setup_connections(20011, 1, compression_ratio=0.05, size_factor=3.0, schedule=schedule)
+        outs = []
+        for step in range(4):
+            xs = [torch.randn(20011, generator=torch.Generator().manual_seed(10 * step + r)).to(device) for r in range(2)]
+            w.run(ars, "apply", [(x,) for x in xs])
+            outs += [x.cpu() for x in xs]
+        outs += [r.cpu().clone() for a in ars for r in a._residuals()]
+        results.append(outs)
+        w.close()
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
 
 
 def test_consistent_bigring_replicas_identical_and_conserving(world):

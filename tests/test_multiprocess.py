@@ -149,6 +149,7 @@ def scenario_allreduce_variants(rank, world, device):
     vals = alt_ramp(n, device)
     runs = 5
     for cls, kw in [(cx.Comprex_BigRingAllreduce, {}), (cx.Comprex_RingAllreduce, {}),
+                    (cx.Comprex_RingAllreduce, dict(schedule="hops")),
                     (cx.Comprex_AllToOneAllreduce, dict(chiefRank=0))]:
         ar = cls(env)
         ar.setup_connections(n, 1, compression_ratio=0.02, size_factor=3.0, **kw)
