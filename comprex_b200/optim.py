@@ -451,8 +451,15 @@ class ComprexOptimizer(torch.optim.Optimizer):
         dev = self._env.device
         self._t = cs["step"]
         self.compression_ratio = cs["ratio"]
+        # Weights and the Adam moments are replicated, so any rank's file restores them.  The
+        # local momentum and the residuals are this rank's own: a file written by another rank
+        # (a new rank of a larger job, or everybody loading rank 0's file) starts them at zero.
+        foreign = int(cs.get("rank", self._env.rank)) != self._env.rank
         self._master.copy_(cs["master"].to(dev))
-        self._update.copy_(cs["update"].to(dev))
+        if foreign:
+            self._update.zero_()
+        else:
+            self._update.copy_(cs["update"].to(dev))
         if self._m is not None and cs["m"] is not None:
             self._m.copy_(cs["m"].to(dev))
         if self._v is not None and cs["v"] is not None:
@@ -464,11 +471,12 @@ class ComprexOptimizer(torch.optim.Optimizer):
             for b, s in zip(self._buckets, cs["allreduce"]):
                 if s is None or b.ar is None:
                     continue
-                if cs["world_size"] == self._env.ranks:
+                if foreign:
+                    b.ar.reset()
+                elif cs["world_size"] == self._env.ranks:
                     b.ar.load_state_dict(s)
                 else:
-                    # residuals are rank-local errors: a restart with another world size keeps
-                    # what this rank had and starts the new ranks from zero
+                    # a restart with another world size keeps what this rank had
                     for dst, src in zip(b.ar._residuals(), s["residuals"]):
                         if dst.numel() == src.numel():
                             dst.copy_(src.to(dev))

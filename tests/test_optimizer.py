@@ -198,6 +198,52 @@ def scenario_optimizer_ranks(rank, world, device, overlap):
     return first, float(loss)
 
 
+def _toy_step(model, opt, rank, i, device):
+    g = torch.Generator().manual_seed(1000 * rank + i)
+    x = torch.rand(16, 1, 28, 28, generator=g).to(device)
+    y = (x.mean(dim=(1, 2, 3)) * 20).long().clamp(0, 9).to(device)
+    opt.zero_grad()
+    torch.nn.functional.cross_entropy(model(x), y).backward()
+    opt.step()
+
+
+def scenario_elastic_restart(rank, world, device, folder, phase):
+    """Save with two ranks, restart with three: old ranks keep their residual and momentum, the
+    new rank starts from another rank's file with both at zero; replicas stay identical."""
+    import os
+    env = cx.GaspiEnvironment(16 << 20, device=device)
+    torch.manual_seed(3)
+    model = LeNet5().to(device)
+    opt = ComprexOptimizer(model.parameters(), env, lr=0.05, momentum=0.9, compression_ratio=0.02, size_factor=1.0)
+    if phase == "save":
+        for i in range(5):
+            _toy_step(model, opt, rank, i, device)
+        torch.save(opt.state_dict(), os.path.join(folder, f"opt_{rank}.pt"))
+        out = (float(opt._buckets[0].ar.rests.abs().sum()), float(opt._update.abs().sum()))
+    else:
+        src = rank if os.path.exists(os.path.join(folder, f"opt_{rank}.pt")) else 0
+        sd = torch.load(os.path.join(folder, f"opt_{src}.pt"), weights_only=False)
+        assert sd["comprex"]["world_size"] == 2 and world == 3
+        opt.load_state_dict(sd)
+        rests, mom = float(opt._buckets[0].ar.rests.abs().sum()), float(opt._update.abs().sum())
+        if src == rank:
+            assert rests > 0 and mom > 0                  # this rank's own state came back
+            assert torch.equal(opt._buckets[0].ar.rests.cpu(), sd["comprex"]["allreduce"][0]["residuals"][0])
+        else:
+            assert rests == 0.0 and mom == 0.0            # a new rank starts clean
+        got = [None] * world
+        dist.all_gather_object(got, opt._master.detach().cpu())
+        assert all(torch.equal(g, got[0]) for g in got)   # same weights everywhere
+        for i in range(5, 9):
+            _toy_step(model, opt, rank, i, device)
+        dist.all_gather_object(got, opt._master.detach().cpu())
+        assert all(torch.equal(g, got[0]) for g in got), "replicas diverged after the restart"
+        out = (rests, mom)
+    env.barrier()
+    env.close()
+    return out
+
+
 def scenario_ddp_hook(rank, world, device):
     from torch.nn.parallel import DistributedDataParallel as DDP
     from comprex_b200.ddp_hook import ComprexHookState, comprex_hook
@@ -262,6 +308,13 @@ def scenario_ddp_hook(rank, world, device):
 def test_optimizer_replicas_stay_identical_cpu(world):
     out = run_ranks(world, "test_optimizer:scenario_optimizer_ranks", args=(False,))
     assert all(last < first for first, last in out)
+
+
+def test_restart_with_more_ranks_cpu(tmp_path):
+    saved = run_ranks(2, "test_optimizer:scenario_elastic_restart", args=(str(tmp_path), "save"))
+    assert all(r > 0 and m > 0 for r, m in saved)
+    loaded = run_ranks(3, "test_optimizer:scenario_elastic_restart", args=(str(tmp_path), "load"))
+    assert loaded[2] == (0.0, 0.0) and loaded[0][0] == saved[0][0]
 
 
 def test_ddp_hook_cpu():
