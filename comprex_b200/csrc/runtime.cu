@@ -223,6 +223,7 @@ struct Lanes {
 };
 Lanes g_lanes[64];
 std::mutex g_lanes_mutex;
+std::mutex g_lanes_in_use[64];   // one sequence at a time per device uses the side streams
 
 Lanes* lanes_for_current_device() {
   int dev = 0;
@@ -245,6 +246,7 @@ Lanes* lanes_for_current_device() {
 int cx_run_ops(CxOp* ops, int count, uint64_t seq, void* stream) {
   cudaStream_t main_stream = reinterpret_cast<cudaStream_t>(stream);
   Lanes* lanes = nullptr;
+  std::unique_lock<std::mutex> lanes_held;   // taken with the first side-stream op, released on return
   uint32_t open_mask = 0;      // side lanes with work that `stream` has not waited for yet
   bool forked = false;         // the fork event of the current region is recorded
   auto join = [&]() -> int {
@@ -263,8 +265,13 @@ int cx_run_ops(CxOp* ops, int count, uint64_t seq, void* stream) {
     int rc;
     if (o.lane > 0 && o.dev == CX_DEV_CUDA) {
       if (o.lane > CX_MAX_LANES) return cx_set_error("cx_run_ops: lane out of range", 0);
-      if (!lanes && !(lanes = lanes_for_current_device()))
-        return cx_set_error("cx_run_ops: side streams", (int)cudaGetLastError());
+      if (!lanes) {
+        if (!(lanes = lanes_for_current_device()))
+          return cx_set_error("cx_run_ops: side streams", (int)cudaGetLastError());
+        int dev = 0;
+        cudaGetDevice(&dev);
+        lanes_held = std::unique_lock<std::mutex>(g_lanes_in_use[dev]);
+      }
       if (!forked) {
         if (cudaEventRecord(lanes->fork, main_stream) != cudaSuccess)
           return cx_set_error("cx_run_ops: fork event", (int)cudaGetLastError());
