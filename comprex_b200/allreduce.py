@@ -78,14 +78,23 @@ class _OpSeq:
         self.arr = (_lib.Op * len(ops))(*ops)
         self.count = len(ops)
         self.graph = None
-        # a graph pays off from about half a dozen launches (measured: 3-launch sequences lose
-        # ~7 us to the cell copy and the graph's own launch, the 24-launch compressed ring gains 25 %)
-        if graph and env.dev == _lib.DEV_CUDA and self.count >= 6 and os.environ.get("COMPREX_GRAPHS", "1") != "0":
-            handle = C.c_void_p()
-            if env.lib.cx_graph_build(self.arr, self.count, C.byref(handle)) == 0:
-                self.graph = handle
-            else:
-                _log.warning("launch sequence not captured as a graph (%s); using the op list", _lib.last_error())
+        if graph:
+            self.enable_graph()
+
+    def enable_graph(self) -> None:
+        """Capture the sequence (once).  A graph pays off from about half a dozen launches
+        (measured: 3-launch sequences lose ~7 us to the cell copy and the graph's own launch, the
+        24-launch compressed ring gains 25 %)."""
+        env = self.env
+        if (self.graph is not None or getattr(self, "_no_graph", False) or env.dev != _lib.DEV_CUDA
+                or self.count < 6 or os.environ.get("COMPREX_GRAPHS", "1") == "0"):
+            return
+        handle = C.c_void_p()
+        if env.lib.cx_graph_build(self.arr, self.count, C.byref(handle)) == 0:
+            self.graph = handle
+        else:
+            _log.warning("launch sequence not captured as a graph (%s); using the op list", _lib.last_error())
+            self._no_graph = True            # not retried
 
     def run(self, seq: int) -> None:
         env = self.env
@@ -196,9 +205,13 @@ class _AllreduceBase:
                     phase()
             finally:
                 env._rec = None
-            ops = cache[key] = _OpSeq(env, rec, graph=True) if rec else False
+            ops = cache[key] = _OpSeq(env, rec) if rec else False
         else:
             self._step += 1
+            if ops and ops.graph is None:
+                # the same vector came back: worth capturing (a caller that hands over a new
+                # tensor every time never pays for a capture)
+                ops.enable_graph()
         if ops:
             ops.run(self._step)
         env.maybe_check()
