@@ -291,8 +291,15 @@ class ComprexOptimizer(torch.optim.Optimizer):
         return u
 
     def _hyper(self):
+        """The update kernels take one learning rate, momentum and weight decay for the whole flat
+        buffer: parameter groups may exist (schedulers address them) but must agree."""
         group = self.param_groups[0]
-        return float(group["lr"]), float(group["momentum"]), float(group["weight_decay"])
+        hyper = (float(group["lr"]), float(group["momentum"]), float(group["weight_decay"]))
+        for other in self.param_groups[1:]:
+            if (float(other["lr"]), float(other["momentum"]), float(other["weight_decay"])) != hyper:
+                raise ComprexError("parameter groups with different lr / momentum / weight_decay are not "
+                                   "supported: the fused update applies one setting to the flat buffer")
+        return hyper
 
     def _comm_stream(self):
         if self._comm is None:

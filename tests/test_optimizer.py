@@ -150,6 +150,26 @@ def test_checkpoint_resume_is_bit_exact(device, rule):
     env_b.close()
 
 
+def test_parameter_groups_must_agree(device):
+    env = cx.GaspiEnvironment(8 << 20, device=device)
+    a = torch.nn.Parameter(torch.randn(100, device=device))
+    b = torch.nn.Parameter(torch.randn(50, device=device))
+    opt = ComprexOptimizer([{"params": [a]}, {"params": [b]}], env, lr=0.1, momentum=0.9, compression_ratio=1.0)
+    for p in (a, b):
+        p.grad = torch.ones_like(p)
+    opt.step()                                   # two groups, same settings: fine
+    sched = torch.optim.lr_scheduler.StepLR(opt, step_size=1, gamma=0.5)
+    sched.step()                                 # schedulers change every group alike
+    for p in (a, b):
+        p.grad = torch.ones_like(p)
+    opt.step()
+    assert opt.param_groups[0]["lr"] == opt.param_groups[1]["lr"] == 0.05
+    opt.param_groups[1]["lr"] = 0.5
+    with pytest.raises(cx.ComprexError, match="parameter groups"):
+        opt.step()
+    env.close()
+
+
 def test_other_allreduce_types_and_validation(device):
     env = cx.GaspiEnvironment(8 << 20, device=device)
     with pytest.raises(ValueError):
