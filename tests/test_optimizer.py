@@ -380,3 +380,34 @@ def test_overlap_matches_no_overlap_single_gpu():
         res.append(opt._master.clone())
         env.close()
     assert torch.equal(res[0], res[1])
+
+
+@pytest.mark.gpu
+def test_no_sync_accumulates_like_plain_accumulation():
+    """Two micro-batches under ``no_sync`` plus one outside it (overlap on: the buckets go out
+    during the last backward) give the bits of plain accumulation without overlap."""
+    res = []
+    for overlap in (False, True):
+        torch.manual_seed(0)
+        env = cx.GaspiEnvironment(16 << 20, device="cuda")
+        model = torch.nn.Sequential(torch.nn.Flatten(), torch.nn.Linear(784, 96), torch.nn.ReLU(),
+                                    torch.nn.Linear(96, 10)).cuda()
+        opt = ComprexOptimizer(model.parameters(), env, lr=0.05, compression_ratio=0.05, size_factor=1.0,
+                               bucket_cap_mb=0.05, overlap=overlap)
+        assert opt.overlap == overlap and len(opt._buckets) > 1
+        for step in range(4):
+            opt.zero_grad()
+            for micro in range(3):
+                g = torch.Generator().manual_seed(10 * step + micro)
+                x = torch.rand(16, 1, 28, 28, generator=g).cuda()
+                y = torch.randint(0, 10, (16,), generator=g).cuda()
+                if micro < 2:
+                    with opt.no_sync():
+                        torch.nn.functional.cross_entropy(model(x), y).backward()
+                else:
+                    torch.nn.functional.cross_entropy(model(x), y).backward()
+            opt.step()
+        env.flush()
+        res.append(opt._master.clone())
+        env.close()
+    assert torch.equal(res[0], res[1])
