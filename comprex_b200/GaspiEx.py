@@ -18,7 +18,6 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from . import _lib
 from .common import AbstractExchange
 from ._lib import ComprexError
 from .ops import primitives as P

@@ -26,7 +26,6 @@ import socket
 import uuid
 from dataclasses import dataclass
 
-import numpy as np
 import torch
 import torch.distributed as dist
 

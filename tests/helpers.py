@@ -1,5 +1,4 @@
 """Plain PyTorch / Python restatements used as oracles by the tests."""
-import math
 
 import numpy as np
 import torch
