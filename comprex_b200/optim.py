@@ -410,6 +410,13 @@ class ComprexOptimizer(torch.optim.Optimizer):
         if self._shadow is not None:
             self._shadow.copy_(self._master)
 
+    def refresh_master(self) -> None:
+        """Take the model's current tensors as the master weights: call it after the parameters
+        were overwritten from outside (a weight broadcast, a manual edit).  With fp32 parameters
+        the model's tensors are the master buffer itself and nothing needs to happen."""
+        if self._shadow is not None:
+            self._master.copy_(self._shadow)
+
     def flush(self) -> None:
         """Apply everything still held in residuals (end of training)."""
         if not self.comprex_allreducers:

@@ -264,6 +264,50 @@ def scenario_elastic_restart(rank, world, device, folder, phase):
     return out
 
 
+def scenario_data_parallel(rank, world, device):
+    """DataParallel wrapper: same weights after construction although every rank initialised
+    differently, disjoint shards, replicas stay identical, periodic sync repairs a perturbed rank
+    (bf16 model: the fp32 master follows the synchronised weights)."""
+    from comprex_b200.parallel.data_parallel import DataParallel
+    from comprex_b200.utils import ComprexConfig
+    env = cx.GaspiEnvironment(16 << 20, device=device)
+    torch.manual_seed(100 + rank)                     # different initial weights on purpose
+    model = torch.nn.Sequential(torch.nn.Flatten(), torch.nn.Linear(784, 64), torch.nn.ReLU(),
+                                torch.nn.Linear(64, 10)).to(device).to(torch.bfloat16)
+    dp = DataParallel(model, env, config=ComprexConfig(compression_ratio=0.05, overlap=False, bucket_cap_mb=25.0),
+                      lr=0.05, momentum=0.9, sync_every=1)
+
+    def same_everywhere(t):
+        got = [None] * world
+        dist.all_gather_object(got, t.detach().float().cpu())
+        return all(torch.equal(g, got[0]) for g in got)
+
+    assert same_everywhere(dp.optimizer._master)
+    shards = [None] * world
+    dist.all_gather_object(shards, list(dp.shard(1003)))
+    flat = sum(shards, [])
+    assert len(flat) == len(set(flat)) == (1003 // world) * world
+    for i in range(4):
+        g = torch.Generator().manual_seed(50 * rank + i)
+        x = torch.rand(16, 1, 28, 28, generator=g).to(device).to(torch.bfloat16)
+        y = torch.randint(0, 10, (16,), generator=g).to(device)
+        dp.zero_grad()
+        torch.nn.functional.cross_entropy(model(x).float(), y).backward()
+        dp.step()
+    assert same_everywhere(dp.optimizer._master)
+    if rank == 1:                                      # someone tampers with one replica
+        with torch.no_grad():
+            model[1].weight.add_(1.0)
+    dp.on_epoch_begin()                                # sync_every=1: rank 0's weights everywhere
+    assert same_everywhere(model[1].weight) and same_everywhere(dp.optimizer._master)
+    assert torch.equal(dp.optimizer._master.to(torch.bfloat16), dp.optimizer._shadow)
+    sd = dp.state_dict()
+    assert set(sd) == {"model", "optimizer", "config"} and sd["config"]["compression_ratio"] == 0.05
+    env.barrier()
+    env.close()
+    return True
+
+
 def scenario_ddp_hook(rank, world, device):
     from torch.nn.parallel import DistributedDataParallel as DDP
     from comprex_b200.ddp_hook import ComprexHookState, comprex_hook
@@ -335,6 +379,10 @@ def test_restart_with_more_ranks_cpu(tmp_path):
     assert all(r > 0 and m > 0 for r, m in saved)
     loaded = run_ranks(3, "test_optimizer:scenario_elastic_restart", args=(str(tmp_path), "load"))
     assert loaded[2] == (0.0, 0.0) and loaded[0][0] == saved[0][0]
+
+
+def test_data_parallel_wrapper_cpu():
+    assert all(run_ranks(2, "test_optimizer:scenario_data_parallel"))
 
 
 def test_ddp_hook_cpu():
