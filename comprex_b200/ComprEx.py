@@ -94,11 +94,19 @@ class ThresholdTopK(_Threshold):
     """
     kind = "topk"
 
-    def __init__(self, topK: float, default_subsamples: int = 1000, subsample_factor: float = 10.0):
+    EXACT = 2 ** 31 - 128      # "sample" larger than any vector: every element is looked at
+
+    def __init__(self, topK: float, default_subsamples: int = 1000, subsample_factor: float = 10.0,
+                 exact: bool = False):
         super().__init__()
         if topK > 1.0 or topK < 0.0:
             raise ComprexError("topK value must be between 0.0 and 1.0!")
         self.topK = float(topK)
+        # exact=True: the threshold is the true ceil(n*topK)-th largest magnitude (a select over
+        # the whole vector, several passes over it) instead of the reference's sampled estimate
+        self.exact = bool(exact)
+        if exact:
+            default_subsamples = self.EXACT
         self.default_subsamples = int(default_subsamples)
         self.subsample_factor = float(subsample_factor)
         self._cell = None

@@ -374,6 +374,17 @@ class _ComprexAllreduceBase(_AllreduceBase):
         self.compression_ratio = float(compression_ratio)
         self.__dict__.pop("_replay_cache", None)      # the ratio is part of the recorded launches
 
+    def set_exact_topk(self, exact: bool = True) -> None:
+        """Threshold from a select over the whole vector (exactly top-k) instead of the sampled
+        estimate of the reference; costs a few extra passes over the vector per call."""
+        if exact:
+            self._sampling = getattr(self, "_sampling", (self._subsamples, self._sample_factor))
+            self._subsamples = 2 ** 31 - 128
+        elif hasattr(self, "_sampling"):
+            self._subsamples, self._sample_factor = self._sampling
+        self.__dict__.pop("_replay_cache", None)
+        self.__dict__.pop("_seq_cache", None)
+
     def reset(self):
         for r in self._residuals():
             r.zero_()

@@ -74,6 +74,25 @@ def test_threshold_matches_reference_rule(device, n, ratio):
     env.close()
 
 
+@pytest.mark.parametrize("n,ratio", [(999, 0.05), (30000, 0.01), (150001, 0.002)])
+def test_exact_topk_threshold(device, n, ratio):
+    """exact=True: the threshold is the ceil(n*ratio)-th largest magnitude of the whole vector
+    (for n above the shared-memory key cache the kernel re-reads the vector in every pass)."""
+    torch.manual_seed(n)
+    env = cx.GaspiEnvironment(1 << 16, device=device)
+    g, r = torch.randn(n).to(device), (0.3 * torch.randn(n)).to(device)
+    thr = cx.ThresholdTopK(ratio, exact=True)
+    thr.prepare_with(r, g)
+    mags = (g + r).abs().cpu().sort(descending=True).values
+    k = int(torch.ceil(torch.tensor(float(n) * ratio)).item())
+    assert thr.getThreshold() == float(mags[k - 1])
+    comp = P.Compressor(env, n)
+    thr._launch(comp, g, r, n)
+    assert comp.thr.item() == float(mags[k - 1])
+    assert int(((g + r).abs() > comp.thr).sum()) == k - 1      # strict ">" of the pair codec
+    env.close()
+
+
 def test_threshold_reference_vector(device):
     """test/threshold.cpp:58-85: 100 ints, top 10 % -> threshold 90, 10 elements pass with >=."""
     from helpers import alt_ramp
