@@ -714,25 +714,94 @@ class Comprex_AllToOneAllreduce(_ComprexAllreduceBase):
     The chief accumulates densely; the broadcast has its own residual so that
     what the chief's sum loses to the threshold is sent later.  Workers'
     vectors are overwritten with the sparse broadcast.  The reference sends
-    both legs one call late (FastComprEx double buffering); here both legs are
-    fresh, ``FastComprex`` offers the stale behaviour as an engine.
-    ``flush`` drains the workers' residuals into the chief and does not
-    broadcast, like the reference.
+    both legs one call late (FastComprEx double buffering, src/comprEx.tpp:428-448);
+    here both legs are fresh by default and ``stale=True`` reproduces the
+    reference: every call first forwards the payload compressed during the
+    previous call (an empty one the first time) and then compresses the current
+    input into a local staging slot.
+    ``flush`` drains the workers' residuals (and their staged payloads) into the
+    chief and does not broadcast, like the reference.
     """
 
-    def setup_connections(self, size, tag=0, chiefRank=0, compression_ratio=0.01, size_factor=1.0):
+    def setup_connections(self, size, tag=0, chiefRank=0, compression_ratio=0.01, size_factor=1.0, stale=False):
         self._setup_compressed(size, compression_ratio, size_factor, False)
         env = self._env
         self.chiefRank = int(chiefRank)
+        self.stale = bool(stale)
         self._subsamples, self._sample_factor = 1000, 10.0  # default sampling (src/allreduce.tpp:142)
         self.cap = _cap_for(size, size_factor)
         self._rs = [[P.SparseSlot.create(env, size, self.cap) for _ in range(2)] for _ in range(env.ranks)]
         self._bc = [P.SparseSlot.create(env, size, self.cap) for _ in range(2)]
         self._comp = P.Compressor(env, size)
         self.rests = torch.zeros(size, dtype=torch.float32, device=env.device)
+        if self.stale:
+            self._stage = [P.SparseSlot.create(env, size, self.cap) for _ in range(2)]   # local staging
+            self._stage_seq, self._first = 0, True
+            self._replay = False        # forwarding is not part of recorded sequences
 
     def _residuals(self):
         return [self.rests]
+
+    def reset(self):
+        super().reset()
+        if self.stale:
+            self._first = True
+
+    # ---- one-call-late mode -------------------------------------------------------------------
+    def _send_pending(self, targets, seq) -> None:
+        """Forward what the previous call staged; an empty payload on the first call."""
+        env = self._env
+        if self._first:
+            self._comp.set_threshold(3.0e38)                 # nothing passes, the residual is untouched
+            self._comp.compress(None, self.rests, self.size, self.cap, seq, targets)
+            self._first = False
+        else:
+            ep = self._stage[self._stage_seq & 1].endpoint(env)
+            P.forward(env, ep, self._stage_seq, targets, seq, self.cap, self._counters, self._status)
+
+    def _stage_new(self, t) -> None:
+        env = self._env
+        self._stage_seq += 1
+        self._comp.threshold_topk(t, self.rests, self.size, self.compression_ratio, self._subsamples,
+                                  self._sample_factor)
+        self._comp.compress(t, self.rests, self.size, self.cap, self._stage_seq,
+                            P.make_targets([self._stage[self._stage_seq & 1].endpoint(env)]))
+
+    def _plan_stale(self, t):
+        env, me, chief = self._env, self._env.rank, self.chiefRank
+        workers = [r for r in range(env.ranks) if r != chief]
+        self._step += 1
+        seq, par = self._step, self._step & 1
+
+        def send():
+            if me != chief:
+                self._send_pending(P.make_targets([self._rs[me][par].endpoint(env, chief)]), seq)
+                self._stage_new(t)
+
+        def reduce():
+            if me != chief or not workers:
+                return
+            src = P.make_sources([self._rs[w][par].endpoint(env) for w in workers], [seq] * len(workers))
+            P.apply_sparse(env, src, self.size, P.args_add(t), self._status)
+            self._send_pending(P.make_targets([self._bc[par].endpoint(env, w) for w in workers]), seq)
+            self._stage_new(t)
+
+        def recv():
+            if me != chief:
+                P.apply_sparse(env, P.make_sources([self._bc[par].endpoint(env)], [seq]), self.size,
+                               P.args_set(t), self._status)
+        return [send, reduce, recv]
+
+    def _fold_pending(self):
+        """Before a flush: a worker's staged payload goes back into its residual; the chief's
+        staged broadcast is dropped with its residual (the reference resets it)."""
+        env = self._env
+        if self.stale and not self._first and env.rank != self.chiefRank:
+            ep = self._stage[self._stage_seq & 1].endpoint(env)
+            P.apply_sparse(env, P.make_sources([ep], [self._stage_seq]), self.size, P.args_add(self.rests),
+                           self._status)
+        if self.stale:
+            self._first = True
 
     def _plan_common(self, t, flush, rounds=1):
         env, me, chief = self._env, self._env.rank, self.chiefRank
@@ -774,7 +843,10 @@ class Comprex_AllToOneAllreduce(_ComprexAllreduceBase):
         return phases
 
     def _plan_apply(self, t):
+        if self.stale:
+            return self._plan_stale(t)
         return self._plan_common(t, flush=False)
 
     def _plan_flush(self, t):
-        return self._plan_common(t, True, rounds=self._flush_rounds(self.size, self.cap)) + [self.reset]
+        return ([self._fold_pending] + self._plan_common(t, True, rounds=self._flush_rounds(self.size, self.cap))
+                + [self.reset])

@@ -46,7 +46,8 @@ def test_dense_allreduce(world, cls, kw, dtype):
 
 @pytest.mark.parametrize("cls,kw", [(cx.Comprex_BigRingAllreduce, {}), (cx.Comprex_RingAllreduce, {}),
                                     (cx.Comprex_RingAllreduce, dict(schedule="hops")),
-                                    (cx.Comprex_AllToOneAllreduce, dict(chiefRank=0))])
+                                    (cx.Comprex_AllToOneAllreduce, dict(chiefRank=0)),
+                                    (cx.Comprex_AllToOneAllreduce, dict(chiefRank=0, stale=True))])
 @pytest.mark.parametrize("n,ratio", [(50, 0.01), (1000, 0.01), (20011, 0.05)])
 def test_compressed_allreduce_conserves_sum(world, cls, kw, n, ratio):
     P, dev = world.size, world.device
@@ -72,6 +73,33 @@ def test_compressed_allreduce_conserves_sum(world, cls, kw, n, ratio):
     for a in ars:
         for r in a._residuals():
             assert float(r.abs().sum()) == 0.0
+
+
+def test_stale_alltoone_is_one_call_late(device):
+    """stale=True (the reference's FastComprEx legs): what a call compresses arrives with the next
+    call.  With a zero vector on the chief, its result of call s equals the fresh mode's result of
+    call s-1 bit for bit, and the first call delivers nothing."""
+    n, P = 6000, 3
+    outs = {}
+    for stale in (False, True):
+        w = cx.LoopbackWorld(P, device=device, timeout_ms=500)
+        ars = [cx.Comprex_AllToOneAllreduce(e) for e in w.envs]
+        for a in ars:
+            a.setup_connections(n, 1, 0, 0.05, 3.0, stale=stale)
+        chief_after, worker_after = [], []
+        for step in range(5):
+            xs = [torch.zeros(n, device=device)] + [
+                torch.randn(n, generator=torch.Generator().manual_seed(10 * step + r)).to(device) for r in range(1, P)]
+            w.run(ars, "apply", [(x,) for x in xs])
+            chief_after.append(xs[0].cpu().clone())
+            worker_after.append(xs[1].cpu().clone())
+        outs[stale] = (chief_after, worker_after)
+        w.close()
+    fresh, stale = outs[False][0], outs[True][0]
+    assert float(stale[0].abs().sum()) == 0.0 and float(fresh[0].abs().sum()) > 0.0
+    for s in range(1, 5):
+        assert torch.equal(stale[s], fresh[s - 1])
+    assert float(outs[True][1][0].abs().sum()) == 0.0          # first broadcast is empty too
 
 
 def test_ring_schedules_agree_on_two_ranks(device):
