@@ -35,6 +35,8 @@ class ComprexConfig:
     topology: str = "comprex_bigring"
     consistent: bool = True                  # replicas apply exactly what was transmitted (bit-identical)
     stale: bool = False                      # FastComprEx semantics: payloads arrive one call late
+    ring_schedule: str = "direct"            # compressed Ring: "direct" stores or the reference's "hops"
+    exact_topk: bool = False                 # threshold from a select over the whole vector
     two_shot_bytes: int = 8 << 20            # dense BigRing: reduce-scatter + allgather above this size
     dense_fallback_bytes: int = 64 << 10     # DDP hook: buckets below this go out dense
     capacity_slack: float = 2.0              # DDP hook: slot room over the expected survivors
@@ -61,6 +63,8 @@ class ComprexConfig:
             raise ValueError("compressor must be 'pairs', 'rle' or 'none'")
         if self.rule not in ("sgd", "adamw"):
             raise ValueError("rule must be 'sgd' or 'adamw'")
+        if self.ring_schedule not in ("direct", "hops"):
+            raise ValueError("ring_schedule must be 'direct' or 'hops'")
 
     # ---- sources of overrides -------------------------------------------------------------------
     @staticmethod
@@ -118,7 +122,8 @@ class ComprexConfig:
     def threshold_object(self):
         from .. import ComprEx as E
         if self.threshold == "topk":
-            return E.ThresholdTopK(self.compression_ratio, self.default_subsamples, self.subsample_factor)
+            return E.ThresholdTopK(self.compression_ratio, self.default_subsamples, self.subsample_factor,
+                                   exact=self.exact_topk)
         if self.threshold == "const":
             return E.ThresholdConst(self.threshold_value)
         return E.ThresholdNone()
@@ -143,16 +148,21 @@ class ComprexConfig:
                "comprex_alltoone": A.Comprex_AllToOneAllreduce, "bigring": A.BigRingAllreduce,
                "ring": A.RingAllreduce, "alltoone": A.AllToOneAllreduce}[self.topology]
         ar = cls(env)
-        if self.topology == "comprex_bigring" or self.topology == "comprex_ring":
+        if self.topology == "comprex_bigring":
             ar.setup_connections(size, tag, self.compression_ratio, self.size_factor, consistent=self.consistent)
+        elif self.topology == "comprex_ring":
+            ar.setup_connections(size, tag, self.compression_ratio, self.size_factor, consistent=self.consistent,
+                                 schedule=self.ring_schedule)
         elif self.topology == "comprex_alltoone":
-            ar.setup_connections(size, tag, 0, self.compression_ratio, self.size_factor)
+            ar.setup_connections(size, tag, 0, self.compression_ratio, self.size_factor, stale=self.stale)
         elif self.topology == "alltoone":
             ar.setup_connections(size, tag, 0)
         elif self.topology == "bigring":
             ar.setup_connections(size, tag, two_shot_bytes=self.two_shot_bytes)
         else:
             ar.setup_connections(size, tag)
+        if self.exact_topk and ar.compressed:
+            ar.set_exact_topk(True)
         return ar
 
     def optimizer(self, params, env, **kwargs):

@@ -45,6 +45,13 @@ def test_config_builds_objects(device):
     opt.step()
     eng = ComprexConfig(compressor="rle", threshold="const", threshold_value=0.5, segment_bytes=8 << 20).engine(env, 100)
     assert eng.compressor.kind == "rle" and eng.threshold.getThreshold() == 0.5
+    ring = ComprexConfig(topology="comprex_ring", ring_schedule="hops", exact_topk=True, segment_bytes=8 << 20)
+    ar2 = ring.allreduce(env, 3000)
+    assert ar2.schedule == "hops" and ar2._subsamples > 10 ** 9 and ring.threshold_object().exact
+    a2o = ComprexConfig(topology="comprex_alltoone", stale=True, segment_bytes=8 << 20).allreduce(env, 3000)
+    assert a2o.stale
+    with pytest.raises(ValueError):
+        ComprexConfig(ring_schedule="tree")
     state = cfg.hook_state(env)
     assert state.compression_ratio == 0.05 and state.dense_fallback_bytes == 64 << 10
     env.close()
