@@ -1,0 +1,35 @@
+// Oracle built from the reference's own headers (included unmodified through -I): reads
+// n, top-k, g[n], r[n] from a binary file, runs ThresholdTopK::prepare_with / get_threshold and
+// CompressorIndexPairs::compress_add_update, writes threshold, nnz, pairs and the new residual.
+// Used by tests/test_reference_oracle.py when COMPREX_REFERENCE points at the reference's tree.
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
+
+#include "compressor.hxx"
+
+int main(int argc, char** argv) {
+  if (argc != 3) return 2;
+  FILE* in = fopen(argv[1], "rb");
+  if (!in) return 3;
+  int n = 0;
+  float ratio = 0.f;
+  if (fread(&n, 4, 1, in) != 1 || fread(&ratio, 4, 1, in) != 1) return 4;
+  std::vector<float> g(n), r(n);
+  if (fread(g.data(), 4, n, in) != (size_t)n || fread(r.data(), 4, n, in) != (size_t)n) return 5;
+  fclose(in);
+  ThresholdTopK<float> thr(ratio);
+  thr.prepare_with(r.data(), n, g.data(), n);
+  const float cut = thr.get_threshold();
+  std::vector<char> buf((size_t)n * 8 + 64);
+  CompressorIndexPairs<float> comp;
+  const int bytes = comp.compress_add_update(buf.data(), r.data(), n, g.data(), n, cut);
+  FILE* out = fopen(argv[2], "wb");
+  if (!out) return 6;
+  fwrite(&cut, 4, 1, out);
+  fwrite(&bytes, 4, 1, out);
+  fwrite(buf.data(), 1, bytes, out);
+  fwrite(r.data(), 4, n, out);
+  fclose(out);
+  return 0;
+}
