@@ -1,6 +1,7 @@
 // Oracle built from the reference's own headers (included unmodified through -I): reads
-// n, top-k, g[n], r[n] from a binary file, runs ThresholdTopK::prepare_with / get_threshold and
-// CompressorIndexPairs::compress_add_update, writes threshold, nnz, pairs and the new residual.
+// n, top-k, g[n], r[n], base[n] from a binary file, runs ThresholdTopK::prepare_with / get_threshold,
+// CompressorIndexPairs::compress_add_update, ::add (into base) and ::decompress, and writes threshold,
+// payload, the new residual, base after the scatter-add and the decompressed vector.
 // Used by tests/test_reference_oracle.py when COMPREX_REFERENCE points at the reference's tree.
 #include <cstdio>
 #include <cstdlib>
@@ -15,8 +16,9 @@ int main(int argc, char** argv) {
   int n = 0;
   float ratio = 0.f;
   if (fread(&n, 4, 1, in) != 1 || fread(&ratio, 4, 1, in) != 1) return 4;
-  std::vector<float> g(n), r(n);
-  if (fread(g.data(), 4, n, in) != (size_t)n || fread(r.data(), 4, n, in) != (size_t)n) return 5;
+  std::vector<float> g(n), r(n), base(n), dec(n, 7.f);
+  if (fread(g.data(), 4, n, in) != (size_t)n || fread(r.data(), 4, n, in) != (size_t)n ||
+      fread(base.data(), 4, n, in) != (size_t)n) return 5;
   fclose(in);
   ThresholdTopK<float> thr(ratio);
   thr.prepare_with(r.data(), n, g.data(), n);
@@ -24,12 +26,16 @@ int main(int argc, char** argv) {
   std::vector<char> buf((size_t)n * 8 + 64);
   CompressorIndexPairs<float> comp;
   const int bytes = comp.compress_add_update(buf.data(), r.data(), n, g.data(), n, cut);
+  comp.add(base.data(), n, buf.data());
+  comp.decompress(dec.data(), n, buf.data());
   FILE* out = fopen(argv[2], "wb");
   if (!out) return 6;
   fwrite(&cut, 4, 1, out);
   fwrite(&bytes, 4, 1, out);
   fwrite(buf.data(), 1, bytes, out);
   fwrite(r.data(), 4, n, out);
+  fwrite(base.data(), 4, n, out);
+  fwrite(dec.data(), 4, n, out);
   fclose(out);
   return 0;
 }

@@ -3,7 +3,8 @@
 When ``COMPREX_REFERENCE`` names the root of the reference's source tree, ``reference_oracle.cpp``
 is compiled against its header-only ``src/threshold.hxx`` / ``src/compressor.hxx`` (unmodified) and
 the host back end must reproduce, bit for bit, the threshold of ``ThresholdTopK::prepare_with``, the
-(index, value) pairs of ``CompressorIndexPairs::compress_add_update`` and the residual it leaves.
+(index, value) pairs of ``CompressorIndexPairs::compress_add_update``, the residual it leaves, and the
+results of ``::add`` (scatter-add) and ``::decompress``.
 (The CUDA kernels are tied to the host back end bit for bit by test_primitives.py.)  Without the
 variable the tests are skipped."""
 import os
@@ -37,12 +38,13 @@ def oracle(tmp_path_factory):
 @pytest.mark.parametrize("ratio", [0.1, 0.01, 0.001])
 def test_threshold_pairs_and_residual_match_the_reference(oracle, tmp_path, n, ratio):
     torch.manual_seed(n)
-    g, r0 = torch.randn(n), 0.5 * torch.randn(n)
+    g, r0, base = torch.randn(n), 0.5 * torch.randn(n), torch.randn(n)
     fin, fout = str(tmp_path / "in.bin"), str(tmp_path / "out.bin")
     with open(fin, "wb") as f:
         f.write(struct.pack("<if", n, ratio))
         f.write(g.numpy().tobytes())
         f.write(r0.numpy().tobytes())
+        f.write(base.numpy().tobytes())
     subprocess.run([oracle, fin, fout], check=True)
     raw = open(fout, "rb").read()
     ref_thr = np.frombuffer(raw, dtype=np.float32, count=1)[0]
@@ -52,7 +54,8 @@ def test_threshold_pairs_and_residual_match_the_reference(oracle, tmp_path, n, r
     pairs = np.frombuffer(payload, dtype=np.int32, offset=8).reshape(-1, 2)
     ref_idx = torch.from_numpy(pairs[:, 0].copy())
     ref_val = torch.from_numpy(pairs[:, 1].copy().view(np.float32))
-    ref_r = torch.from_numpy(np.frombuffer(raw, dtype=np.float32, offset=8 + nbytes).copy())
+    tail = torch.from_numpy(np.frombuffer(raw, dtype=np.float32, offset=8 + nbytes).copy())
+    ref_r, ref_add, ref_dec = tail[:n], tail[n:2 * n], tail[2 * n:3 * n]
     assert ref_n == n and ref_nnz == ref_idx.numel()
 
     world = cx.LoopbackWorld(2, device="cpu", timeout_ms=200)
@@ -67,4 +70,12 @@ def test_threshold_pairs_and_residual_match_the_reference(oracle, tmp_path, n, r
     assert hdr.nnz == ref_nnz
     assert torch.equal(idx.to(torch.int32), ref_idx) and torch.equal(val, ref_val)
     assert torch.equal(r, ref_r)
+    status = e1.new_status("oracle")
+    src = P.make_sources([slot.endpoint(e1)], [1])
+    acc = base.clone()
+    P.apply_sparse(e1, src, n, P.args_add(acc), status)
+    assert torch.equal(acc, ref_add)
+    dec = torch.full((n,), 7.0)
+    P.apply_sparse(e1, src, n, P.args_set(dec), status)
+    assert torch.equal(dec, ref_dec) and status.value == 0
     world.close()
