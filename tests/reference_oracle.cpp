@@ -10,7 +10,7 @@
 #include "compressor.hxx"
 
 int main(int argc, char** argv) {
-  if (argc != 3) return 2;
+  if (argc < 3) return 2;
   FILE* in = fopen(argv[1], "rb");
   if (!in) return 3;
   int n = 0;
@@ -20,12 +20,19 @@ int main(int argc, char** argv) {
   if (fread(g.data(), 4, n, in) != (size_t)n || fread(r.data(), 4, n, in) != (size_t)n ||
       fread(base.data(), 4, n, in) != (size_t)n) return 5;
   fclose(in);
+  // mode (argv[3], default 0): 0 compress_add_update(r, g), 1 compress_update(r), 2 compress(g)
+  const int mode = argc > 3 ? atoi(argv[3]) : 0;
   ThresholdTopK<float> thr(ratio);
-  thr.prepare_with(r.data(), n, g.data(), n);
+  if (mode == 0) thr.prepare_with(r.data(), n, g.data(), n);
+  else if (mode == 1) thr.prepare(r.data(), n);
+  else thr.prepare(g.data(), n);
   const float cut = thr.get_threshold();
   std::vector<char> buf((size_t)n * 8 + 64);
   CompressorIndexPairs<float> comp;
-  const int bytes = comp.compress_add_update(buf.data(), r.data(), n, g.data(), n, cut);
+  int bytes;
+  if (mode == 0) bytes = comp.compress_add_update(buf.data(), r.data(), n, g.data(), n, cut);
+  else if (mode == 1) bytes = comp.compress_update(buf.data(), r.data(), n, cut);
+  else bytes = comp.compress(buf.data(), g.data(), n, cut);
   comp.add(base.data(), n, buf.data());
   comp.decompress(dec.data(), n, buf.data());
   FILE* out = fopen(argv[2], "wb");

@@ -34,9 +34,10 @@ def oracle(tmp_path_factory):
     return exe
 
 
+@pytest.mark.parametrize("mode", [0, 1, 2], ids=["add_update", "update", "compress"])
 @pytest.mark.parametrize("n", [50, 999, 1000, 4097, 100003, 1 << 20])
 @pytest.mark.parametrize("ratio", [0.1, 0.01, 0.001])
-def test_threshold_pairs_and_residual_match_the_reference(oracle, tmp_path, n, ratio):
+def test_threshold_pairs_and_residual_match_the_reference(oracle, tmp_path, n, ratio, mode):
     torch.manual_seed(n)
     g, r0, base = torch.randn(n), 0.5 * torch.randn(n), torch.randn(n)
     fin, fout = str(tmp_path / "in.bin"), str(tmp_path / "out.bin")
@@ -45,7 +46,7 @@ def test_threshold_pairs_and_residual_match_the_reference(oracle, tmp_path, n, r
         f.write(g.numpy().tobytes())
         f.write(r0.numpy().tobytes())
         f.write(base.numpy().tobytes())
-    subprocess.run([oracle, fin, fout], check=True)
+    subprocess.run([oracle, fin, fout, str(mode)], check=True)
     raw = open(fout, "rb").read()
     ref_thr = np.frombuffer(raw, dtype=np.float32, count=1)[0]
     nbytes = struct.unpack_from("<i", raw, 4)[0]
@@ -63,9 +64,10 @@ def test_threshold_pairs_and_residual_match_the_reference(oracle, tmp_path, n, r
     slot = [P.SparseSlot.create(e, n, n) for e in world.envs][1]
     comp = P.Compressor(e0, n)
     r = r0.clone()
-    comp.threshold_topk(g, r, n, ratio)
+    g_arg, r_arg = (g, r) if mode == 0 else ((None, r) if mode == 1 else (g, None))
+    comp.threshold_topk(g_arg, r_arg, n, ratio)
     assert comp.thr.numpy().view(np.uint32)[0] == np.float32(ref_thr).view(np.uint32)      # same bits
-    comp.compress(g, r, n, n, 1, P.make_targets([slot.endpoint(e0, 1)]))
+    comp.compress(g_arg, r_arg, n, n, 1, P.make_targets([slot.endpoint(e0, 1)]))
     hdr, idx, val, _ = read_pairs(e1, slot)
     assert hdr.nnz == ref_nnz
     assert torch.equal(idx.to(torch.int32), ref_idx) and torch.equal(val, ref_val)
