@@ -134,7 +134,7 @@ class ComprexOptimizer(torch.optim.Optimizer):
     def __init__(self, params, gaspi_env, lr=0.01, momentum=0.9, compression_ratio=0.01, nesterov=False,
                  allreduce_type="comprex_bigring", size_factor=1.0, logging=False, pre_clipnorm=5.0,
                  weight_decay=0.0, local_momentum=True, rule="sgd", betas=(0.9, 0.999), eps=1e-8,
-                 learning_rate=None, bucket_cap_mb=None, overlap=False):
+                 learning_rate=None, bucket_cap_mb=None, overlap=False, consistent=True):
         if learning_rate is not None:
             lr = learning_rate
         if not 0 <= momentum <= 1:
@@ -158,7 +158,12 @@ class ComprexOptimizer(torch.optim.Optimizer):
         self.betas, self.eps = betas, eps
         self.momentum_correction = 1.0
         self._t = 0
-        self._fused = allreduce_type == "comprex_bigring"
+        # consistent=False is the reference's rule for the compressed BigRing (a rank applies its
+        # own update densely and the peers' sparsely, keras/comprex_optimizer.py:117-133 with
+        # src/allreduce.tpp:649-681): replicas drift apart by what each keeps in its residual.  It
+        # runs through the generic path (allreduce in place, then a tensor update).
+        self.consistent = bool(consistent)
+        self._fused = allreduce_type == "comprex_bigring" and self.consistent
         if (bucket_cap_mb or overlap) and not self._fused:
             raise ComprexError("buckets and overlap need allreduce_type='comprex_bigring'")
 
@@ -232,7 +237,7 @@ class ComprexOptimizer(torch.optim.Optimizer):
         cls = _TYPES[name]
         ar = cls(self._env)
         if name == "comprex_bigring":
-            ar.setup_connections(size, 1, self.compression_ratio, self.size_factor, consistent=True)
+            ar.setup_connections(size, 1, self.compression_ratio, self.size_factor, consistent=self.consistent)
         elif name == "comprex_ring":
             ar.setup_connections(size, 1, self.compression_ratio, self.size_factor)
         elif name == "comprex_alltoone":

@@ -49,6 +49,8 @@ def main():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--train-samples", type=int, default=60000)
     ap.add_argument("--model", default="lenet5", choices=["lenet5", "reference"])
+    ap.add_argument("--reference-semantics", action="store_true",
+                    help="also run comprex_bigring the reference's way (own update dense, peers' sparse)")
     args = ap.parse_args()
     cx.initGaspiCxx()
     env = cx.GaspiEnvironment(64 << 20)
@@ -57,12 +59,16 @@ def main():
     shard = slice(rank * (len(xtr) // ranks), (rank + 1) * (len(xtr) // ranks))   # one shard per rank
     xtr, ytr = xtr[shard], ytr[shard]
     runs = [("ring", 1.0), ("bigring", 1.0)] + [(k, r) for r in (1e-2, 1e-3) for k in ("comprex_ring", "comprex_bigring")]
-    for kind, ratio in runs:
+    runs = [(k, r, True) for k, r in runs]
+    if args.reference_semantics:
+        runs += [("comprex_bigring", r, False) for r in (1e-2, 1e-3)]
+    for kind, ratio, consistent in runs:
         torch.manual_seed(0)
         model = (LeNet5() if args.model == "lenet5" else LeNetReference()).to(dev)
         BroadcastInitWeights(0, env).on_train_begin(model)
         opt = ComprexOptimizer(model.parameters(), env, lr=0.01 * ranks, momentum=0.9, compression_ratio=ratio,
-                               allreduce_type=kind, size_factor=3.0, local_momentum=kind.startswith("comprex"))
+                               allreduce_type=kind, size_factor=3.0, local_momentum=kind.startswith("comprex"),
+                               consistent=consistent)
         t0 = time.time()
         for epoch in range(args.epochs):
             perm = torch.randperm(len(xtr), device=dev, generator=torch.Generator(device=dev).manual_seed(epoch))
@@ -75,7 +81,8 @@ def main():
             with torch.no_grad():
                 acc = float((model(xte).argmax(1) == yte).float().mean())
             if rank == 0:
-                print(f"{kind} ratio {ratio:g} epoch {epoch + 1}: loss {loss.item():.4f} test accuracy {acc:.4f} "
+                tag = kind if consistent else kind + " (reference semantics)"
+                print(f"{tag} ratio {ratio:g} epoch {epoch + 1}: loss {loss.item():.4f} test accuracy {acc:.4f} "
                       f"time {time.time() - t0:.1f} s", flush=True)
         env.barrier()
     env.close()

@@ -150,6 +150,23 @@ def test_checkpoint_resume_is_bit_exact(device, rule):
     env_b.close()
 
 
+def test_reference_semantics_option(device):
+    """consistent=False: the reference's rule for the compressed BigRing - the rank's own update is
+    applied densely (nothing of it waits in a residual for the weights of this rank)."""
+    env = cx.GaspiEnvironment(8 << 20, device=device)
+    params = _const_grad_model(device)
+    w0 = [p.detach().clone() for p in params]
+    cs = [torch.randn_like(p) for p in params]
+    opt = ComprexOptimizer(params, env, lr=0.1, momentum=0.0, compression_ratio=0.01, size_factor=3.0,
+                           pre_clipnorm=None, consistent=False)
+    assert not opt._fused
+    _set_grads(opt, params, cs)
+    opt.step()
+    for p, w, c in zip(params, w0, cs):          # single rank: w -= lr * g, in full, immediately
+        torch.testing.assert_close(p.detach(), w - 0.1 * c, rtol=1e-6, atol=1e-6)
+    env.close()
+
+
 def test_parameter_groups_must_agree(device):
     env = cx.GaspiEnvironment(8 << 20, device=device)
     a = torch.nn.Parameter(torch.randn(100, device=device))
