@@ -2,7 +2,8 @@
 // compiled unmodified against the GaspiCxx stand-in of baseline/gaspicxx_shim) on float vectors
 // read from files, and writes the vector after every call.  Used by
 // tests/test_reference_allreduce_parity.py when COMPREX_REFERENCE names the reference's tree.
-//   argv: variant(bigring|ring|alltoone) n ratio size_factor runs in_prefix out_prefix
+//   argv: variant(bigring|ring|alltoone|dense_bigring|dense_ring|dense_alltoone) n ratio size_factor runs
+//         in_prefix out_prefix
 // Input of rank r for call k: <in_prefix>_r<r>_k<k>.bin (n floats); output likewise.
 #include <cstdio>
 #include <cstdlib>
@@ -46,9 +47,21 @@ int main(int argc, char** argv) {
     auto* a = new Comprex_RingAllreduce<float>(&env);
     a->setupConnections(n, 1, ratio, size_factor);
     ar = a;
-  } else {
+  } else if (variant == "alltoone") {
     auto* a = new Comprex_AllToOneAllreduce<float>(&env);
     a->setupConnections(n, 1, 0, ratio, size_factor);
+    ar = a;
+  } else if (variant == "dense_bigring") {
+    auto* a = new BigRingAllreduce<float>(&env);
+    a->setupConnections(n, 1);
+    ar = a;
+  } else if (variant == "dense_ring") {
+    auto* a = new RingAllreduce<float>(&env);
+    a->setupConnections(n, 1);
+    ar = a;
+  } else {
+    auto* a = new AllToOneAllreduce<float>(&env);
+    a->setupConnections(n, 1, 0);
     ar = a;
   }
   for (int k = 0; k < runs; ++k) {

@@ -92,3 +92,38 @@ def test_allreduce_matches_reference_call_by_call(driver, tmp_path, variant, P, 
                           f"max |diff| {float((xs[r] - ref).abs().max())}")
     assert changed > 0          # the calls did exchange something
     world.close()
+
+
+@pytest.mark.parametrize("variant", ["dense_bigring", "dense_ring", "dense_alltoone"])
+@pytest.mark.parametrize("P", [2, 3, 4])
+def test_dense_allreduce_matches_reference(driver, tmp_path, variant, P):
+    """The dense classes: same sums as the reference's (bit for bit where the order of the
+    additions is the same - BigRing, AllToOne; to rounding for the Ring, whose direct
+    reduce-scatter adds in rank order instead of ring order)."""
+    n, runs = 30011, 2
+    pin, pout = str(tmp_path / "in"), str(tmp_path / "out")
+    inputs = {}
+    for r in range(P):
+        for k in range(runs):
+            x = torch.randn(n, generator=torch.Generator().manual_seed(77 * r + k))
+            inputs[(r, k)] = x
+            x.numpy().tofile(f"{pin}_r{r}_k{k}.bin")
+    run_reference(driver, variant, P, n, 1.0, 1.0, runs, pin, pout)
+    world = cx.LoopbackWorld(P, device="cpu", timeout_ms=2000)
+    cls = {"dense_bigring": cx.BigRingAllreduce, "dense_ring": cx.RingAllreduce, "dense_alltoone": cx.AllToOneAllreduce}[variant]
+    ars = [cls(e) for e in world.envs]
+    for a in ars:
+        if variant == "dense_alltoone":
+            a.setup_connections(n, 1, 0)
+        else:
+            a.setup_connections(n, 1)
+    for k in range(runs):
+        xs = [inputs[(r, k)].clone() for r in range(P)]
+        world.run(ars, "apply", [(x,) for x in xs])
+        for r in range(P):
+            ref = torch.from_numpy(np.fromfile(f"{pout}_r{r}_k{k}.bin", dtype=np.float32))
+            if variant == "dense_ring" and P > 2:
+                torch.testing.assert_close(xs[r], ref, rtol=1e-5, atol=1e-5)
+            else:
+                assert torch.equal(xs[r], ref), f"rank {r}, call {k}"
+    world.close()
