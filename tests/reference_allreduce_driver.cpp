@@ -4,7 +4,8 @@
 // tests/test_reference_allreduce_parity.py when COMPREX_REFERENCE names the reference's tree.
 //   argv: variant(bigring|ring|alltoone|dense_bigring|dense_ring|dense_alltoone) n ratio size_factor runs
 //         in_prefix out_prefix
-// Input of rank r for call k: <in_prefix>_r<r>_k<k>.bin (n floats); output likewise.
+// Input of rank r for call k: <in_prefix>_r<r>_k<k>.bin (n floats); output likewise.  For the
+// compressed variants one more vector (k = runs) goes through flush().
 #include <cstdio>
 #include <cstdlib>
 #include <string>
@@ -70,6 +71,17 @@ int main(int argc, char** argv) {
     env.barrier();
     ar->apply(v.data(), n);
     write_vec(out + tag, v);
+  }
+  {
+    const std::string tag = "_r" + std::to_string(me) + "_k" + std::to_string(runs) + ".bin";
+    if (variant == "bigring" || variant == "ring" || variant == "alltoone") {
+      std::vector<float> v = read_vec(in + tag, n);
+      env.barrier();
+      if (variant == "bigring") dynamic_cast<Comprex_BigRingAllreduce<float>*>(ar)->flush(v.data(), n);
+      else if (variant == "ring") dynamic_cast<Comprex_RingAllreduce<float>*>(ar)->flush(v.data(), n);
+      else dynamic_cast<Comprex_AllToOneAllreduce<float>*>(ar)->flush(v.data(), n);
+      write_vec(out + tag, v);
+    }
   }
   env.barrier();
   delete ar;

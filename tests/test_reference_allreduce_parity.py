@@ -61,7 +61,7 @@ def test_allreduce_matches_reference_call_by_call(driver, tmp_path, variant, P, 
     pin, pout = str(tmp_path / "in"), str(tmp_path / "out")
     inputs = {}
     for r in range(P):
-        for k in range(runs):
+        for k in range(runs + 1):                  # the last one goes through flush
             x = torch.randn(n, generator=torch.Generator().manual_seed(1000 * r + k))
             inputs[(r, k)] = x
             x.numpy().tofile(f"{pin}_r{r}_k{k}.bin")
@@ -91,6 +91,23 @@ def test_allreduce_matches_reference_call_by_call(driver, tmp_path, variant, P, 
             assert same, (f"rank {r}, call {k}: {int((xs[r] != ref).sum())} of {n} elements differ, "
                           f"max |diff| {float((xs[r] - ref).abs().max())}")
     assert changed > 0          # the calls did exchange something
+    # flush: everything still held back arrives.  BigRing adds the peers' residuals in ring order
+    # on both sides (bit for bit); the chief of AllToOne adds its workers in rank order (bit for
+    # bit); the Ring's owners sum in ring order there and in rank order here (to rounding, and only
+    # the chunk a rank owns is exact in the reference, test/RingAllreduce.cpp:87-100).
+    xs = [inputs[(r, runs)].clone() for r in range(P)]
+    world.run(ars, "flush", [(x,) for x in xs])
+    for r in range(P):
+        ref = torch.from_numpy(np.fromfile(f"{pout}_r{r}_k{runs}.bin", dtype=np.float32))
+        if variant == "ring":
+            a = ars[r]
+            c = (r + 1) % P
+            sl = slice(a.segment_starts[c], a.segment_starts[c] + a.segment_sizes[c])
+            torch.testing.assert_close(xs[r][sl], ref[sl], rtol=1e-5, atol=1e-5)
+        elif variant == "alltoone" and r != 0:
+            continue                                   # workers' vectors are not defined by a flush
+        else:
+            assert torch.equal(xs[r], ref), f"flush, rank {r}: {int((xs[r] != ref).sum())} elements differ"
     world.close()
 
 
