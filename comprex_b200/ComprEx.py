@@ -22,7 +22,7 @@ import ctypes as C
 import torch
 
 from . import _lib
-from .common import AbstractExchange
+from .common import AbstractExchange, Getable  # noqa: F401  (the reference defines Getable in this module too)
 from ._lib import ComprexError
 from .GaspiEx import to_device_vector, write_back
 from .ops import primitives as P
@@ -316,18 +316,18 @@ class Comprex(AbstractExchange):
             self.setRests(state["rests"].to(self._env.device))
 
     # ---- connections --------------------------------------------------------------------------
-    def connectTx(self, targRank: int, tag: int = 0) -> None:
-        self._check_rank(targRank)
-        self._dest = int(targRank)
+    def connectTx(self, Rank: int, tag: int = 0) -> None:      # parameter name as in ComprEx.py:148
+        self._check_rank(Rank)
+        self._dest = int(Rank)
         self._alloc_rests()
         if self._dense is not None:
-            self._dense.connectTx(targRank, tag)
+            self._dense.connectTx(Rank, tag)
 
-    def connectRx(self, srcRank: int, tag: int = 0) -> None:
-        self._check_rank(srcRank)
-        self._src = int(srcRank)
+    def connectRx(self, Rank: int, tag: int = 0) -> None:
+        self._check_rank(Rank)
+        self._src = int(Rank)
         if self._dense is not None:
-            self._dense.connectRx(srcRank, tag)
+            self._dense.connectRx(Rank, tag)
 
     def connectTo(self, srcRank: int, targRank: int, tag: int = 0) -> None:
         self.connectRx(srcRank, tag)

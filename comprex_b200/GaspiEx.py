@@ -18,7 +18,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from .common import AbstractExchange
+from .common import AbstractExchange, Getable  # noqa: F401  (the reference defines Getable in this module too)
 from ._lib import ComprexError
 from .ops import primitives as P
 

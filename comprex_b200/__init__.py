@@ -7,6 +7,7 @@ optimizer), built on hand-written sm_100a kernels that store compressed
 payloads directly into peer GPUs' memory.
 """
 from ._lib import ComprexError, launch_count  # noqa: F401
+from .common import Getable, Gettable, Subscribable  # noqa: F401
 from .gpi import GaspiEnvironment, Gaspi_Runtime, Gaspi_Segment, LoopbackWorld, gaspi_printf, initGaspiCxx  # noqa: F401
 from .GaspiEx import GaspiEx  # noqa: F401
 from .ComprEx import (Comprex, FastComprex, ThresholdNone, ThresholdConst, ThresholdTopK,  # noqa: F401

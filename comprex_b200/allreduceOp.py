@@ -69,8 +69,11 @@ class AllreduceOp:
     def __del__(self):
         unregister(getattr(self, "handle", -1))
 
-    def __call__(self, tensor):
-        return self.apply(tensor)
+    def __call__(self, inputs):
+        return self.apply(inputs)
+
+    def get_size(self):
+        return self.size
 
     def _setup(self, size, *args, **kw):
         if self.size is not None:
@@ -80,16 +83,19 @@ class AllreduceOp:
         self.size = size
         self.allreduce.setup_connections(size, *args, **kw)
 
-    def apply(self, tensor: torch.Tensor) -> torch.Tensor:
-        """In place on ``tensor``; returns it (the TF op forwards its input as output)."""
-        allreduce_apply(tensor, self.handle)
-        return tensor
+    def apply(self, inputs: torch.Tensor) -> torch.Tensor:
+        """In place on ``inputs``; returns it (the TF op forwards its input as output)."""
+        allreduce_apply(inputs, self.handle)
+        return inputs
 
 
 class _CompressedOp(AllreduceOp):
-    def flush(self, tensor: torch.Tensor) -> torch.Tensor:
-        allreduce_flush(tensor, self.handle)
-        return tensor
+    def flush(self, inputs: torch.Tensor) -> torch.Tensor:
+        allreduce_flush(inputs, self.handle)
+        return inputs
+
+    def reset(self) -> None:
+        self.allreduce.reset()
 
     def set_compression_ratio(self, compression_ratio: float) -> None:
         self.allreduce.set_compression_ratio(compression_ratio)

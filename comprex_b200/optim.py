@@ -134,7 +134,7 @@ class ComprexOptimizer(torch.optim.Optimizer):
     def __init__(self, params, gaspi_env, lr=0.01, momentum=0.9, compression_ratio=0.01, nesterov=False,
                  allreduce_type="comprex_bigring", size_factor=1.0, logging=False, pre_clipnorm=5.0,
                  weight_decay=0.0, local_momentum=True, rule="sgd", betas=(0.9, 0.999), eps=1e-8,
-                 learning_rate=None, bucket_cap_mb=None, overlap=False, consistent=True):
+                 learning_rate=None, bucket_cap_mb=None, overlap=False, consistent=True, name="ComprexOptimizer"):
         if learning_rate is not None:
             lr = learning_rate
         if not 0 <= momentum <= 1:
@@ -146,6 +146,7 @@ class ComprexOptimizer(torch.optim.Optimizer):
         defaults = dict(lr=lr, momentum=momentum, weight_decay=weight_decay)
         super().__init__(params, defaults)
         self.gaspi_env = gaspi_env
+        self.name = name
         self._env = env = gaspi_env.get()
         self.compression_ratio = float(compression_ratio)
         self.nesterov = nesterov          # accepted and unused, like the reference
@@ -414,6 +415,13 @@ class ComprexOptimizer(torch.optim.Optimizer):
             self._master.mul_(1 - wd).sub_(self._m)
         if self._shadow is not None:
             self._shadow.copy_(self._master)
+
+    def apply_gradients(self, grads_and_vars, *args, **kwargs):
+        """Keras-style entry (keras/comprex_optimizer.py:144-145): ``(gradient, variable)`` pairs are
+        installed as the variables' ``.grad`` and one step is taken."""
+        for g, v in grads_and_vars:
+            v.grad = g
+        return self.step()
 
     def refresh_master(self) -> None:
         """Take the model's current tensors as the master weights: call it after the parameters
