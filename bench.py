@@ -34,9 +34,10 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-REFERENCE_UNAVAILABLE = ("reference is not installable offline: its tree has no setup.py/pyproject.toml "
-                         "(pip: 'Neither setup.py nor pyproject.toml found'), and it needs GPI-2, GaspiCxx and "
-                         "TensorFlow 2.3, none of which are on this image")
+REFERENCE_UNAVAILABLE = ("the metric needs the reference's Keras optimizer and TF custom ops: TensorFlow 2.3 is not on this "
+                         "image and cannot be installed offline; pip cannot install the tree either (no setup.py/pyproject.toml; "
+                         "GPI-2 and GaspiCxx absent). Its Python package and allreduce benchmark do run from baseline/_ref on a "
+                         "shared-memory GaspiCxx stand-in (baseline/README.md), on CPU only")
 
 
 def parse():
