@@ -312,7 +312,7 @@ class BigRingAllreduce(_AllreduceBase):
 
     One-shot moves (P-1) n elements out of every GPU.  Through a switch that gives every
     pair full bandwidth this is the lowest-latency schedule for small vectors and the
-    wrong one for large vectors, so above ``two_shot_bytes`` (default 8 MiB, environment
+    wrong one for large vectors, so above ``two_shot_bytes`` (default 1 MiB, environment
     variable ``COMPREX_TWO_SHOT_BYTES``; never with two ranks, where both schedules move
     the same bytes) the call runs the reduce-scatter + allgather schedule of
     ``RingAllreduce``: 2 (P-1)/P n elements, every rank ends with the same bits."""
@@ -321,7 +321,7 @@ class BigRingAllreduce(_AllreduceBase):
         self._setup_common(size, dtype)
         env, nb = self._env, size * torch.empty(0, dtype=dtype).element_size()
         if two_shot_bytes is None:
-            two_shot_bytes = int(os.environ.get("COMPREX_TWO_SHOT_BYTES", 8 << 20))
+            two_shot_bytes = int(os.environ.get("COMPREX_TWO_SHOT_BYTES", 1 << 20))
         self._two_shot = None
         if env.ranks > 2 and nb > two_shot_bytes:
             self._two_shot = RingAllreduce(self.gaspi_env)

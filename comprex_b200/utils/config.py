@@ -37,7 +37,7 @@ class ComprexConfig:
     stale: bool = False                      # FastComprEx semantics: payloads arrive one call late
     ring_schedule: str = "direct"            # compressed Ring: "direct" stores or the reference's "hops"
     exact_topk: bool = False                 # threshold from a select over the whole vector
-    two_shot_bytes: int = 8 << 20            # dense BigRing: reduce-scatter + allgather above this size
+    two_shot_bytes: int = 1 << 20            # dense BigRing: reduce-scatter + allgather above this size
     dense_fallback_bytes: int = 64 << 10     # DDP hook: buckets below this go out dense
     capacity_slack: float = 2.0              # DDP hook: slot room over the expected survivors
     # optimizer
