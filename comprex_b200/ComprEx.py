@@ -56,11 +56,16 @@ class _Threshold:
         """Compute the threshold for ``rests + add_vec``."""
 
     def apply(self, vec: torch.Tensor) -> torch.Tensor:
-        """Dense copy with everything below the threshold zeroed (``|x| >= thr`` stays)."""
+        """Dense copy with everything below the threshold zeroed (``|x| >= thr`` stays).  Like the
+        reference (src/threshold.hxx:19-27) the threshold is first prepared from ``vec`` itself."""
+        self.prepare(vec)
+        self._threshold = self.getThreshold()
         return torch.where(vec.abs() >= self._threshold, vec, torch.zeros_like(vec))
 
     def apply_split(self, vec: torch.Tensor):
-        """(kept, rest): the part at or above the threshold and the remainder."""
+        """(kept, rest): the part at or above the threshold and the remainder (prepared from ``vec``)."""
+        self.prepare(vec)
+        self._threshold = self.getThreshold()
         keep = vec.abs() >= self._threshold
         zero = torch.zeros_like(vec)
         return torch.where(keep, vec, zero), torch.where(keep, zero, vec)
@@ -139,14 +144,6 @@ class ThresholdTopK(_Threshold):
         if rests.numel() != add_vec.numel():
             raise ComprexError("vector sizes must be the same!")
         self._standalone(add_vec.contiguous().view(-1), rests.contiguous().view(-1))
-
-    def apply(self, vec):
-        self._threshold = self.getThreshold()
-        return super().apply(vec)
-
-    def apply_split(self, vec):
-        self._threshold = self.getThreshold()
-        return super().apply_split(vec)
 
     def _launch(self, comp: P.Compressor, g, r, n: int) -> None:
         comp.threshold_topk(g, r, n, self.topK, self.default_subsamples, self.subsample_factor)

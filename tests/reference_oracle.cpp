@@ -20,8 +20,23 @@ int main(int argc, char** argv) {
   if (fread(g.data(), 4, n, in) != (size_t)n || fread(r.data(), 4, n, in) != (size_t)n ||
       fread(base.data(), 4, n, in) != (size_t)n) return 5;
   fclose(in);
-  // mode (argv[3], default 0): 0 compress_add_update(r, g), 1 compress_update(r), 2 compress(g)
+  // mode (argv[3], default 0): 0 compress_add_update(r, g), 1 compress_update(r), 2 compress(g),
+  // 3: ThresholdTopK::apply and ::apply_split of g only (writes out, high, low)
   const int mode = argc > 3 ? atoi(argv[3]) : 0;
+  if (mode == 3) {
+    ThresholdTopK<float> t(ratio);
+    std::vector<float> o(n), hi(n), lo(n);
+    t.apply(o.data(), n, g.data(), n);
+    ThresholdTopK<float> t2(ratio);
+    t2.apply_split(hi.data(), n, lo.data(), n, g.data(), n);
+    FILE* out = fopen(argv[2], "wb");
+    if (!out) return 6;
+    fwrite(o.data(), 4, n, out);
+    fwrite(hi.data(), 4, n, out);
+    fwrite(lo.data(), 4, n, out);
+    fclose(out);
+    return 0;
+  }
   ThresholdTopK<float> thr(ratio);
   if (mode == 0) thr.prepare_with(r.data(), n, g.data(), n);
   else if (mode == 1) thr.prepare(r.data(), n);

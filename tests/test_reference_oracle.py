@@ -81,3 +81,21 @@ def test_threshold_pairs_and_residual_match_the_reference(oracle, tmp_path, n, r
     P.apply_sparse(e1, src, n, P.args_set(dec), status)
     assert torch.equal(dec, ref_dec) and status.value == 0
     world.close()
+
+
+@pytest.mark.parametrize("n", [100, 4097, 100003])
+@pytest.mark.parametrize("ratio", [0.1, 0.01])
+def test_threshold_apply_and_split_match_the_reference(oracle, tmp_path, n, ratio):
+    torch.manual_seed(n + 1)
+    g = torch.randn(n)
+    fin, fout = str(tmp_path / "in.bin"), str(tmp_path / "out.bin")
+    with open(fin, "wb") as f:
+        f.write(struct.pack("<if", n, ratio))
+        f.write(g.numpy().tobytes() * 3)               # g, r, base slots of the file format
+    subprocess.run([oracle, fin, fout, "3"], check=True)
+    ref = torch.from_numpy(np.fromfile(fout, dtype=np.float32))
+    ref_out, ref_hi, ref_lo = ref[:n], ref[n:2 * n], ref[2 * n:]
+    thr = cx.ThresholdTopK(ratio)
+    assert torch.equal(thr.apply(g), ref_out)
+    hi, lo = cx.ThresholdTopK(ratio).apply_split(g)
+    assert torch.equal(hi, ref_hi) and torch.equal(lo, ref_lo)
