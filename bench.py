@@ -22,6 +22,14 @@ timed region.
 ``--impl reference`` reports why the reference cannot run here.  ``--impl dense`` runs the
 comparison arm on the same model and data: stock DistributedDataParallel (dense NCCL allreduce)
 with the stock torch optimizer.
+
+The default arm (``ours``) also runs that dense arm afterwards in the same invocation, on the
+same batches, for the same steps and warm-up: the reference publishes no number, so
+``vs_baseline`` is ``value`` divided by the dense arm's value and ``baseline`` holds the dense
+arm's figures (``--skip-baseline`` leaves both out).  With N > 1 the line also carries an
+``allreduce`` block: compressed BigRing and Ring of one 2^24-element fp32 vector at top-k 1 %
+(achieved sent fraction stated) next to ``torch.distributed.all_reduce`` of the same tensor,
+CUDA-event microseconds, max over ranks.
 """
 import argparse
 import json
@@ -52,6 +60,10 @@ def parse():
     ap.add_argument("--bucket-mb", type=float, default=25.0)
     ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-baseline", action="store_true", help="do not run the dense DDP comparison arm afterwards")
+    ap.add_argument("--skip-allreduce", action="store_true", help="N > 1: do not time the compressed allreduce block")
+    ap.add_argument("--allreduce", default="comprex_bigring",
+                    help="allreduce_type of the compressed optimizer (comprex_bigring, comprex_ring, auto, ...)")
     return ap.parse_args()
 
 
@@ -102,35 +114,8 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def main():
-    args = parse()
-    if args.impl == "reference":
-        if int(os.environ.get("RANK", "0")) == 0:          # one line per job, also under torchrun
-            print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
-        return 0
-
-    import torch
-    import torch.distributed as dist
-    import torch.nn.functional as F
-    import comprex_b200 as cx
-    from comprex_b200 import _lib
-    from comprex_b200.callbacks import broadcast_parameters
-    from comprex_b200.optim import ComprexOptimizer
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    torch.backends.cudnn.benchmark = True
-    torch.backends.cuda.matmul.allow_tf32 = True
-    torch.backends.cudnn.allow_tf32 = True
-    torch.manual_seed(1234)
-
+def build_workload(args, torch, F, dev, world):
+    """Model, per-rank host batch maker, loss function and the config block of the named workload."""
     if args.model == "resnet50":
         from comprex_b200.models.resnet import resnet50
         batch = args.batch or 128
@@ -143,8 +128,8 @@ def main():
                     .contiguous(memory_format=torch.channels_last).pin_memory(),
                     torch.randint(0, 1000, (batch,), generator=g).pin_memory())
 
-        def loss_fn(x, y):
-            return F.cross_entropy(model(x).float(), y)
+        def loss_of(net, x, y):
+            return F.cross_entropy(net(x).float(), y)
         cfg = {"model": "resnet50", "global_batch": batch * world, "seq_len": None, "image": "224x224x3",
                "optimizer": "sgd momentum 0.9 (local momentum, fused update)"}
     elif args.model == "gpt2":
@@ -158,8 +143,8 @@ def main():
             t = torch.randint(0, 50257, (batch, 1025), generator=g)
             return t[:, :-1].contiguous().pin_memory(), t[:, 1:].contiguous().pin_memory()
 
-        def loss_fn(x, y):
-            return model(x, y)
+        def loss_of(net, x, y):
+            return net(x, y)
         cfg = {"model": "gpt2-medium", "global_batch": batch * world, "seq_len": 1024, "optimizer": "adamw (fused)"}
     else:
         from comprex_b200.models.lenet import LeNet5
@@ -172,19 +157,36 @@ def main():
             return (torch.rand(batch, 1, 28, 28, generator=g).pin_memory(),
                     torch.randint(0, 10, (batch,), generator=g).pin_memory())
 
-        def loss_fn(x, y):
-            return F.cross_entropy(model(x), y)
+        def loss_of(net, x, y):
+            return F.cross_entropy(net(x), y)
         cfg = {"model": "lenet5", "global_batch": batch * world, "seq_len": None, "optimizer": "sgd 0.01"}
+    return model, batch, ratio, opt_kw, host_batch, loss_of, cfg
 
+
+def run_arm(args, impl, rank, world, local):
+    """One arm (``ours`` or ``dense``) of the training benchmark: fresh model and optimizer, warm-up,
+    the device-timed loop, then the end-to-end loop.  Returns the numbers of that arm."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    import comprex_b200 as cx
+    from comprex_b200 import _lib
+    from comprex_b200.callbacks import broadcast_parameters
+    from comprex_b200.optim import ComprexOptimizer
+
+    dev = torch.device("cuda", local)
+    torch.manual_seed(1234)
+    model, batch, ratio, opt_kw, host_batch, loss_of, cfg = build_workload(args, torch, F, dev, world)
     nparams = sum(p.numel() for p in model.parameters())
     env = cx.GaspiEnvironment(256 << 20, device=dev)
     broadcast_parameters(model, env, 0)
     # slots sized for 2x the expected survivors (what does not fit stays in the residual)
     size_factor = max(4.0 * ratio, 1e-3) + 1e-4
-    dense = args.impl == "dense"
+    dense = impl == "dense"
+    net = model
     if dense:
         # comparison arm: stock DistributedDataParallel (dense NCCL allreduce, 25 MB buckets) and
-        # the stock fused torch optimizer on the same model, data and step structure
+        # the stock torch optimizer on the same model, data and step structure
         from torch.nn.parallel import DistributedDataParallel as DDP
         if args.model == "gpt2":
             opt = torch.optim.AdamW(model.parameters(), lr=opt_kw["lr"], betas=opt_kw["betas"],
@@ -192,14 +194,14 @@ def main():
         else:
             opt = torch.optim.SGD(model.parameters(), lr=opt_kw["lr"], momentum=opt_kw.get("momentum", 0.0))
         if world > 1:
-            ddp = DDP(model, device_ids=[local], bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True)
-            def loss_fn(x, y, _m=ddp):   # route the forward through the DDP wrapper
-                if args.model == "gpt2":
-                    return _m(x, y)
-                return F.cross_entropy(_m(x).float() if args.model == "resnet50" else _m(x), y)
+            net = DDP(model, device_ids=[local], bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True)
     else:
         opt = ComprexOptimizer(model.parameters(), env, compression_ratio=ratio, size_factor=size_factor,
-                               bucket_cap_mb=args.bucket_mb, overlap=not args.no_overlap, **opt_kw)
+                               bucket_cap_mb=args.bucket_mb, overlap=not args.no_overlap,
+                               allreduce_type=args.allreduce, **opt_kw)
+
+    def loss_fn(x, y):
+        return loss_of(net, x, y)
 
     gen = torch.Generator().manual_seed(100 + rank)
     host = [host_batch(gen) for _ in range(4)]
@@ -282,20 +284,126 @@ def main():
                "h2d_bytes_per_step": hx.numel() * hx.element_size() + hy.numel() * hy.element_size(),
                "d2h_bytes_per_step": 4, "ms_per_step": round(sec * 1e3 / args.steps, 3)}
     stats = {} if dense else opt.stats()
-    if rank == 0:
-        cfg.update({"parallelism": f"dp{world}", "per_gpu_batch": batch, "params": nparams,
-                    "compression_ratio": ratio, "bucket_mb": args.bucket_mb, "overlap": not args.no_overlap,
-                    "allreduce": ("dense NCCL allreduce (DistributedDataParallel), stock torch optimizer" if dense else
-                                  "comprex_bigring (direct NVLink peer stores, replica-consistent)"),
-                    "cache": "inputs_larger_than_L2 (activations + weights per step exceed 126 MB)",
-                    "first_bucket_nnz": stats.get("nnz"), "first_bucket_n": stats.get("n"), "final_loss": final_loss})
-        print(json.dumps({
-            "metric": "train samples/sec", "value": round(batch * world * args.steps / (ms / 1e3), 2),
-            "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": warm,
-            "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "fp32" if args.model == "lenet" else "bf16", "data": "synthetic",
-            "impl": "dense_nccl_ddp" if dense else "ours", "config": cfg, "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches)}))
+    cfg.update({"parallelism": f"dp{world}", "per_gpu_batch": batch, "params": nparams,
+                "compression_ratio": None if dense else ratio, "bucket_mb": args.bucket_mb,
+                "overlap": not args.no_overlap,
+                "allreduce": ("dense NCCL allreduce (DistributedDataParallel), stock torch optimizer" if dense else
+                              getattr(opt, "describe", lambda: args.allreduce)()),
+                "cache": "inputs_larger_than_L2 (activations + weights per step exceed 126 MB)",
+                "first_bucket_nnz": stats.get("nnz"), "first_bucket_n": stats.get("n"), "final_loss": final_loss})
+    out = {"impl": "dense_nccl_ddp" if dense else "ours", "value": round(batch * world * args.steps / (ms / 1e3), 2),
+           "ms_per_step": round(ms / args.steps, 3), "warm": warm, "config": cfg, "clocks": clocks, "e2e": e2e,
+           "gpu_launches": int(launches), "final_loss": final_loss, "dtype": "fp32" if args.model == "lenet" else "bf16"}
+    del opt, net, model, dev_batches
     env.close()
+    torch.cuda.empty_cache()
+    return out
+
+
+def allreduce_block(rank, world, local, log2n=24, ratio=0.01, reps=10, warmup=3):
+    """Compressed allreduce of one fp32 vector against ``torch.distributed.all_reduce`` of the same
+    tensor (the reference's examples/allreduce_speed.cpp:259-279 protocol, device-timed): CUDA-event
+    microseconds, ranks aligned by a barrier before every repetition, L2 flushed between repetitions,
+    MAX over ranks per repetition, median over repetitions."""
+    import torch
+    import torch.distributed as dist
+    import comprex_b200 as cx
+
+    dev = torch.device("cuda", local)
+    n = 1 << log2n
+    env = cx.GaspiEnvironment(256 << 20, device=dev)
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    torch.manual_seed(1000 + rank)
+    x = torch.randn(n, device=dev)
+
+    def time_op(fn):
+        out = []
+        for i in range(warmup + reps):
+            flush.add_(1)
+            torch.cuda.synchronize(dev)
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize(dev)
+            t = torch.tensor([a.elapsed_time(b) * 1e3], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if i >= warmup:
+                out.append(float(t.item()))
+        return statistics.median(out)
+
+    work = x.clone()
+    block = {"n": n, "dtype": "fp32", "nominal_topk": ratio, "ranks": world,
+             "nccl_all_reduce_us": round(time_op(lambda: dist.all_reduce(work)), 2)}
+    sf = max(4.0 * ratio, 2e-3)
+    for name, cls, kw in (("comprex_bigring", cx.Comprex_BigRingAllreduce, {"consistent": True}),
+                          ("comprex_ring", cx.Comprex_RingAllreduce, {})):
+        mark = env.heap_mark()
+        ar = cls(env)
+        ar.setup_connections(n, 1, ratio, sf, **kw)
+        buf = x.clone()
+        # the input is not reset between repetitions: the residual carries what was not sent, as in training
+        us = time_op(lambda: ar.apply(buf))
+        st = ar.stats()
+        block[name] = {"us": round(us, 2), "sent_fraction": round(st["nnz"] / max(st["n"], 1), 5),
+                       "speedup_vs_nccl": round(block["nccl_all_reduce_us"] / us, 2)}
+        del ar, buf
+        env.heap_release(mark)
+    env.barrier()
+    env.close()
+    return block
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) == 0:          # one line per job, also under torchrun
+            print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    torch.backends.cudnn.benchmark = True
+    torch.backends.cuda.matmul.allow_tf32 = True
+    torch.backends.cudnn.allow_tf32 = True
+
+    main_arm = run_arm(args, args.impl, rank, world, local)
+    base = None
+    if args.impl == "ours" and not args.skip_baseline:
+        # the comparison arm in the same invocation, on the same batches: stock DDP + NCCL + torch optimizer
+        base = run_arm(args, "dense", rank, world, local)
+    ar_block = None
+    if world > 1 and args.impl == "ours" and not args.skip_allreduce:
+        ar_block = allreduce_block(rank, world, local)
+    if rank == 0:
+        line = {"metric": "train samples/sec", "value": main_arm["value"], "unit": "samples/s", "n_gpus": world,
+                "steps": args.steps, "warmup": main_arm["warm"], "ms_per_step": main_arm["ms_per_step"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": main_arm["dtype"],
+                "data": "synthetic", "impl": main_arm["impl"], "config": main_arm["config"],
+                "clocks": main_arm["clocks"], "e2e": main_arm["e2e"], "gpu_launches": main_arm["gpu_launches"]}
+        if base is not None:
+            # no published reference number exists: the baseline is the dense arm measured just now
+            line["vs_baseline"] = round(main_arm["value"] / base["value"], 4)
+            bl = {"impl": base["impl"], "value": base["value"], "ms_per_step": base["ms_per_step"],
+                  "e2e": base["e2e"], "final_loss": base["final_loss"], "clocks": base["clocks"],
+                  "ratio": line["vs_baseline"], "what": base["config"]["allreduce"]}
+            if base["e2e"] and main_arm["e2e"]:
+                bl["e2e_ratio"] = round(main_arm["e2e"]["value"] / base["e2e"]["value"], 4)
+            line["baseline"] = bl
+        if ar_block is not None:
+            line["allreduce"] = ar_block
+        print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
     return 0

@@ -12,8 +12,9 @@ from .gpi import GaspiEnvironment, Gaspi_Runtime, Gaspi_Segment, LoopbackWorld, 
 from .GaspiEx import GaspiEx  # noqa: F401
 from .ComprEx import (Comprex, FastComprex, ThresholdNone, ThresholdConst, ThresholdTopK,  # noqa: F401
                       CompressorNone, CompressorRLE, CompressorIndexPairs)
-from .allreduce import (AllToOneAllreduce, RingAllreduce, BigRingAllreduce,  # noqa: F401
-                        Comprex_AllToOneAllreduce, Comprex_RingAllreduce, Comprex_BigRingAllreduce)
+from .allreduce import (AllToOneAllreduce, RingAllreduce, BigRingAllreduce, AutoAllreduce,  # noqa: F401
+                        Comprex_AllToOneAllreduce, Comprex_RingAllreduce, Comprex_BigRingAllreduce,
+                        select_schedule)
 from .utils import ComprexConfig  # noqa: F401
 
 __version__ = "0.1.0"

@@ -61,7 +61,7 @@ class ApplyArgs(C.Structure):
                 ("bc1", C.c_float), ("bc2", C.c_float), ("momentum", C.c_float), ("pad2", C.c_float)]
 
 
-OPK_THRESHOLD, OPK_COMPRESS, OPK_APPLY, OPK_DENSE_SEND, OPK_DENSE_REDUCE = 1, 2, 3, 4, 5
+OPK_THRESHOLD, OPK_COMPRESS, OPK_APPLY, OPK_DENSE_SEND, OPK_DENSE_REDUCE, OPK_UPDATE = 1, 2, 3, 4, 5, 6
 
 
 class Op(C.Structure):
@@ -100,6 +100,7 @@ def _declare(lib) -> None:
         "cx_threshold_topk": (i32, [i32, i32, vp, vp, i64, f32, i32, f32, vp, vp]),
         "cx_compress": (i32, [i32, i32, vp, vp, i64, vp, u32, u64, P(Targets), vp, i64, vp, u32, vp]),
         "cx_apply": (i32, [i32, P(Sources), i64, P(ApplyArgs), vp, u64, vp]),
+        "cx_update_dense": (i32, [i32, vp, i64, P(ApplyArgs), vp]),
         "cx_forward": (i32, [i32, P(Endpoint), u64, P(Targets), u64, u32, vp, vp, u64, vp]),
         "cx_dense_send": (i32, [i32, i32, vp, vp, i64, u64, P(Targets), P(i64), P(i64), vp, u32, vp]),
         "cx_dense_reduce": (i32, [i32, i32, vp, vp, i64, P(Sources), f32, P(Targets), u64, P(i64), P(i64),

@@ -51,10 +51,16 @@ from .ops import primitives as P
 _log = logging.getLogger("comprex.allreduce")
 
 
-def _chunks(size: int, nranks: int):
-    """Chunk sizes and starts of the ring (src/allreduce.tpp:279-295)."""
-    base, rem = divmod(size, nranks)
-    sizes = [base + (1 if i < rem else 0) for i in range(nranks)]
+def _chunks(size: int, nranks: int, align: int = 1):
+    """Chunk sizes and starts of the ring (src/allreduce.tpp:279-295).  With ``align`` > 1 every
+    chunk but the last is a multiple of ``align`` elements, so that every chunk starts on an
+    address the kernels can use 16-byte accesses on (the last chunk takes the remainder)."""
+    if align > 1:
+        base = (size // nranks) // align * align
+        sizes = [base] * (nranks - 1) + [size - base * (nranks - 1)]
+    else:
+        base, rem = divmod(size, nranks)
+        sizes = [base + (1 if i < rem else 0) for i in range(nranks)]
     starts = [0] * nranks
     for i in range(1, nranks):
         starts[i] = starts[i - 1] + sizes[i - 1]
@@ -120,6 +126,9 @@ class _AllreduceBase:
         self.gaspi_env = gaspi_env
         self.size = None
         self._step = 0
+        # dense variants: factor applied to the sum inside the reducing kernel (1/P gives the mean
+        # without an extra pass); set it before the first apply
+        self.result_scale = 1.0
 
     def get(self):
         return self
@@ -250,8 +259,8 @@ class AllToOneAllreduce(_AllreduceBase):
             if me == chief:
                 src = P.make_sources([self._rs[w][par].endpoint(env) for w in workers], [seq] * len(workers))
                 push = P.make_targets([self._bc[par].endpoint(env, w) for w in workers])
-                P.dense_reduce(env, t, t, self.size, src, self._status, push=push, push_seq=seq,
-                               counters=self._counters)
+                P.dense_reduce(env, t, t, self.size, src, self._status, scale=self.result_scale, push=push,
+                               push_seq=seq, counters=self._counters)
 
         def recv():
             if me != chief:
@@ -295,8 +304,8 @@ class RingAllreduce(_AllreduceBase):
                 return
             src = P.make_sources([self._rs[j][par].endpoint(env) for j in peers], [seq] * len(peers))
             push = P.make_targets([self._ag[me][par].endpoint(env, j) for j in peers])
-            P.dense_reduce(env, my_view, my_view, self.segment_sizes[mine], src, self._status, push=push,
-                           push_seq=seq, counters=self._counters)
+            P.dense_reduce(env, my_view, my_view, self.segment_sizes[mine], src, self._status,
+                           scale=self.result_scale, push=push, push_seq=seq, counters=self._counters)
 
         def gather():
             if nr == 1:
@@ -332,6 +341,7 @@ class BigRingAllreduce(_AllreduceBase):
     def _plan_apply(self, t):
         if self._two_shot is not None:
             self._two_shot._step = self._step          # one step counter: sequence numbers and parity agree
+            self._two_shot.result_scale = self.result_scale
             self._step += 1
             return self._two_shot._plan_apply(t)
         env, me, nr = self._env, self._env.rank, self._env.ranks
@@ -349,7 +359,7 @@ class BigRingAllreduce(_AllreduceBase):
             if nr > 1:
                 src = self._cached_sources(("src", par), lambda: [self._slots[j][par].endpoint(env) for j in arrival],
                                            seq)
-                P.dense_reduce(env, t, t, self.size, src, self._status)
+                P.dense_reduce(env, t, t, self.size, src, self._status, scale=self.result_scale)
         return [send, reduce]
 
 
@@ -373,6 +383,7 @@ class _ComprexAllreduceBase(_AllreduceBase):
         kept (the reference silently falls back to the defaults here)."""
         self.compression_ratio = float(compression_ratio)
         self.__dict__.pop("_replay_cache", None)      # the ratio is part of the recorded launches
+        self.__dict__.pop("_fast_cache", None)
 
     def set_exact_topk(self, exact: bool = True) -> None:
         """Threshold from a select over the whole vector (exactly top-k) instead of the sampled
@@ -384,6 +395,7 @@ class _ComprexAllreduceBase(_AllreduceBase):
             self._subsamples, self._sample_factor = self._sampling
         self.__dict__.pop("_replay_cache", None)
         self.__dict__.pop("_seq_cache", None)
+        self.__dict__.pop("_fast_cache", None)
 
     def reset(self):
         for r in self._residuals():
@@ -411,7 +423,13 @@ class _ComprexAllreduceBase(_AllreduceBase):
         return self._comp.last_stats()
 
     def _flush_rounds(self, n, cap):
-        return max(1, math.ceil(n / cap))
+        """Compress calls that drain a fully dense residual of ``n`` elements through a slot of
+        ``cap`` pairs.  The compress kernel cuts the pair list into R regions and sub-tile s may
+        only use region s mod R, so the bound is the busiest region's, not n / cap."""
+        regions, region_size = P.compress_regions(n, cap)
+        nsub = (n + _lib.SUBTILE - 1) // _lib.SUBTILE
+        per_region = math.ceil(nsub / regions) * _lib.SUBTILE
+        return max(1, math.ceil(per_region / max(region_size, 1)))
 
 
 class Comprex_BigRingAllreduce(_ComprexAllreduceBase):
@@ -555,14 +573,19 @@ class Comprex_RingAllreduce(_ComprexAllreduceBase):
     """
 
     def setup_connections(self, size, tag=0, compression_ratio=0.01, size_factor=1.0, consistent=False,
-                          owner_residual=False, schedule="direct"):
+                          owner_residual=False, schedule="direct", chunk_align=1):
         if schedule not in ("direct", "hops"):
             raise ComprexError("schedule must be 'direct' or 'hops'")
+        if consistent and schedule != "direct":
+            raise ComprexError("consistent=True needs the direct schedule")
         self._setup_compressed(size, compression_ratio, size_factor, consistent)
         env = self._env
         self.schedule = schedule
-        self.owner_residual = bool(owner_residual)
-        self.segment_sizes, self.segment_starts = _chunks(size, env.ranks)
+        # consistent: the owner, too, applies only what it broadcast, and keeps the rest of its
+        # reduced chunk in a residual of its own (otherwise that rest would be lost for everyone)
+        self.owner_residual = bool(owner_residual) or self.consistent
+        owner_residual = self.owner_residual
+        self.segment_sizes, self.segment_starts = _chunks(size, env.ranks, chunk_align)
         nmax = max(max(self.segment_sizes), 1)
         self.cap = _cap_for(nmax, size_factor)
         self._rs = [[P.SparseSlot.create(env, nmax, self.cap) for _ in range(2)] for _ in range(env.ranks)]
@@ -639,17 +662,24 @@ class Comprex_RingAllreduce(_ComprexAllreduceBase):
     def _view(self, t, c):
         return t[self.segment_starts[c]: self.segment_starts[c] + self.segment_sizes[c]]
 
-    def _plan_ring(self, t, flush, rounds=1):
+    def _plan_ring(self, t, flush, rounds=1, final_args=None, fixed=None):
+        """Phases of one call.  ``final_args(chunk)`` replaces the plain decode of the allgather
+        (``SET`` into the chunk's part of ``t``) by another receive operation, e.g. a fused
+        parameter update; ``fixed=(seq, parity)`` plans for that step instead of the next one."""
         env, me, nr = self._env, self._env.rank, self._env.ranks
         mine = (me + 1) % nr
         # chunk order starts behind this rank's own chunk: at any moment every rank addresses a
         # different owner instead of all ranks storing into the same receiver
         others = [(mine + k) % nr for k in range(1, nr)]
         peers = [r for r in range(nr) if r != me]
+        everyone = list(range(nr))
         phases = []
         for rnd in range(rounds):
-            self._step += 1
-            seq, par = self._step, self._step & 1
+            if fixed is None:
+                self._step += 1
+                seq, par = self._step, self._step & 1
+            else:
+                seq, par = fixed
 
             def scatter(seq=seq, par=par):
                 for k, c in enumerate(others):
@@ -665,33 +695,85 @@ class Comprex_RingAllreduce(_ComprexAllreduceBase):
                                       P.make_targets([self._rs[me][par].endpoint(env, self._owner(c))]))
 
             def reduce(seq=seq, par=par, last=(rnd == rounds - 1)):
-                if nr == 1:
+                if nr == 1 and not self.consistent:
                     return
                 n = self.segment_sizes[mine]
                 mv = self._view(t, mine)
-                src = P.make_sources([self._rs[j][par].endpoint(env) for j in peers], [seq] * len(peers))
-                P.apply_sparse(env, src, n, P.args_add(mv), self._status)
+                if peers:
+                    src = P.make_sources([self._rs[j][par].endpoint(env) for j in peers], [seq] * len(peers))
+                    P.apply_sparse(env, src, n, P.args_add(mv), self._status)
                 if flush and not last:
                     return  # more residual rounds follow; broadcast once at the end
-                r = None
+                r = self.owner_rests[:n] if self.owner_rests is not None else None
                 if flush:
-                    self._comp.set_threshold(0.0)
+                    self._comp.set_threshold(0.0)      # the owner's own residual is drained too
                 else:
-                    r = self.owner_rests[:n] if self.owner_rests is not None else None
                     self._comp.threshold_topk(mv, r, n, self.compression_ratio)
+                dests = everyone if self.consistent else peers
                 self._comp.compress(mv, r, n, self.cap, seq,
-                                    P.make_targets([self._ag[me][par].endpoint(env, j) for j in peers]))
+                                    P.make_targets([self._ag[me][par].endpoint(env, j) for j in dests]))
 
             def gather(seq=seq, par=par, last=(rnd == rounds - 1)):
                 if flush and not last:
                     return
-                for k, j in enumerate(peers):
+                for k, j in enumerate(everyone if self.consistent else peers):
                     c = (j + 1) % nr
                     src = P.make_sources([self._ag[j][par].endpoint(env)], [seq])
+                    args = final_args(c) if final_args is not None else P.args_set(self._view(t, c))
                     with P.lane(env, k + 1):     # the chunks are disjoint: decode them side by side
-                        P.apply_sparse(env, src, self.segment_sizes[c], P.args_set(self._view(t, c)), self._status)
+                        P.apply_sparse(env, src, self.segment_sizes[c], args, self._status)
             phases += [scatter, reduce, gather]
         return phases
+
+    # ---- pre-built launch sequences for the optimizer: a send half and a receive half ---------
+    def _fast_seqs(self, t, par):
+        cache = self.__dict__.setdefault("_fast_cache", {})
+        key = (t.data_ptr(), par)
+        got = cache.get(key)
+        if got is None:
+            env = self._env
+            if len(cache) >= 16:
+                cache.clear()
+            patch = []                      # (index into the receive list, chunk) of the final decodes
+
+            def placeholder(c):
+                patch.append((len(env._rec), c))
+                return P.args_set(self._view(t, c))
+            plan = self._plan_ring(t, False, final_args=placeholder, fixed=(0, par))
+            env._rec = send_rec = []
+            try:
+                plan[0]()
+                env._rec = recv_rec = []
+                plan[1]()
+                plan[2]()
+            finally:
+                env._rec = None
+            got = cache[key] = (_OpSeq(env, send_rec) if send_rec else None,
+                                _OpSeq(env, recv_rec) if recv_rec else None, patch)
+        return got
+
+    def send_fast(self, t: torch.Tensor):
+        """First half of a call on ``t`` (float32, this allreduce's size; it is used as work space):
+        every foreign chunk is compressed into its owner's slot.  One native call; returns
+        (seq, parity) for :meth:`recv_fast`."""
+        self._step += 1
+        seq, par = self._step, self._step & 1
+        send, _, _ = self._fast_seqs(t, par)
+        if send is not None:
+            send.run(seq)
+        return seq, par
+
+    def recv_fast(self, t: torch.Tensor, seq: int, par: int, args_of_chunk=None) -> None:
+        """Second half: reduce the own chunk, broadcast its top-k, decode every chunk.
+        ``args_of_chunk(chunk, start, size)`` returns the receive operation for a chunk (a fused
+        parameter update, say); the default writes the chunk into ``t``."""
+        _, recv, patch = self._fast_seqs(t, par)
+        if recv is None:
+            return
+        if args_of_chunk is not None:
+            for i, c in patch:
+                recv.arr[i].apply = args_of_chunk(c, self.segment_starts[c], self.segment_sizes[c])
+        recv.run(seq)
 
     def _plan_apply(self, t):
         if self.schedule == "hops":
@@ -850,3 +932,107 @@ class Comprex_AllToOneAllreduce(_ComprexAllreduceBase):
     def _plan_flush(self, t):
         return ([self._fold_pending] + self._plan_common(t, True, rounds=self._flush_rounds(self.size, self.cap))
                 + [self.reset])
+
+
+# =====================================================================================
+# choice of schedule by size, ratio and number of ranks
+# =====================================================================================
+# Cost model behind ``select_schedule``: time = launch floor + bytes through HBM / HBM rate
+# + bytes over NVLink / link rate, with the rates this package's kernels reach on 8 B200 behind
+# an NVSwitch (measured with bench/allreduce_sweep.py; microseconds, bytes per microsecond).
+_COST = {
+    "floor_dense_us": 30.0,      # dense one-shot: two launches
+    "floor_two_shot_us": 60.0,   # dense reduce-scatter + allgather: three launches, two dependent exchanges
+    "floor_bigring_us": 42.0,    # threshold + compress + apply
+    "floor_ring_us": 135.0,      # 3 P launches on side streams, two dependent exchanges
+    "hbm_bpus": 5.0e6,           # streaming kernels: ~5 TB/s effective
+    "link_dense_bpus": 5.5e5,    # dense peer stores / multimem: ~550 GB/s per direction
+    "link_pairs_bpus": 2.6e5,    # 8-byte pairs stored to P-1 peers by one kernel: ~260 GB/s out
+    "scatter_bpus": 1.2e6,       # decode: 64 bytes of sector traffic per pair
+}
+
+
+def schedule_costs(n: int, ratio: float, ranks: int, elem_bytes: int = 4) -> dict:
+    """Modelled microseconds of the three schedules ``select_schedule`` chooses from."""
+    c, p = _COST, max(int(ranks), 1)
+    pairs = 8.0 * ratio * n                                   # bytes of one rank's payload
+    one_shot = n * elem_bytes <= (1 << 20) or p <= 2
+    dense_link = (p - 1) * n * elem_bytes if one_shot else 2.0 * (p - 1) / p * n * elem_bytes
+    dense = ((c["floor_dense_us"] if one_shot else c["floor_two_shot_us"]) + dense_link / c["link_dense_bpus"]
+             + 3.0 * n * elem_bytes / c["hbm_bpus"])
+    bigring = (c["floor_bigring_us"] + 12.0 * n / c["hbm_bpus"] + (p - 1) * pairs / c["link_pairs_bpus"]
+               + (p - 1) * ratio * n * 64.0 / c["scatter_bpus"] / 8.0)
+    ring = (c["floor_ring_us"] + 12.0 * n / c["hbm_bpus"] + 2.0 * (p - 1) / p * pairs / c["link_pairs_bpus"]
+            + 2.0 * ratio * n * 64.0 / c["scatter_bpus"] / 8.0 + 8.0 * n / p / c["hbm_bpus"])
+    return {"bigring": dense, "comprex_bigring": bigring, "comprex_ring": ring}
+
+
+def select_schedule(n: int, ratio: float, ranks: int, elem_bytes: int = 4) -> str:
+    """``"bigring"`` (dense P2P kernels), ``"comprex_bigring"`` or ``"comprex_ring"``: the schedule
+    with the lowest modelled time for a vector of ``n`` elements at top-k ``ratio`` on ``ranks``
+    GPUs.  Tiny vectors are latency bound and go dense; a compressed BigRing pays (P-1) copies of
+    the payload and wins while the payload is small; the compressed Ring moves 2 (P-1)/P payloads
+    through two dependent exchanges and wins for large vectors and high ratios."""
+    if ranks <= 1:
+        return "comprex_bigring"
+    if ratio >= 1.0:
+        return "bigring"
+    costs = schedule_costs(n, ratio, ranks, elem_bytes)
+    return min(costs, key=costs.get)
+
+
+class AutoAllreduce(_AllreduceBase):
+    """The allreduce that ``select_schedule`` picks for (size, ratio, ranks), behind the common
+    surface (``apply``, ``flush``, ``reset``, ``set_compression_ratio``, ``stats``,
+    ``state_dict``).  ``choice`` names the schedule that was set up.  The compressed schedules are
+    set up replica-consistent (``consistent=True``) unless told otherwise."""
+
+    def setup_connections(self, size, tag=0, compression_ratio=0.01, size_factor=1.0, consistent=True,
+                          dtype=torch.float32):
+        env = self._env
+        es = torch.empty(0, dtype=dtype).element_size()
+        self.choice = select_schedule(int(size), float(compression_ratio), env.ranks, es)
+        if dtype != torch.float32:
+            self.choice = "bigring"           # compressed schedules exchange fp32 vectors
+        self.size, self.dtype = int(size), dtype
+        if self.choice == "bigring":
+            self.impl = BigRingAllreduce(self.gaspi_env)
+            self.impl.setup_connections(size, tag, dtype=dtype)
+        elif self.choice == "comprex_bigring":
+            self.impl = Comprex_BigRingAllreduce(self.gaspi_env)
+            self.impl.setup_connections(size, tag, compression_ratio, size_factor, consistent=consistent)
+        else:
+            self.impl = Comprex_RingAllreduce(self.gaspi_env)
+            self.impl.setup_connections(size, tag, compression_ratio, size_factor, consistent=consistent,
+                                        chunk_align=4)
+        self.compressed = self.impl.compressed
+
+    def apply(self, vector):
+        return self.impl.apply(vector)
+
+    __call__ = apply
+
+    def flush(self, vector):
+        return self.impl.flush(vector) if self.impl.compressed else vector
+
+    def reset(self):
+        if self.impl.compressed:
+            self.impl.reset()
+
+    def set_compression_ratio(self, compression_ratio):
+        """Changes top-k of the schedule that was chosen at set-up (the choice itself is kept:
+        slots and residuals belong to it)."""
+        if self.impl.compressed:
+            self.impl.set_compression_ratio(compression_ratio)
+
+    def stats(self):
+        return self.impl.stats() if self.impl.compressed else {}
+
+    def state_dict(self):
+        return {"choice": self.choice, "impl": self.impl.state_dict() if self.impl.compressed else None}
+
+    def load_state_dict(self, state):
+        if state["choice"] != self.choice:
+            raise ComprexError("state_dict belongs to another schedule")
+        if state["impl"] is not None:
+            self.impl.load_state_dict(state["impl"])

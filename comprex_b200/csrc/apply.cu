@@ -71,7 +71,7 @@ __device__ __forceinline__ bool wait_sources(const ApplyParams& p, uint32_t* s_n
   }
   __syncthreads();
   const uint32_t bad = s_bad;
-  if (bad && threadIdx.x == 0 && p.status) *p.status = *p.status | bad;
+  if (bad && threadIdx.x == 0 && p.status) atomicOr(p.status, bad);
   return bad == 0;
 }
 
@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(kThreads) apply_sparse_kernel(const ApplyParam
       __syncwarp();  // the next source may address the same elements from other lanes
     }
   }
-  if (bad && p.status) *p.status = *p.status | bad;
+  if (bad && p.status) atomicOr(p.status, bad);
 }
 
 // The update rule on four elements held in registers (g = scale * sum of the payloads).
@@ -163,9 +163,8 @@ __device__ __forceinline__ void store_state4(const CxApplyArgs& a, int64_t i, co
 }
 
 template <int OP, typename TO>
-__device__ __forceinline__ void update4(const ApplyParams& p, int64_t i, const float (&acc)[4],
-                                        bool vec) {
-  const CxApplyArgs& a = p.a;
+__device__ __forceinline__ void update4(const CxApplyArgs& a, const int64_t n, int64_t i,
+                                        const float (&acc)[4], bool vec) {
   if (OP == CX_OP_SET) {
     float o[4];
 #pragma unroll
@@ -173,7 +172,7 @@ __device__ __forceinline__ void update4(const ApplyParams& p, int64_t i, const f
     TO* out = reinterpret_cast<TO*>(a.out);
     if (vec) cx::store4(out + i, o);
     else
-      for (int e = 0; e < 4; ++e) if (i + e < p.n) out[i + e] = cx::Elem<TO>::from_f(o[e]);
+      for (int e = 0; e < 4; ++e) if (i + e < n) out[i + e] = cx::Elem<TO>::from_f(o[e]);
     return;
   }
   float* w = reinterpret_cast<float*>(a.out);
@@ -184,7 +183,7 @@ __device__ __forceinline__ void update4(const ApplyParams& p, int64_t i, const f
     if (OP == CX_OP_ADAMW) cx::load4(a.v + i, vv);
   } else {
     for (int e = 0; e < 4; ++e) {
-      const bool in = i + e < p.n;
+      const bool in = i + e < n;
       wv[e] = in ? w[i + e] : 0.f;
       mv[e] = (in && OP != CX_OP_SGD) ? a.m[i + e] : 0.f;
       vv[e] = (in && OP == CX_OP_ADAMW) ? a.v[i + e] : 0.f;
@@ -195,7 +194,7 @@ __device__ __forceinline__ void update4(const ApplyParams& p, int64_t i, const f
     store_state4<OP, TO>(a, i, wv, mv, vv);
   } else {
     for (int e = 0; e < 4; ++e) {
-      if (i + e >= p.n) continue;
+      if (i + e >= n) continue;
       w[i + e] = wv[e];
       if (OP != CX_OP_SGD) a.m[i + e] = mv[e];
       if (OP == CX_OP_ADAMW) a.v[i + e] = vv[e];
@@ -427,7 +426,7 @@ __global__ void __launch_bounds__(kBulkMaxThreads, 1) apply_dense_bulk_kernel(co
         if (i >= p.n) continue;
         float av[4];
         cx::load4(acc + e0, av);
-        update4<OP, TO>(p, i, av, p.vec && i + 3 < p.n);
+        update4<OP, TO>(p.a, p.n, i, av, p.vec && i + 3 < p.n);
       }
     }
     __syncwarp();
@@ -455,11 +454,46 @@ __global__ void __launch_bounds__(kThreads) apply_dense_kernel(const ApplyParams
       if (i >= p.n) continue;
       const float4 t = *reinterpret_cast<const float4*>(acc + e0);
       const float av[4] = {t.x, t.y, t.z, t.w};
-      update4<OP, TO>(p, i, av, p.vec && i + 3 < p.n);
+      update4<OP, TO>(p.a, p.n, i, av, p.vec && i + 3 < p.n);
     }
     __syncwarp();
   }
-  if (bad && p.status) *p.status = *p.status | bad;
+  if (bad && p.status) atomicOr(p.status, bad);
+}
+
+// ---- dense update: the averaged gradient is a plain vector -------------------------------
+// After a dense allreduce (or on a single rank, where nothing is exchanged) the gradient is an
+// ordinary fp32 vector; the same rule runs over it in one pass with 16-byte accesses.
+struct UpdateParams {
+  const float* g;
+  CxApplyArgs a;
+  int64_t n;
+  uint32_t vec;
+};
+
+template <int OP, typename TO>
+__global__ void __launch_bounds__(kThreads) update_dense_kernel(const UpdateParams q) {
+  const int64_t gsz = (int64_t)gridDim.x * kThreads;
+  const int64_t nv = (q.n + 3) / 4;
+  for (int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x; v < nv; v += gsz) {
+    const int64_t i = v * 4;
+    float gv[4];
+    const bool vec = q.vec && i + 3 < q.n;
+    if (vec) cx::load4(q.g + i, gv);
+    else
+      for (int e = 0; e < 4; ++e) gv[e] = i + e < q.n ? q.g[i + e] : 0.f;
+    update4<OP, TO>(q.a, q.n, i, gv, vec);
+  }
+}
+
+template <typename TO>
+int launch_update(const UpdateParams& q, int grid, cudaStream_t s) {
+  switch (q.a.op) {
+    case CX_OP_SGD: update_dense_kernel<CX_OP_SGD, TO><<<grid, kThreads, 0, s>>>(q); return 0;
+    case CX_OP_MOMENTUM: update_dense_kernel<CX_OP_MOMENTUM, TO><<<grid, kThreads, 0, s>>>(q); return 0;
+    case CX_OP_ADAMW: update_dense_kernel<CX_OP_ADAMW, TO><<<grid, kThreads, 0, s>>>(q); return 0;
+    default: return cx_set_error("cx_update_dense: op must be an update rule", 0);
+  }
 }
 
 // ---- verbatim forwarding of a received slot (ring allgather hop) ----------
@@ -479,11 +513,17 @@ __global__ void __launch_bounds__(kThreads) forward_kernel(const ForwardParams p
   __shared__ uint32_t s_ok, s_last;
   if (threadIdx.x == 0) s_ok = cx::wait_seq(&p.from.hdr->seq, p.expect, p.timeout_ns) ? 1u : 0u;
   __syncthreads();
-  if (!s_ok) {
-    if (threadIdx.x == 0 && p.status) *p.status = *p.status | CX_ST_TIMEOUT;
-    return;
+  // A CTA whose wait ran out copies nothing but still arrives at the completion counter and
+  // marks the launch as failed there: the CTA that arrives last then publishes nothing and
+  // leaves the counters clean for the next launch, whatever the other CTAs saw.
+  const bool ok = s_ok != 0;
+  if (!ok && threadIdx.x == 0) {
+    if (p.status) atomicOr(p.status, (uint32_t)CX_ST_TIMEOUT);
+    atomicOr(&p.ctr->pad[0], 1u);
   }
   CxHeader hv;
+  if (!ok) { hv.nnz = 0; hv.nsub = 0; hv.n = 0; hv.nnz_found = 0; hv.kind = CX_KIND_ERROR; hv.threshold = 0.f; hv.src_rank = 0; hv.dtype = 0; }
+  else
   {
     const uint4* hp = reinterpret_cast<const uint4*>(p.from.hdr);
     uint4* dp = reinterpret_cast<uint4*>(&hv);
@@ -513,7 +553,8 @@ __global__ void __launch_bounds__(kThreads) forward_kernel(const ForwardParams p
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  if ((int)threadIdx.x < p.tg.count) {
+  const uint32_t failed = *reinterpret_cast<volatile uint32_t*>(&p.ctr->pad[0]);
+  if (!failed && (int)threadIdx.x < p.tg.count) {
     CxHeader* o = p.tg.ep[threadIdx.x].hdr;
     o->bytes = 8ull + 8ull * nnz; o->n = h->n; o->nnz = nnz; o->nnz_found = h->nnz_found;
     o->kind = h->kind; o->threshold = h->threshold; o->nsub = nsub; o->src_rank = h->src_rank;
@@ -521,7 +562,8 @@ __global__ void __launch_bounds__(kThreads) forward_kernel(const ForwardParams p
     __threadfence_system();
     cx::st_release_sys(&o->seq, p.seq);
   }
-  if (threadIdx.x == 0) p.ctr->done = 0;
+  __syncthreads();
+  if (threadIdx.x == 0) { p.ctr->pad[0] = 0; p.ctr->done = 0; }
 }
 
 #ifndef CX_APPLY_STAGES
@@ -630,6 +672,34 @@ int cx_apply_cuda(const CxSources* src, int64_t n, const CxApplyArgs* a, uint32_
   if (rc) return rc;
   cx_note_launch();
   return cx_check_launch("apply_kernel");
+}
+
+int cx_update_dense_cuda(const float* g, int64_t n, const CxApplyArgs* a, void* stream) {
+  if (!a->out || !g) return cx_set_error("cx_update_dense: NULL vector", 0);
+  if (n < 0 || n > 0x7fffffffLL) return cx_set_error("cx_update_dense: n out of range", 0);
+  if (a->op != CX_OP_SGD && a->op != CX_OP_MOMENTUM && a->op != CX_OP_ADAMW)
+    return cx_set_error("cx_update_dense: op must be an update rule", 0);
+  if (a->op != CX_OP_SGD && !a->m) return cx_set_error("cx_update_dense: momentum buffer missing", 0);
+  if (a->op == CX_OP_ADAMW && !a->v) return cx_set_error("cx_update_dense: second-moment buffer missing", 0);
+  if (n == 0) return 0;
+  UpdateParams q;
+  q.g = g; q.a = *a; q.n = n;
+  q.vec = aligned16(g) && aligned16(a->out) && (!a->shadow || aligned16(a->shadow)) && (!a->m || aligned16(a->m)) &&
+          (!a->v || aligned16(a->v));
+  int grid = cx_sm_count() * 8;
+  const int need = (int)(((n + 3) / 4 + kThreads - 1) / kThreads);
+  if (grid > need) grid = need;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int rc;
+  switch (a->shadow ? a->shadow_dtype : CX_F32) {
+    case CX_F32: rc = launch_update<float>(q, grid, s); break;
+    case CX_BF16: rc = launch_update<__nv_bfloat16>(q, grid, s); break;
+    case CX_F16: rc = launch_update<__half>(q, grid, s); break;
+    default: return cx_set_error("cx_update_dense: unsupported dtype on CUDA", 0);
+  }
+  if (rc) return rc;
+  cx_note_launch();
+  return cx_check_launch("update_dense_kernel");
 }
 
 int cx_forward_cuda(const CxEndpoint* from, uint64_t expect_seq, const CxTargets* tg, uint64_t seq,

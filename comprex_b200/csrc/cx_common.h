@@ -163,6 +163,11 @@ int cx_compress(int dev, int gdtype, const void* g, float* r, int64_t n,
 int cx_apply(int dev, const CxSources* src, int64_t n, const CxApplyArgs* a,
              uint32_t* status, uint64_t timeout_ns, void* stream);
 
+/* The same update rules on a dense averaged gradient g (fp32): what follows a dense allreduce,
+ * and the whole step of a single rank (keras/comprex_optimizer.py:150-163).  a->scale
+ * multiplies g; a->op is CX_OP_SGD, CX_OP_MOMENTUM or CX_OP_ADAMW. */
+int cx_update_dense(int dev, const float* g, int64_t n, const CxApplyArgs* a, void* stream);
+
 /* copy a received sparse slot verbatim into other slots (forward_buffer /
  * readRemote_forward, src/comprEx.tpp:248-301); counters: one zeroed
  * CxWorkCounters in device memory */
@@ -250,6 +255,7 @@ int cx_host_free(void* p);
 #define CX_OPK_APPLY 3
 #define CX_OPK_DENSE_SEND 4
 #define CX_OPK_DENSE_REDUCE 5
+#define CX_OPK_UPDATE 6        /* cx_update_dense: g, n, apply */
 
 typedef struct CxOp {
   int32_t kind;

@@ -186,7 +186,7 @@ __device__ __forceinline__ bool wait_dense(const CxSources& src, uint64_t timeou
   }
   __syncthreads();
   const uint32_t bad = s_bad;
-  if (bad && threadIdx.x == 0 && status) *status = *status | bad;
+  if (bad && threadIdx.x == 0 && status) atomicOr(status, bad);
   return bad == 0;
 }
 
@@ -229,7 +229,20 @@ __device__ __forceinline__ float ldcg1<__half>(const __half* p) {
 template <typename T>
 __global__ void __launch_bounds__(kThreads) dense_reduce_kernel(const ReduceParams p) {
   __shared__ uint32_t s_last;
-  if (!wait_dense(p.src, p.timeout_ns, p.status, p.dtype, p.seq_cell)) return;
+  if (!wait_dense(p.src, p.timeout_ns, p.status, p.dtype, p.seq_cell)) {
+    // The verdict is per CTA, the bookkeeping is per grid: a CTA that gave up still arrives at
+    // the completion counter of a pushing launch and marks the launch as failed, so that the
+    // CTA arriving last publishes nothing and hands clean counters to the next launch.
+    if (!p.has_push) return;
+    if (threadIdx.x == 0) {
+      atomicOr(&p.ctr->pad[0], 1u);
+      __threadfence();
+      s_last = (atomicAdd(&p.ctr->done, 1u) == gridDim.x - 1) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) { p.ctr->pad[0] = 0; p.ctr->done = 0; }
+    return;
+  }
   T* out = reinterpret_cast<T*>(p.out);
   const T* own = reinterpret_cast<const T*>(p.own);
   const int64_t gtid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
@@ -311,9 +324,11 @@ __global__ void __launch_bounds__(kThreads) dense_reduce_kernel(const ReducePara
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  if ((int)threadIdx.x < p.push.count)
+  const uint32_t failed = *reinterpret_cast<volatile uint32_t*>(&p.ctr->pad[0]);
+  if (!failed && (int)threadIdx.x < p.push.count)
     publish_dense<T>(p.push, threadIdx.x, p.n, cx::seq_of(p.seq_cell, p.push_seq), p.src_rank, p.dtype);
-  if (threadIdx.x == 0) p.ctr->done = 0;
+  __syncthreads();
+  if (threadIdx.x == 0) { p.ctr->pad[0] = 0; p.ctr->done = 0; }
 }
 
 // ---- elementwise helpers ----------------------------------------------------

@@ -225,6 +225,30 @@ int cx_compress_host(int gdtype, const void* g, float* r, int64_t n, const float
   return 0;
 }
 
+// The parameter update of one element from its averaged gradient g (SGD, momentum, AdamW);
+// shared by the sparse receive path and the dense update.
+static inline void rule_host(const CxApplyArgs* a, float* w, int64_t i, float g, int sdt) {
+  float wv = w[i];
+  if (a->op == CX_OP_SGD) {
+    wv = (1.f - a->wd) * wv - g;
+  } else if (a->op == CX_OP_MOMENTUM) {
+    const float mv = a->momentum * a->m[i] + a->lr * g;
+    a->m[i] = mv;
+    wv = (1.f - a->wd) * wv - mv;
+  } else {
+    // same operation order as the kernel (fused multiply-adds in the same places); the
+    // kernel's square root and reciprocal are the hardware approximations, so w agrees
+    // to a few ulp of the step, m and v bit for bit
+    const float mv = fmaf(a->beta1, a->m[i], (1.f - a->beta1) * g);
+    const float vv = fmaf(a->beta2, a->v[i], ((1.f - a->beta2) * g) * g);
+    a->m[i] = mv; a->v[i] = vv;
+    const float mh = mv * (1.f / a->bc1), vh = vv * (1.f / a->bc2);
+    wv = fmaf(-(a->lr * mh), 1.f / (sqrtf(vh) + a->eps), wv * (1.f - a->lr * a->wd));
+  }
+  w[i] = wv;
+  if (a->shadow) store_elem(sdt, a->shadow, i, wv);
+}
+
 int cx_apply_host(const CxSources* src, int64_t n, const CxApplyArgs* a, uint32_t* status,
                   uint64_t timeout_ns) {
   if (src->count < 0 || src->count > CX_MAX_PEERS) return cx_set_error("cx_apply: bad source count", 0);
@@ -273,25 +297,7 @@ int cx_apply_host(const CxSources* src, int64_t n, const CxApplyArgs* a, uint32_
     for (int64_t i = lo; i < hi; ++i) {
       const float g = a->scale * acc[i - lo];
       if (a->op == CX_OP_SET) { store_elem(a->out_dtype, a->out, i, g); continue; }
-      float wv = w[i];
-      if (a->op == CX_OP_SGD) {
-        wv = (1.f - a->wd) * wv - g;
-      } else if (a->op == CX_OP_MOMENTUM) {
-        const float mv = a->momentum * a->m[i] + a->lr * g;
-        a->m[i] = mv;
-        wv = (1.f - a->wd) * wv - mv;
-      } else {
-        // same operation order as the kernel (fused multiply-adds in the same places); the
-        // kernel's square root and reciprocal are the hardware approximations, so w agrees
-        // to a few ulp of the step, m and v bit for bit
-        const float mv = fmaf(a->beta1, a->m[i], (1.f - a->beta1) * g);
-        const float vv = fmaf(a->beta2, a->v[i], ((1.f - a->beta2) * g) * g);
-        a->m[i] = mv; a->v[i] = vv;
-        const float mh = mv * (1.f / a->bc1), vh = vv * (1.f / a->bc2);
-        wv = fmaf(-(a->lr * mh), 1.f / (sqrtf(vh) + a->eps), wv * (1.f - a->lr * a->wd));
-      }
-      w[i] = wv;
-      if (a->shadow) store_elem(sdt, a->shadow, i, wv);
+      rule_host(a, w, i, g, sdt);
     }
   }
   if (bad && status) *status |= bad;
@@ -566,5 +572,18 @@ int cx_fold_host(int gdtype, const void* const* seg_ptr, const int64_t* item_off
       dst[i] = mu * y + a * load_elem(gdtype, seg_ptr[seg], item_rel[it] + i);
     }
   }
+  return 0;
+}
+
+// Dense form of the update: the averaged gradient is a plain fp32 vector (a dense allreduce's
+// result, or this rank's own vector when it is alone), keras/comprex_optimizer.py:150-163.
+int cx_update_dense_host(const float* g, int64_t n, const CxApplyArgs* a) {
+  if (!a->out || !g) return cx_set_error("cx_update_dense: NULL vector", 0);
+  if (a->op != CX_OP_SGD && a->op != CX_OP_MOMENTUM && a->op != CX_OP_ADAMW)
+    return cx_set_error("cx_update_dense: op must be an update rule", 0);
+  if (a->op != CX_OP_SGD && !a->m) return cx_set_error("cx_update_dense: momentum buffer missing", 0);
+  if (a->op == CX_OP_ADAMW && !a->v) return cx_set_error("cx_update_dense: second-moment buffer missing", 0);
+  float* w = reinterpret_cast<float*>(a->out);
+  for (int64_t i = 0; i < n; ++i) rule_host(a, w, i, a->scale * g[i], a->shadow_dtype);
   return 0;
 }

@@ -54,6 +54,8 @@ int cx_fold_cuda(int, const void* const*, const int64_t*, const int64_t*, const 
 int cx_fold_host(int, const void* const*, const int64_t*, const int64_t*, const int32_t*, const int32_t*,
                  const int32_t*, int, float*, float*, float, float, float);
 int cx_axpy_host(int, void*, int, const void*, float, int64_t);
+int cx_update_dense_cuda(const float*, int64_t, const CxApplyArgs*, void*);
+int cx_update_dense_host(const float*, int64_t, const CxApplyArgs*);
 
 // ---- errors and accounting -------------------------------------------------------
 static thread_local char g_err[512] = "";
@@ -111,6 +113,10 @@ int cx_apply(int dev, const CxSources* src, int64_t n, const CxApplyArgs* a, uin
              uint64_t timeout_ns, void* stream) {
   return dev == CX_DEV_CUDA ? cx_apply_cuda(src, n, a, status, timeout_ns, stream)
                             : cx_apply_host(src, n, a, status, timeout_ns);
+}
+
+int cx_update_dense(int dev, const float* g, int64_t n, const CxApplyArgs* a, void* stream) {
+  return dev == CX_DEV_CUDA ? cx_update_dense_cuda(g, n, a, stream) : cx_update_dense_host(g, n, a);
 }
 
 int cx_forward(int dev, const CxEndpoint* from, uint64_t expect_seq, const CxTargets* tg,
@@ -209,6 +215,8 @@ int run_one(CxOp& o, uint64_t seq, void* stream) {
                              o.has_push ? &o.tg : nullptr, seq, o.has_ranges ? o.starts : nullptr,
                              o.has_ranges ? o.lens : nullptr, o.workspace, o.src_rank, o.status,
                              o.timeout_ns, stream);
+    case CX_OPK_UPDATE:
+      return cx_update_dense(o.dev, reinterpret_cast<const float*>(o.g), o.n, &o.apply, stream);
     default:
       return cx_set_error("cx_run_ops: unknown op kind", 0);
   }

@@ -57,6 +57,7 @@ class ComprexHookState:
             if n * torch.empty(0, dtype=dtype).element_size() < self.dense_fallback_bytes:
                 red = _ar.BigRingAllreduce(self.env)
                 red.setup_connections(n, 1, dtype=dtype)
+                red.result_scale = 1.0 / self.env.ranks        # the mean comes out of the reducing kernel
             else:
                 red = _ar.Comprex_BigRingAllreduce(self.env)
                 red.setup_connections(n, 1, self.compression_ratio, self._size_factor(n), consistent=True)
@@ -117,7 +118,6 @@ def comprex_hook(state: ComprexHookState, bucket: dist.GradBucket) -> torch.futu
         else:
             for phase in red._plan_apply(buf):
                 phase()
-            buf.mul_(scale)
 
     if cuda:
         comm = state.stream()

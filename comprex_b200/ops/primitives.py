@@ -138,6 +138,17 @@ def _flat(t: torch.Tensor, what: str) -> torch.Tensor:
     return t
 
 
+def compress_regions(n: int, cap: int):
+    """(regions, pairs per region) the compress kernel uses for a vector of ``n`` elements and a
+    slot of ``cap`` pairs (the rule of ``cx_compress``: at least 8 sub-tiles and 256 pairs per
+    region, at most 32 regions, a power of two)."""
+    nsub = (n + _lib.SUBTILE - 1) // _lib.SUBTILE
+    regions = 1
+    while regions < 32 and nsub // (2 * regions) >= 8 and cap // (2 * regions) >= 256:
+        regions *= 2
+    return regions, cap // regions
+
+
 class Compressor:
     """Scratch, threshold cell and statistics of one sparse sender.
 
@@ -264,6 +275,20 @@ def args_update(op: int, w: torch.Tensor, scale: float, *, shadow=None, m=None, 
     a.bc1 = 1.0 - beta1 ** step
     a.bc2 = 1.0 - beta2 ** step
     return a
+
+
+def update_dense(env: GaspiEnvironment, g: torch.Tensor, n: int, args: ApplyArgs) -> None:
+    """Parameter update from a dense averaged gradient ``g`` (float32): what follows a dense
+    allreduce, and the whole step of a single rank (keras/comprex_optimizer.py:150-163)."""
+    if g.dtype != torch.float32:
+        raise ComprexError("the dense update reads a float32 vector")
+    if _recording(env):
+        op = _new_op(env, _lib.OPK_UPDATE, _lib.F32, n)
+        op.g, op.apply = g.data_ptr(), args
+        env._rec.append(op)
+        return
+    _lib.check(env.lib.cx_update_dense(env.dev, g.data_ptr(), n, C.byref(args), _lib.stream_ptr(env.device)),
+               "cx_update_dense")
 
 
 def forward(env: GaspiEnvironment, src: Endpoint, expect_seq: int, targets: Targets, seq: int, cap: int,

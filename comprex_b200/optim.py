@@ -32,9 +32,21 @@ drops the learning rate there, keras/comprex_optimizer.py:134-141).
 
 ``rule="adamw"`` exchanges the clipped gradient itself and runs AdamW in the
 receive kernel.  Residuals, momentum and master weights travel in
-``state_dict()`` under the key ``"comprex"``.
+``state_dict()`` under the key ``"comprex"``, keyed by parameter.
+
+All six collectives of the reference (keras/comprex_optimizer.py:49-70) run through the same
+bucketed, overlapped step.  ``comprex_bigring`` and ``comprex_ring`` (replica-consistent) fuse the
+parameter update into their final decode; the other types, and ``consistent=False``, allreduce a
+work copy of the bucket's vector in place and update from it with one dense kernel.
+``allreduce_type="auto"`` picks per bucket between the dense kernels, the compressed BigRing and
+the compressed Ring (``allreduce.select_schedule``).  ``aggregate_blob=False`` is the reference's
+per-tensor mode (keras/comprex_optimizer.py:77-96): one allreducer per tensor.  A single rank
+exchanges nothing (keras/comprex_optimizer.py:134-141): the clipped, folded gradient goes straight
+into the dense update kernel.
 """
 from __future__ import annotations
+
+import warnings
 
 import torch
 
@@ -51,12 +63,14 @@ _TYPES = {
 
 
 class _Bucket:
-    __slots__ = ("start", "end", "params", "offsets", "ar", "ready", "sent", "seq", "par", "fold")
+    __slots__ = ("start", "end", "params", "offsets", "ar", "ready", "sent", "seq", "par", "fold", "kind", "xbuf",
+                 "plan", "u")
 
     def __init__(self, start):
         self.start, self.end = start, start
         self.params, self.offsets = [], []
         self.ar, self.ready, self.sent, self.fold = None, 0, False, None
+        self.kind, self.xbuf, self.plan, self.u = None, None, None, None
 
 
 _ITEM = 65536     # elements per fold work item
@@ -134,22 +148,26 @@ class ComprexOptimizer(torch.optim.Optimizer):
     def __init__(self, params, gaspi_env, lr=0.01, momentum=0.9, compression_ratio=0.01, nesterov=False,
                  allreduce_type="comprex_bigring", size_factor=1.0, logging=False, pre_clipnorm=5.0,
                  weight_decay=0.0, local_momentum=True, rule="sgd", betas=(0.9, 0.999), eps=1e-8,
-                 learning_rate=None, bucket_cap_mb=None, overlap=False, consistent=True, name="ComprexOptimizer"):
+                 learning_rate=None, bucket_cap_mb=None, overlap=False, consistent=True, aggregate_blob=True,
+                 single_rank_bypass=True, name="ComprexOptimizer"):
         if learning_rate is not None:
             lr = learning_rate
         if not 0 <= momentum <= 1:
             raise ValueError("`momentum` must be between [0, 1].")
-        if allreduce_type not in _TYPES:
+        if allreduce_type not in _TYPES and allreduce_type != "auto":
             raise ValueError("AllreduceOp with name %s is not known!" % allreduce_type)
         if rule not in ("sgd", "adamw"):
             raise ValueError("rule must be 'sgd' or 'adamw'")
+        if nesterov:
+            warnings.warn("ComprexOptimizer: nesterov=True is accepted for interface parity and has no effect "
+                          "(the reference stores the flag and never reads it, keras/comprex_optimizer.py:33)")
         defaults = dict(lr=lr, momentum=momentum, weight_decay=weight_decay)
         super().__init__(params, defaults)
         self.gaspi_env = gaspi_env
         self.name = name
         self._env = env = gaspi_env.get()
         self.compression_ratio = float(compression_ratio)
-        self.nesterov = nesterov          # accepted and unused, like the reference
+        self.nesterov = nesterov
         self.logging = logging
         self.allreduce_type = allreduce_type
         self.size_factor = float(size_factor)
@@ -159,29 +177,39 @@ class ComprexOptimizer(torch.optim.Optimizer):
         self.betas, self.eps = betas, eps
         self.momentum_correction = 1.0
         self._t = 0
-        # consistent=False is the reference's rule for the compressed BigRing (a rank applies its
+        # consistent=False is the reference's rule for the compressed collectives (a rank applies its
         # own update densely and the peers' sparsely, keras/comprex_optimizer.py:117-133 with
-        # src/allreduce.tpp:649-681): replicas drift apart by what each keeps in its residual.  It
-        # runs through the generic path (allreduce in place, then a tensor update).
+        # src/allreduce.tpp:649-681): replicas drift apart by what each keeps in its residual.
         self.consistent = bool(consistent)
-        self._fused = allreduce_type == "comprex_bigring" and self.consistent
-        if (bucket_cap_mb or overlap) and not self._fused:
-            raise ComprexError("buckets and overlap need allreduce_type='comprex_bigring'")
+        self.aggregate_blob = bool(aggregate_blob)
+        # a job of one rank exchanges nothing (keras/comprex_optimizer.py:134-141)
+        self._local = env.ranks == 1 and bool(single_rank_bypass)
 
-        plist = [p for g in self.param_groups for p in g["params"] if p.requires_grad]
-        if not plist:
+        # keys: the names torch recorded when named parameters were passed, else the position
+        keyed, pos = [], 0
+        for g in self.param_groups:
+            names = g.get("param_names")
+            for i, p in enumerate(g["params"]):
+                if p.requires_grad:
+                    keyed.append((str(names[i]) if names else f"param{pos}", p))
+                pos += 1
+        if not keyed:
             raise ValueError("optimizer got an empty parameter list")
+        plist = [p for _, p in keyed]
         dt = plist[0].dtype
         if any(p.dtype != dt or p.device != env.device for p in plist):
             raise ComprexError("all parameters must share one dtype and live on the environment's device")
         # reverse order: the gradients that backward produces first come first
-        self._params = plist[::-1]
+        keyed = keyed[::-1]
+        self._params = [p for _, p in keyed]
+        self._keys = [k for k, _ in keyed]
         es = torch.empty(0, dtype=dt).element_size()
         cap_elems = int(bucket_cap_mb * (1 << 20) / es) if bucket_cap_mb else None
         self._buckets, self._offsets, off = [_Bucket(0)], [], 0
         for p in self._params:
             b = self._buckets[-1]
-            if cap_elems and b.params and (off - b.start) + p.numel() > cap_elems:
+            full = cap_elems and (off - b.start) + p.numel() > cap_elems
+            if b.params and (full or not self.aggregate_blob):
                 off = (off + 1023) // 1024 * 1024          # buckets start on a sub-tile boundary
                 b = _Bucket(off)
                 self._buckets.append(b)
@@ -215,11 +243,10 @@ class ComprexOptimizer(torch.optim.Optimizer):
         self._m = torch.zeros(n, dtype=torch.float32, device=dev) if rule == "adamw" or not local_momentum else None
         self._v = torch.zeros(n, dtype=torch.float32, device=dev) if rule == "adamw" else None
         self.comprex_allreducers = {}
-        self._xbuf = None
         self._comm = None
         # with a single bucket there is nothing to overlap with: its last gradient appears when
         # backward ends, and the hooks and the side stream would only add latency
-        self.overlap = bool(overlap) and dev.type == "cuda" and len(self._buckets) > 1
+        self.overlap = bool(overlap) and dev.type == "cuda" and len(self._buckets) > 1 and not self._local
         self._armed = False
         self._hooks = []
         if self.overlap:
@@ -240,7 +267,8 @@ class ComprexOptimizer(torch.optim.Optimizer):
         if name == "comprex_bigring":
             ar.setup_connections(size, 1, self.compression_ratio, self.size_factor, consistent=self.consistent)
         elif name == "comprex_ring":
-            ar.setup_connections(size, 1, self.compression_ratio, self.size_factor)
+            ar.setup_connections(size, 1, self.compression_ratio, self.size_factor, consistent=self.consistent,
+                                 chunk_align=4)
         elif name == "comprex_alltoone":
             ar.setup_connections(size, 1, 0, self.compression_ratio, self.size_factor)
         elif name == "alltoone":
@@ -250,14 +278,39 @@ class ComprexOptimizer(torch.optim.Optimizer):
         return ar
 
     def _ensure_allreducers(self) -> None:
-        if self.comprex_allreducers:
+        if self._armed:
             return
-        if self._fused:
-            for i, b in enumerate(self._buckets):
-                b.ar = self.comprex_allreducers[i] = self.create_allreduce_op(self.allreduce_type, b.end - b.start)
-        else:
-            self._buckets[0].ar = self.comprex_allreducers[0] = self.create_allreduce_op(self.allreduce_type, self.blob_size)
+        dev = self._env.device
+        for i, b in enumerate(self._buckets):
+            n = b.end - b.start
+            if self._local:
+                b.kind = "local"
+                continue
+            name = self.allreduce_type
+            if name == "auto":
+                name = _ar.select_schedule(n, self.compression_ratio, self._env.ranks)
+            b.ar = self.comprex_allreducers[i] = self.create_allreduce_op(name, n)
+            if name == "comprex_bigring" and self.consistent:
+                b.kind = "bigring"
+            elif name == "comprex_ring" and self.consistent:
+                b.kind = "ring"
+            else:
+                b.kind = "phased"
+            if b.kind != "bigring":
+                b.xbuf = torch.empty(n, dtype=torch.float32, device=dev)     # the exchange works in place on a copy
         self._armed = True
+
+    def describe(self) -> str:
+        """One line that names the exchange of every bucket (for logs and benchmark records)."""
+        if self._local:
+            return "single rank: no exchange, dense fused update"
+        self._ensure_allreducers()
+        kinds = {}
+        for b in self._buckets:
+            name = type(b.ar).__name__ + ("" if b.kind == "phased" else " (update fused into the decode)")
+            kinds[name] = kinds.get(name, 0) + 1
+        mode = "replica-consistent" if self.consistent else "reference semantics (own update dense)"
+        return "; ".join(f"{v} x {k}" for k, v in kinds.items()) + f"; direct NVLink peer stores, {mode}"
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         """Drop the gradients (autograd then writes fresh tensors, which the fold kernels read
@@ -313,11 +366,40 @@ class ComprexOptimizer(torch.optim.Optimizer):
         return self._comm
 
     def _send(self, b: _Bucket) -> None:
+        """First half of a bucket's exchange: fold, then everything that waits for nobody."""
         lr, mu, _ = self._hyper()
         with nvtx_range("comprex.fold+send"):
-            x = self._fold(b, lr, mu)
-            b.seq, b.par = b.ar.send_fast(x)
+            u = self._fold(b, lr, mu)
+            if b.kind == "bigring":
+                b.seq, b.par = b.ar.send_fast(u)
+            elif b.kind == "ring":
+                b.xbuf.copy_(u)
+                b.seq, b.par = b.ar.send_fast(b.xbuf)
+            elif b.kind == "phased":
+                b.xbuf.copy_(u)
+                b.plan = b.ar._plan_apply(b.xbuf)
+                if b.plan:
+                    b.plan[0]()                 # the first phase of every schedule only sends
+            else:
+                b.u = u
         b.sent = True
+
+    def _recv(self, b: _Bucket, lr, mu, wd) -> None:
+        """Second half: wait for the peers, reduce / decode, update the parameters."""
+        env, n = self._env, b.end - b.start
+        with nvtx_range("comprex.recv+update"):
+            if b.kind == "bigring":
+                b.ar.recv_fast(b.seq, b.par, self._args(b.start, n, lr, mu, wd, 1.0 / env.ranks))
+            elif b.kind == "ring":
+                b.ar.recv_fast(b.xbuf, b.seq, b.par,
+                               lambda c, start, size: self._args(b.start + start, size, lr, mu, wd, 1.0 / env.ranks))
+            elif b.kind == "phased":
+                for phase in b.plan[1:]:
+                    phase()
+                b.plan = None
+                P.update_dense(env, b.xbuf, n, self._args(b.start, n, lr, mu, wd, 1.0 / env.ranks))
+            else:
+                P.update_dense(env, b.u, n, self._args(b.start, n, lr, mu, wd, 1.0))
 
     def no_sync(self):
         """Context for gradient accumulation with ``overlap=True``: backward passes inside it
@@ -346,17 +428,20 @@ class ComprexOptimizer(torch.optim.Optimizer):
         with torch.cuda.stream(comm):
             self._send(b)
 
-    def _recv_args(self, b: _Bucket, lr, mu, wd):
-        nr = self._env.ranks
-        sl = slice(b.start, b.end)
+    def _args(self, start: int, n: int, lr, mu, wd, scale: float):
+        """Receive-side update of the flat range [start, start + n): the rule and its state."""
+        sl = slice(start, start + n)
         sh = None if self._shadow is None else self._shadow[sl]
         if self.rule == "adamw":
-            return P.args_update(_lib.OP_ADAMW, self._master[sl], 1.0 / nr, shadow=sh, m=self._m[sl], v=self._v[sl],
+            return P.args_update(_lib.OP_ADAMW, self._master[sl], scale, shadow=sh, m=self._m[sl], v=self._v[sl],
                                  lr=lr, beta1=self.betas[0], beta2=self.betas[1], eps=self.eps, wd=wd, step=self._t)
         if self.local_momentum:
-            return P.args_update(_lib.OP_SGD, self._master[sl], 1.0 / nr, shadow=sh, wd=wd)
-        return P.args_update(_lib.OP_MOMENTUM, self._master[sl], 1.0 / nr, shadow=sh, m=self._m[sl], lr=lr,
+            return P.args_update(_lib.OP_SGD, self._master[sl], scale, shadow=sh, wd=wd)
+        return P.args_update(_lib.OP_MOMENTUM, self._master[sl], scale, shadow=sh, m=self._m[sl], lr=lr,
                              momentum=mu * self.momentum_correction, wd=wd)
+
+    def _recv_args(self, b: _Bucket, lr, mu, wd):
+        return self._args(b.start, b.end - b.start, lr, mu, wd, 1.0 / self._env.ranks)
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -366,12 +451,8 @@ class ComprexOptimizer(torch.optim.Optimizer):
                 loss = closure()
         lr, mu, wd = self._hyper()
         self._t += 1
-        first = not self.comprex_allreducers
+        first = not self._armed
         self._ensure_allreducers()
-        if not self._fused:
-            self._generic_step(self._buckets[0].ar, self._fold(self._buckets[0], lr, mu), lr, mu, wd)
-            self._env.maybe_check()
-            return loss
         use_side = self.overlap and not first
         if use_side:
             comm = self._comm_stream()
@@ -385,36 +466,12 @@ class ComprexOptimizer(torch.optim.Optimizer):
                 if not b.sent:
                     self._send(b)
             for b in self._buckets:          # then receive: all peers' payloads are on their way
-                with nvtx_range("comprex.recv+update"):
-                    b.ar.recv_fast(b.seq, b.par, self._recv_args(b, lr, mu, wd))
+                self._recv(b, lr, mu, wd)
                 b.sent, b.ready = False, 0
         if use_side:
             torch.cuda.current_stream(self._env.device).wait_stream(comm)
         self._env.maybe_check()
         return loss
-
-    def _generic_step(self, ar, x, lr, mu, wd) -> None:
-        """Other collectives: allreduce a copy of the vector in place, then update with tensor ops."""
-        if self._xbuf is None:
-            self._xbuf = torch.empty(self.blob_size, dtype=torch.float32, device=self._env.device)
-        buf = self._xbuf
-        buf.copy_(x)
-        ar.apply(buf)
-        avg = buf.div_(self._env.ranks)
-        if self.rule == "adamw":
-            b1, b2 = self.betas
-            self._m.mul_(b1).add_(avg, alpha=1 - b1)
-            self._v.mul_(b2).addcmul_(avg, avg, value=1 - b2)
-            mh = self._m / (1 - b1 ** self._t)
-            vh = self._v / (1 - b2 ** self._t)
-            self._master.mul_(1 - lr * wd).addcdiv_(mh, vh.sqrt_().add_(self.eps), value=-lr)
-        elif self.local_momentum:
-            self._master.mul_(1 - wd).sub_(avg)
-        else:
-            self._m.mul_(mu * self.momentum_correction).add_(avg, alpha=lr)
-            self._master.mul_(1 - wd).sub_(self._m)
-        if self._shadow is not None:
-            self._shadow.copy_(self._master)
 
     def apply_gradients(self, grads_and_vars, *args, **kwargs):
         """Keras-style entry (keras/comprex_optimizer.py:144-145): ``(gradient, variable)`` pairs are
@@ -453,57 +510,109 @@ class ComprexOptimizer(torch.optim.Optimizer):
         return ar.stats() if ar is not None and ar.compressed else {}
 
     # ---- checkpoint ---------------------------------------------------------------------------------
+    def _layout(self):
+        """(key, offset, numel) of every parameter in the flat buffers."""
+        return [(k, int(o), int(p.numel())) for k, o, p in zip(self._keys, self._offsets, self._params)]
+
+    def _residual_flat(self):
+        """The buckets' main residuals as one vector in the layout of the flat buffers."""
+        if not self.comprex_allreducers:
+            return None
+        flat = torch.zeros(self.blob_size, dtype=torch.float32)
+        for b in self._buckets:
+            r = getattr(b.ar, "rests", None) if b.ar is not None else None
+            if r is not None:
+                flat[b.start:b.start + r.numel()] = r.detach().cpu()
+        return flat
+
     def state_dict(self):
         sd = super().state_dict()
         self._env.flush()
         ars = [b.ar for b in self._buckets]
         sd["comprex"] = {
-            "version": 1, "world_size": self._env.ranks, "rank": self._env.rank, "ratio": self.compression_ratio,
+            "version": 2, "world_size": self._env.ranks, "rank": self._env.rank, "ratio": self.compression_ratio,
             "topology": self.allreduce_type, "step": self._t, "rule": self.rule,
+            "layout": self._layout(), "buckets": [(b.start, b.end, type(b.ar).__name__) for b in self._buckets],
             "master": self._master.detach().cpu().clone(), "update": self._update.detach().cpu().clone(),
             "m": None if self._m is None else self._m.detach().cpu().clone(),
             "v": None if self._v is None else self._v.detach().cpu().clone(),
+            "residual": self._residual_flat(),
             "allreduce": [a.state_dict() if a is not None and a.compressed else None for a in ars],
         }
         return sd
 
+    def _remap(self, flat, layout):
+        """A flat vector saved under ``layout`` rearranged into this optimizer's layout, by key."""
+        if flat is None:
+            return None
+        saved = {k: (o, n) for k, o, n in layout}
+        out = torch.zeros(self.blob_size, dtype=flat.dtype)
+        for k, o, n in self._layout():
+            if k not in saved or saved[k][1] != n:
+                raise ComprexError(f"checkpoint has no parameter '{k}' of {n} elements: it was written for another model")
+            so = saved[k][0]
+            out[o:o + n] = flat[so:so + n]
+        return out
+
     def load_state_dict(self, state_dict):
         state_dict = dict(state_dict)
         cs = state_dict.pop("comprex", None)
+        layout, mine = None, self._layout()
+        if cs is not None:
+            layout = cs.get("layout")
+            if layout is None:                              # version 1: flat vectors in this layout or nothing
+                if cs["master"].numel() != self.blob_size:
+                    raise ComprexError("checkpoint belongs to a model of a different size")
+                layout = mine
+            if len(layout) != len(mine) or {k for k, _, _ in layout} != {k for k, _, _ in mine}:
+                raise ComprexError("checkpoint was written for other parameters (names or count differ)")
         super().load_state_dict(state_dict)
         if cs is None:
             return
-        if cs["master"].numel() != self.blob_size:
-            raise ComprexError("checkpoint belongs to a model of a different size")
+        same_layout = [tuple(x) for x in layout] == mine
+        pick = (lambda t: t) if same_layout else (lambda t: self._remap(t, layout))
         dev = self._env.device
         self._t = cs["step"]
-        self.compression_ratio = cs["ratio"]
         # Weights and the Adam moments are replicated, so any rank's file restores them.  The
         # local momentum and the residuals are this rank's own: a file written by another rank
         # (a new rank of a larger job, or everybody loading rank 0's file) starts them at zero.
         foreign = int(cs.get("rank", self._env.rank)) != self._env.rank
-        self._master.copy_(cs["master"].to(dev))
+        self._master.copy_(pick(cs["master"]).to(dev))
         if foreign:
             self._update.zero_()
         else:
-            self._update.copy_(cs["update"].to(dev))
+            self._update.copy_(pick(cs["update"]).to(dev))
         if self._m is not None and cs["m"] is not None:
-            self._m.copy_(cs["m"].to(dev))
+            self._m.copy_(pick(cs["m"]).to(dev))
         if self._v is not None and cs["v"] is not None:
-            self._v.copy_(cs["v"].to(dev))
+            self._v.copy_(pick(cs["v"]).to(dev))
         if self._shadow is not None:
             self._shadow.copy_(self._master)
-        if any(s is not None for s in cs["allreduce"]):
+        if any(s is not None for s in cs["allreduce"]) and not self._local:
             self._ensure_allreducers()
-            for b, s in zip(self._buckets, cs["allreduce"]):
-                if s is None or b.ar is None:
+            saved_buckets = cs.get("buckets")
+            same_buckets = (same_layout and cs["world_size"] == self._env.ranks and
+                            (saved_buckets is None or [tuple(x) for x in saved_buckets] ==
+                             [(b.start, b.end, type(b.ar).__name__) for b in self._buckets]))
+            residual = None if cs.get("residual") is None else pick(cs["residual"])
+            for i, b in enumerate(self._buckets):
+                if b.ar is None or not b.ar.compressed:
                     continue
                 if foreign:
                     b.ar.reset()
-                elif cs["world_size"] == self._env.ranks:
-                    b.ar.load_state_dict(s)
+                elif same_buckets and i < len(cs["allreduce"]) and cs["allreduce"][i] is not None:
+                    b.ar.load_state_dict(cs["allreduce"][i])
                 else:
-                    # a restart with another world size keeps what this rank had
-                    for dst, src in zip(b.ar._residuals(), s["residuals"]):
-                        if dst.numel() == src.numel():
-                            dst.copy_(src.to(dev))
+                    # another bucket layout, schedule or world size: every parameter keeps what this
+                    # rank had not sent yet (the residual follows the parameter, not the bucket);
+                    # secondary residuals (a ring owner's) start at zero
+                    b.ar.reset()
+                    r = getattr(b.ar, "rests", None)
+                    if r is not None and residual is not None:
+                        r.copy_(residual[b.start:b.start + r.numel()].to(dev))
+                    elif r is not None and i < len(cs["allreduce"]) and cs["allreduce"][i] is not None:
+                        src = cs["allreduce"][i]["residuals"][0]          # version 1 file, same buckets
+                        if src.numel() == r.numel():
+                            r.copy_(src.to(dev))
+        # every reducer, restored or reset, selects with the checkpoint's ratio from here on
+        self.set_compression_ratio(cs["ratio"])

@@ -66,4 +66,9 @@ class DataParallel:
                 "config": self.config.to_dict()}
 
     def load_state_dict(self, state: dict) -> None:
-        self.optimizer.load_state_dict(state["optimizer"])          # master weights: the model's tensors are views
+        """Restore model and optimizer.  The model's own state goes in first: its buffers
+        (BatchNorm running statistics and the like) live only there; its parameters are views of
+        the optimizer's flat weights, which the optimizer state then sets authoritatively."""
+        if state.get("model") is not None:
+            self.model.load_state_dict(state["model"])
+        self.optimizer.load_state_dict(state["optimizer"])

@@ -35,7 +35,7 @@ def test_sgd_rule_matches_reference_after_flush(device, buckets, local_momentum)
     w0 = [p.detach().clone() for p in params]
     cs = [torch.randn_like(p) * 3 for p in params]
     lr, mu, wd, clip, steps = 0.1, 0.9, 0.0, 5.0, 7
-    opt = ComprexOptimizer(params, env, lr=lr, momentum=mu, compression_ratio=0.05, size_factor=3.0,
+    opt = ComprexOptimizer(params, env, single_rank_bypass=False, lr=lr, momentum=mu, compression_ratio=0.05, size_factor=3.0,
                            pre_clipnorm=clip, weight_decay=wd, local_momentum=local_momentum, bucket_cap_mb=buckets)
     if buckets:
         assert len(opt._buckets) > 1
@@ -68,7 +68,7 @@ def test_fold_clips_per_tensor_and_keeps_memory_format(device, dtype):
     params = [torch.nn.Parameter(t.to(dtype)) for t in shapes]
     w0 = [p.detach().float().clone() for p in params]
     lr, mu, clip = 0.05, 0.9, 2.0
-    opt = ComprexOptimizer(params, env, lr=lr, momentum=mu, compression_ratio=1.0, size_factor=1.0, pre_clipnorm=clip)
+    opt = ComprexOptimizer(params, env, single_rank_bypass=False, lr=lr, momentum=mu, compression_ratio=1.0, size_factor=1.0, pre_clipnorm=clip)
     assert params[1].is_contiguous(memory_format=torch.channels_last) and not params[1].is_contiguous()
     for p, w in zip(params, w0):
         torch.testing.assert_close(p.detach().float(), w)
@@ -95,7 +95,7 @@ def test_training_reduces_loss_and_bf16_shadow(device):
     torch.manual_seed(0)
     env = cx.GaspiEnvironment(8 << 20, device=device)
     model = LeNet5().to(device).to(torch.bfloat16)
-    opt = ComprexOptimizer(model.parameters(), env, lr=0.05, momentum=0.9, compression_ratio=0.1, size_factor=1.0)
+    opt = ComprexOptimizer(model.parameters(), env, single_rank_bypass=False, lr=0.05, momentum=0.9, compression_ratio=0.1, size_factor=1.0)
     x = torch.rand(64, 1, 28, 28, device=device).to(torch.bfloat16)
     y = torch.randint(0, 10, (64,), device=device)
     losses = []
@@ -122,7 +122,7 @@ def test_checkpoint_resume_is_bit_exact(device, rule):
         # linear layers only: cuDNN's convolution backward is not run-to-run deterministic
         model = torch.nn.Sequential(torch.nn.Flatten(), torch.nn.Linear(784, 96), torch.nn.ReLU(),
                                     torch.nn.Linear(96, 10)).to(device)
-        opt = ComprexOptimizer(model.parameters(), env, lr=0.02, momentum=0.9, compression_ratio=0.02,
+        opt = ComprexOptimizer(model.parameters(), env, single_rank_bypass=False, lr=0.02, momentum=0.9, compression_ratio=0.02,
                                size_factor=1.0, rule=rule, weight_decay=0.01, bucket_cap_mb=0.05)
         return env, model, opt
 
@@ -157,9 +157,10 @@ def test_reference_semantics_option(device):
     params = _const_grad_model(device)
     w0 = [p.detach().clone() for p in params]
     cs = [torch.randn_like(p) for p in params]
-    opt = ComprexOptimizer(params, env, lr=0.1, momentum=0.0, compression_ratio=0.01, size_factor=3.0,
+    opt = ComprexOptimizer(params, env, single_rank_bypass=False, lr=0.1, momentum=0.0, compression_ratio=0.01, size_factor=3.0,
                            pre_clipnorm=None, consistent=False)
-    assert not opt._fused
+    opt._ensure_allreducers()
+    assert opt._buckets[0].kind == "phased"
     _set_grads(opt, params, cs)
     opt.step()
     for p, w, c in zip(params, w0, cs):          # single rank: w -= lr * g, in full, immediately
@@ -197,7 +198,7 @@ def test_other_allreduce_types_and_validation(device):
         params = _const_grad_model(device)
         w0 = [p.detach().clone() for p in params]
         cs = [torch.randn_like(p) for p in params]
-        opt = ComprexOptimizer(params, env, lr=0.1, momentum=0.0, compression_ratio=0.5, size_factor=3.0,
+        opt = ComprexOptimizer(params, env, single_rank_bypass=False, lr=0.1, momentum=0.0, compression_ratio=0.5, size_factor=3.0,
                                allreduce_type=kind, pre_clipnorm=None)
         _set_grads(opt, params, cs)
         opt.step()
@@ -233,6 +234,52 @@ def scenario_optimizer_ranks(rank, world, device, overlap):
     env.barrier()
     env.close()
     return first, float(loss)
+
+
+def scenario_optimizer_kinds(rank, world, device, kind, aggregate_blob, overlap):
+    """Every collective through the bucketed step.  Replica-consistent kinds keep all ranks'
+    weights bit-identical; for the fused Ring the decode-with-update must give the bits of the
+    two-stage path (allreduce into a work vector, then the dense update kernel)."""
+    env = cx.GaspiEnvironment(16 << 20, device=device)
+
+    def make(force_phased=False):
+        torch.manual_seed(7)
+        model = LeNet5().to(device)
+        opt = ComprexOptimizer(model.parameters(), env, lr=0.05, momentum=0.9, compression_ratio=0.05, size_factor=1.0,
+                               bucket_cap_mb=0.05 if aggregate_blob else None, overlap=overlap, allreduce_type=kind,
+                               aggregate_blob=aggregate_blob)
+        if force_phased:
+            opt._ensure_allreducers()
+            for b in opt._buckets:
+                if b.kind == "ring":
+                    b.kind = "phased"
+        return model, opt
+    arms = [make()] + ([make(True)] if kind == "comprex_ring" else [])
+    first = last = None
+    for i in range(8):
+        g = torch.Generator().manual_seed(1000 * rank + i)
+        x = torch.rand(32, 1, 28, 28, generator=g).to(device)
+        y = (x.mean(dim=(1, 2, 3)) * 20).long().clamp(0, 9).to(device)
+        for model, opt in arms:
+            opt.zero_grad()
+            loss = torch.nn.functional.cross_entropy(model(x), y)
+            loss.backward()
+            opt.step()
+        first = first if first is not None else float(loss)
+        last = float(loss)
+        env.flush()
+        if len(arms) == 2:
+            assert torch.equal(arms[0][1]._master, arms[1][1]._master), "fused ring differs from the two-stage path"
+        if kind in ("comprex_bigring", "comprex_ring", "auto", "ring", "alltoone"):
+            got = [None] * world
+            dist.all_gather_object(got, arms[0][1]._master.detach().cpu())
+            for other in got[1:]:
+                assert torch.equal(other, got[0]), f"replicas diverged ({kind})"
+    assert "x " in arms[0][1].describe()
+    assert len(arms[0][1]._buckets) > 1
+    env.barrier()
+    env.close()
+    return first, last
 
 
 def _toy_step(model, opt, rank, i, device):
@@ -406,6 +453,121 @@ def test_ddp_hook_cpu():
     run_ranks(2, "test_optimizer:scenario_ddp_hook")
 
 
+@pytest.mark.parametrize("kind,blob", [("comprex_ring", True), ("auto", True), ("comprex_alltoone", True),
+                                       ("ring", True), ("bigring", True), ("alltoone", True),
+                                       ("comprex_bigring", False), ("comprex_ring", False)])
+def test_every_collective_runs_bucketed_cpu(kind, blob):
+    out = run_ranks(2 if kind != "comprex_ring" else 3, "test_optimizer:scenario_optimizer_kinds",
+                    args=(kind, blob, False))
+    assert all(last < first for first, last in out)
+
+
+def test_single_rank_bypass_is_plain_momentum_sgd(device):
+    """One rank exchanges nothing: the step is clip + local momentum + dense update, every step
+    (with compression the same total would only arrive after a flush)."""
+    env = cx.GaspiEnvironment(8 << 20, device=device)
+    params = _const_grad_model(device)
+    w0 = [p.detach().clone() for p in params]
+    cs = [torch.randn_like(p) * 3 for p in params]
+    lr, mu, clip = 0.1, 0.9, 5.0
+    opt = ComprexOptimizer(params, env, lr=lr, momentum=mu, compression_ratio=0.01, pre_clipnorm=clip)
+    assert opt._local and "single rank" in opt.describe()
+    moms, refs = [torch.zeros_like(w) for w in w0], [w.clone() for w in w0]
+    for _ in range(4):
+        _set_grads(opt, params, cs)
+        opt.step()
+        for k, c in enumerate(cs):
+            g = c * clip / max(float(c.norm()), clip)
+            moms[k] = mu * moms[k] + lr * g
+            refs[k] = refs[k] - moms[k]
+        for p, ref in zip(params, refs):
+            torch.testing.assert_close(p.detach(), ref, rtol=1e-5, atol=1e-5)
+    assert opt.stats() == {} and not opt.comprex_allreducers
+    sd = opt.state_dict()
+    opt.load_state_dict(sd)
+    env.close()
+
+
+def test_nesterov_is_accepted_with_a_warning(device):
+    env = cx.GaspiEnvironment(8 << 20, device=device)
+    with pytest.warns(UserWarning, match="nesterov"):
+        ComprexOptimizer(_const_grad_model(device), env, nesterov=True)
+    env.close()
+
+
+def test_checkpoint_follows_parameters_across_bucket_layouts(device):
+    """State is keyed by parameter: a checkpoint written with one bucket size loads into an
+    optimizer with another one (weights, momentum and residuals land at each parameter's new
+    place), and a checkpoint for other parameters is refused."""
+    def make(cap, seed=0):
+        env = cx.GaspiEnvironment(8 << 20, device=device)
+        torch.manual_seed(seed)
+        model = LeNet5().to(device)
+        opt = ComprexOptimizer(model.named_parameters(), env, single_rank_bypass=False, lr=0.02, momentum=0.9,
+                               compression_ratio=0.02, size_factor=1.0, bucket_cap_mb=cap)
+        return env, model, opt
+
+    def steps(model, opt, k, start):
+        for i in range(start, start + k):
+            g = torch.Generator().manual_seed(i)
+            x = torch.rand(16, 1, 28, 28, generator=g).to(device)
+            y = torch.randint(0, 10, (16,), generator=g).to(device)
+            opt.zero_grad()
+            torch.nn.functional.cross_entropy(model(x), y).backward()
+            opt.step()
+    env_a, model_a, opt_a = make(0.05)
+    steps(model_a, opt_a, 5, 0)
+    sd = copy.deepcopy(opt_a.state_dict())
+    assert sd["comprex"]["version"] == 2 and sd["comprex"]["layout"][0][0].endswith(("weight", "bias"))
+    env_b, model_b, opt_b = make(0.02, seed=1)
+    assert len(opt_b._buckets) != len(opt_a._buckets)
+    opt_b.load_state_dict(sd)
+    by_key_a = {k: (o, p.numel()) for k, o, p in zip(opt_a._keys, opt_a._offsets, opt_a._params)}
+    res_a, res_b = opt_a._residual_flat(), opt_b._residual_flat()
+    assert float(res_a.abs().sum()) > 0
+    for k, o, p in zip(opt_b._keys, opt_b._offsets, opt_b._params):
+        oa, n = by_key_a[k]
+        assert torch.equal(opt_b._master[o:o + n].cpu(), opt_a._master[oa:oa + n].cpu())
+        assert torch.equal(opt_b._update[o:o + n].cpu(), opt_a._update[oa:oa + n].cpu())
+        assert torch.equal(res_b[o:o + n], res_a[oa:oa + n])
+    steps(model_b, opt_b, 2, 5)            # and training goes on
+    other = ComprexOptimizer(_const_grad_model(device), env_b, single_rank_bypass=False)
+    with pytest.raises(cx.ComprexError, match="other parameters"):
+        other.load_state_dict(sd)
+    env_a.close()
+    env_b.close()
+
+
+def test_data_parallel_restores_model_buffers(device):
+    """BatchNorm running statistics live in the model's state, not in the optimizer's."""
+    from comprex_b200.parallel.data_parallel import DataParallel
+
+    def make(seed):
+        torch.manual_seed(seed)
+        model = torch.nn.Sequential(torch.nn.Conv2d(1, 4, 3), torch.nn.BatchNorm2d(4), torch.nn.ReLU(),
+                                    torch.nn.Flatten(), torch.nn.Linear(4 * 26 * 26, 10)).to(device)
+        env = cx.GaspiEnvironment(8 << 20, device=device)
+        return env, model, DataParallel(model, env, lr=0.05, momentum=0.9)
+    env_a, model_a, dp_a = make(0)
+    for i in range(3):
+        g = torch.Generator().manual_seed(i)
+        x = torch.rand(8, 1, 28, 28, generator=g).to(device) * 3 + 1
+        dp_a.zero_grad()
+        model_a(x).square().mean().backward()
+        dp_a.step()
+    state = copy.deepcopy(dp_a.state_dict())
+    env_b, model_b, dp_b = make(1)
+    assert not torch.equal(model_b[1].running_mean, model_a[1].running_mean)
+    dp_b.load_state_dict(state)
+    assert torch.equal(model_b[1].running_mean, model_a[1].running_mean)
+    assert torch.equal(model_b[1].running_var, model_a[1].running_var)
+    assert int(model_b[1].num_batches_tracked) == 3
+    for pa, pb in zip(model_a.parameters(), model_b.parameters()):
+        assert torch.equal(pa, pb)
+    env_a.close()
+    env_b.close()
+
+
 def _gpus():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
@@ -432,7 +594,7 @@ def test_overlap_matches_no_overlap_single_gpu():
         env = cx.GaspiEnvironment(16 << 20, device="cuda")
         model = torch.nn.Sequential(torch.nn.Flatten(), torch.nn.Linear(784, 96), torch.nn.ReLU(),
                                     torch.nn.Linear(96, 10)).cuda()
-        opt = ComprexOptimizer(model.parameters(), env, lr=0.05, compression_ratio=0.05, size_factor=1.0,
+        opt = ComprexOptimizer(model.parameters(), env, single_rank_bypass=False, lr=0.05, compression_ratio=0.05, size_factor=1.0,
                                bucket_cap_mb=0.05, overlap=overlap)
         for i in range(6):
             g = torch.Generator().manual_seed(i)
@@ -457,7 +619,7 @@ def test_no_sync_accumulates_like_plain_accumulation():
         env = cx.GaspiEnvironment(16 << 20, device="cuda")
         model = torch.nn.Sequential(torch.nn.Flatten(), torch.nn.Linear(784, 96), torch.nn.ReLU(),
                                     torch.nn.Linear(96, 10)).cuda()
-        opt = ComprexOptimizer(model.parameters(), env, lr=0.05, compression_ratio=0.05, size_factor=1.0,
+        opt = ComprexOptimizer(model.parameters(), env, single_rank_bypass=False, lr=0.05, compression_ratio=0.05, size_factor=1.0,
                                bucket_cap_mb=0.05, overlap=overlap)
         assert opt.overlap == overlap and len(opt._buckets) > 1
         for step in range(4):

@@ -372,6 +372,38 @@ def test_apply_timeout_sets_status_and_leaves_output(world):
     assert torch.equal(out.cpu(), 2 * torch.ones(n))
 
 
+def test_pushing_reduce_timeout_leaves_counters_clean(world):
+    """A pushing reduce whose source never arrives reports TIMEOUT, publishes nothing and leaves
+    the completion counters at zero, so that the same launch works when the sender is there."""
+    e0, e1 = world.envs
+    n = 5000
+    src_slot = [P.DenseSlot.create(e, 4 * n) for e in world.envs][0]
+    dst_slot = [P.DenseSlot.create(e, 4 * n) for e in world.envs][0]
+    own = torch.ones(n, device=world.device)
+    out = torch.zeros(n, device=world.device)
+    st = e0.new_status("reducer")
+    counters = e0.scratch(int(e0.lib.cx_sizeof(4)))
+    push = P.make_targets([dst_slot.endpoint(e0, 1)])
+
+    def reduce(seq):
+        P.dense_reduce(e0, out, own, n, P.make_sources([src_slot.endpoint(e0)], [seq]), st, push=push,
+                       push_seq=seq, counters=counters)
+    reduce(1)
+    with pytest.raises(cx.ComprexError, match="TIMEOUT"):
+        e0.flush()
+    assert int(counters.view(torch.int32)[:64].abs().sum()) == 0          # done and the failure mark
+    assert e1.read_header(dst_slot.endpoint(e1).hdr).seq == 0             # nothing was published
+    sender_counters = e1.scratch(int(e1.lib.cx_sizeof(4)))
+    P.dense_send(e1, 2 * torch.ones(n, device=world.device), None, n, 1,
+                 P.make_targets([src_slot.endpoint(e1, 0)]), sender_counters)
+    e1.flush()
+    reduce(1)
+    e0.flush()
+    assert torch.equal(out.cpu(), 3 * torch.ones(n))
+    assert e1.read_header(dst_slot.endpoint(e1).hdr).seq == 1
+    assert int(counters.view(torch.int32)[:64].abs().sum()) == 0
+
+
 def test_apply_rejects_corrupt_header_and_index(world):
     """Host-written garbage in a local slot is reported, never dereferenced."""
     e0 = world.envs[0]
