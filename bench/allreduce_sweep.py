@@ -11,10 +11,14 @@ every repetition before the median is taken.
         --out results/sweep_p8.jsonl
 
 Every row carries the dense ``torch.distributed.all_reduce`` (NCCL) time of the
-same tensor, the speed-up against it, the fraction of the vector that was sent,
-and for the compressed BigRing the roofline fraction: the slower of (bytes the
-compress kernel must move through HBM) / (measured copy bandwidth) and (bytes
-that must leave over NVLink) / (770 GB/s per direction), divided by the time.
+same tensor, the speed-up against it, the nominal top-k and the fraction of the
+vector that was actually sent, and the roofline fraction: the slower of (bytes
+the kernels must move through HBM) / (measured copy bandwidth) and (bytes that
+must cross this GPU's NVLink port in one direction) / (the peer-store bandwidth
+measured at the start of the run: one kernel storing 256 MiB into one peer and
+into all peers), divided by the time.  ``--exact-control`` adds, for every
+compressed cell, a run with the exact top-k threshold (``set_exact_topk``) so
+that speed-ups can be read at the nominal ratio too.
 """
 import argparse
 import json
@@ -30,7 +34,7 @@ sys.path.insert(0, ROOT)
 
 import comprex_b200 as cx  # noqa: E402
 
-NVLINK_GBS = 770.0
+NVLINK_GBS = 770.0        # peer-copy rate of this pool; replaced by the store bandwidth measured in the run
 
 
 def hbm_gbs():
@@ -66,18 +70,55 @@ def time_op(fn, reps, warmup, flush, dev, after=None, samples=None):
     return statistics.median(out), min(out)
 
 
+def measure_store_bandwidth(env, dev, world, rank, flush, nbytes=256 << 20):
+    """One kernel storing ``nbytes`` into one peer's memory, then into every peer's: GB/s out of
+    this GPU (CUDA events, max over ranks of the time; all ranks store at the same moment, so the
+    figure is what a port sustains in both directions at once)."""
+    from comprex_b200.ops import primitives as P
+    n = nbytes // 4
+    x = torch.ones(n, device=dev)
+    mark = env.heap_mark()
+    slots = [P.DenseSlot.create(env, nbytes) for _ in range(world)]      # slot r: what rank r sends
+    counters = env.scratch(64)
+    peers = [r for r in range(world) if r != rank]
+    seq = [0]
+
+    def send(targets):
+        seq[0] += 1
+        P.dense_send(env, x, None, n, seq[0], targets, counters)
+    one = P.make_targets([slots[rank].endpoint(env, (rank + 1) % world)])
+    every = P.make_targets([slots[rank].endpoint(env, r) for r in peers])          # plain stores, P-1 copies
+    t_one, _ = time_op(lambda: send(one), 5, 2, flush, dev)
+    t_all, _ = time_op(lambda: send(every), 5, 2, flush, dev)
+    row = {"variant": "p2p_store_bandwidth", "bytes": nbytes, "ranks": world,
+           "one_peer_gbs": round(nbytes / t_one / 1e3, 1),
+           "all_peers_egress_gbs": round((world - 1) * nbytes / t_all / 1e3, 1)}
+    mc = slots[rank].mc_endpoint(env)
+    if mc is not None and world > 2:
+        multi = P.make_targets([slots[rank].endpoint(env, r) for r in peers], mc=mc)  # one multimem store
+        t_mc, _ = time_op(lambda: send(multi), 5, 2, flush, dev)
+        row["multicast_ingress_gbs"] = round((world - 1) * nbytes / t_mc / 1e3, 1)
+    env.flush()
+    del slots
+    env.heap_release(mark)
+    return row
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--log2-sizes", type=int, nargs="+", default=[16, 18, 20, 22, 24, 26, 28])
     ap.add_argument("--ratios", type=float, nargs="+", default=[0.001, 0.01, 0.1])
     ap.add_argument("--variants", nargs="+", default=["comprex_bigring", "comprex_ring", "comprex_alltoone",
-                                                      "bigring", "ring", "alltoone"])
+                                                      "bigring", "ring", "ring_inplace", "alltoone", "auto"])
     ap.add_argument("--dtypes", nargs="+", default=["fp32", "bf16"])
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--max-log2-onetoall", type=int, default=26,
                     help="largest size for the schedules that hold P full-size slots (dense BigRing, AllToOne)")
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--no-p2p", action="store_true", help="skip the peer-store bandwidth measurement")
+    ap.add_argument("--exact-control", action="store_true",
+                    help="also run every compressed cell with the exact top-k threshold")
     ap.add_argument("--out", default=None)
     ap.add_argument("--csv", default=None,
                     help="also write the reference benchmark's table (examples/allreduce_speed.cpp:182-184): "
@@ -98,6 +139,28 @@ def main():
         if rank == 0:
             print(json.dumps({k: v for k, v in row.items() if k != "csv"}), flush=True)
 
+    link_gbs, link_how = NVLINK_GBS, "peer-copy figure"
+    if world > 1 and not args.no_p2p:
+        bw = measure_store_bandwidth(env, dev, world, rank, flush)
+        emit(bw)
+        link_gbs, link_how = max(bw["one_peer_gbs"], bw["all_peers_egress_gbs"]), "measured store bandwidth"
+
+    def roofline(variant, n, es, sent, mm):
+        """(HBM bytes, link bytes in the busier direction) of one call on one GPU."""
+        p = world
+        pairs = 8.0 * sent * n + 8.0 * n / 1024           # one rank's payload: pairs + table
+        if variant == "comprex_bigring":
+            return 12.0 * n, (p - 1) * pairs                # compress pass; everyone's payload comes in
+        if variant == "comprex_ring":
+            return 16.0 * n, 2.0 * (p - 1) / p * pairs      # two compress passes over n(P-1)/P + n/P, decode; two exchanges
+        if variant == "comprex_alltoone":
+            return 24.0 * n, (p - 1) * pairs                # the chief: decode, compress, P-1 payloads in and out
+        if variant == "alltoone":
+            return 3.0 * n * es, (p - 1) * n * es           # the chief's port carries every worker's vector
+        if mm:
+            return 2.0 * n * es, (p + 1.0) / p * n * es     # in-switch reduction: n out, n/P + n in (staging copies not counted)
+        return 3.0 * n * es, 2.0 * (p - 1) / p * n * es     # reduce-scatter + allgather
+
     for lg in args.log2_sizes:
         n = 1 << lg
         for dname in args.dtypes:
@@ -110,29 +173,38 @@ def main():
                   "us_min": round(nccl_min, 2),
                   "busbw_gbs": round(2 * (world - 1) / world * n * x.element_size() / nccl_med / 1e3, 1)})
             for variant in args.variants:
-                compressed = variant.startswith("comprex")
-                if compressed and dname != "fp32":
-                    continue   # compressed payloads and residuals are fp32; bf16 enters through the optimizer
-                if variant in ("bigring", "alltoone", "comprex_alltoone") and lg > args.max_log2_onetoall:
+                compressed = variant.startswith("comprex") or variant == "auto"
+                # the schedules that keep P full-size slots (or a full-size residual per rank at the
+                # chief) stop where those no longer fit next to the vector
+                if variant in ("alltoone", "comprex_alltoone") and lg > args.max_log2_onetoall:
+                    emit({"variant": variant, "n": n, "dtype": dname, "ranks": world, "skipped": "slots do not fit"})
                     continue
-                for ratio in (args.ratios if compressed else [1.0]):
+                for ratio, exact in [(r, e) for r in (args.ratios if compressed else [1.0])
+                                     for e in ((False, True) if compressed and args.exact_control else (False,))]:
                     mark = env.heap_mark()
                     cls = {"comprex_bigring": cx.Comprex_BigRingAllreduce, "comprex_ring": cx.Comprex_RingAllreduce,
                            "comprex_alltoone": cx.Comprex_AllToOneAllreduce, "bigring": cx.BigRingAllreduce,
-                           "ring": cx.RingAllreduce, "alltoone": cx.AllToOneAllreduce}[variant]
+                           "ring": cx.RingAllreduce, "ring_inplace": cx.RingAllreduce,
+                           "alltoone": cx.AllToOneAllreduce, "auto": cx.AutoAllreduce}[variant]
                     ar = cls(env)
                     sf = max(4.0 * ratio, 2e-3)     # slots hold twice the expected survivors
                     if variant == "comprex_bigring":
                         ar.setup_connections(n, 1, ratio, sf, consistent=True)
                     elif variant == "comprex_ring":
-                        ar.setup_connections(n, 1, ratio, sf)
+                        ar.setup_connections(n, 1, ratio, sf, chunk_align=8)
                     elif variant == "comprex_alltoone":
                         ar.setup_connections(n, 1, 0, ratio, sf)
                     elif variant == "alltoone":
                         ar.setup_connections(n, 1, 0, dtype=dt)
+                    elif variant == "auto":
+                        ar.setup_connections(n, 1, ratio, sf, dtype=dt)
                     else:
                         ar.setup_connections(n, 1, dtype=dt)
-                    buf = x.clone()
+                    if exact:
+                        (ar.impl if variant == "auto" else ar).set_exact_topk() if getattr(ar, "compressed", False) else None
+                    # "ring_inplace": the vector lives in the symmetric heap (env.empty), like the
+                    # reference's buffers live in its registered segment: no staging copies
+                    buf = env.empty(n, dt) if variant == "ring_inplace" else x.clone()
 
                     def run():
                         buf.copy_(x)
@@ -150,17 +222,24 @@ def main():
                     row = {"variant": variant, "n": n, "dtype": dname, "ranks": world, "ratio": ratio,
                            "us_median": round(med, 2), "us_min": round(best, 2), "nccl_us": round(nccl_med, 2),
                            "speedup_vs_nccl": round(nccl_med / med, 2)}
-                    if compressed:
-                        st = ar.stats()
-                        row["sent_fraction"] = round(st["nnz"] / max(st["n"], 1), 5)
+                    kind, sent = ("ring" if variant == "ring_inplace" else variant), 1.0
+                    if variant == "auto":
+                        kind = row["chosen"] = ar.choice
+                    st = ar.stats() if getattr(ar, "compressed", False) else None
+                    if st:
+                        sent = st["nnz"] / max(st["n"], 1)
+                        row["nominal_topk"] = ratio
+                        row["exact_topk"] = exact
+                        row["sent_fraction"] = round(sent, 5)
                         row["overflow"] = bool(st["status"] & 4)
                         row["result_sparsity"] = res_sparsity
-                        if variant == "comprex_bigring":
-                            hbm_b = 12.0 * n
-                            link_b = (world - 1) * (8.0 * st["nnz"] + 8.0 * n / 1024)
-                            roof_us = max(hbm_b / (peak * 1e3), link_b / (NVLINK_GBS * 1e3))
-                            row["roofline_us"] = round(roof_us, 2)
-                            row["frac_of_roofline_" + how] = round(roof_us / med, 3)
+                    mm = bool(getattr(getattr(ar, "impl", ar), "_mm", None))
+                    if mm:
+                        row["through_switch"] = True
+                    hbm_b, link_b = roofline(kind, n, x.element_size(), sent, mm)
+                    roof_us = max(hbm_b / (peak * 1e3), link_b / (link_gbs * 1e3))
+                    row["roofline_us"] = round(roof_us, 2)
+                    row["frac_of_roofline_" + how] = round(roof_us / med, 3)
                     if args.csv:
                         ts = [max(t - cmed, 0.01) for t in times]
                         row["csv"] = (variant, n * x.element_size() / 1e6, ratio, statistics.mean(ts),

@@ -75,6 +75,7 @@ def main():
     ap.add_argument("--sources", type=int, default=7)
     ap.add_argument("--iters", type=int, default=7)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--kernels", nargs="+", default=None, help="only these rows (threshold, compress, apply_add, ...)")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
     peak, how = peak_gbs()
@@ -139,6 +140,8 @@ def main():
                 for name, (fn, nbytes) in kernels.items():
                     if name != "compress" and dname != args.dtypes[0]:
                         continue   # only the compress kernel reads the gradient dtype
+                    if args.kernels and name not in args.kernels:
+                        continue
                     for _ in range(args.warmup):
                         fn()
                     reps = 10 if n * 12 < (100 << 20) else 1

@@ -20,6 +20,7 @@ F32, BF16, F16 = 0, 1, 2
 KIND_PAIRS, KIND_DENSE, KIND_RLE = 1, 2, 3
 ST_TIMEOUT, ST_BAD_HEADER, ST_OVERFLOW, ST_BAD_INDEX = 1, 2, 4, 8
 OP_ADD, OP_SET, OP_SGD, OP_MOMENTUM, OP_ADAMW = 0, 1, 2, 3, 4
+TG_MULTICAST = 1      # Targets.pad flag: ep[count] is the multicast alias of the targets' slots
 
 _DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 
@@ -61,7 +62,7 @@ class ApplyArgs(C.Structure):
                 ("bc1", C.c_float), ("bc2", C.c_float), ("momentum", C.c_float), ("pad2", C.c_float)]
 
 
-OPK_THRESHOLD, OPK_COMPRESS, OPK_APPLY, OPK_DENSE_SEND, OPK_DENSE_REDUCE, OPK_UPDATE = 1, 2, 3, 4, 5, 6
+OPK_THRESHOLD, OPK_COMPRESS, OPK_APPLY, OPK_DENSE_SEND, OPK_DENSE_REDUCE, OPK_UPDATE, OPK_MM_ALLREDUCE = 1, 2, 3, 4, 5, 6, 7
 
 
 class Op(C.Structure):
@@ -101,6 +102,10 @@ def _declare(lib) -> None:
         "cx_compress": (i32, [i32, i32, vp, vp, i64, vp, u32, u64, P(Targets), vp, i64, vp, u32, vp]),
         "cx_apply": (i32, [i32, P(Sources), i64, P(ApplyArgs), vp, u64, vp]),
         "cx_update_dense": (i32, [i32, vp, i64, P(ApplyArgs), vp]),
+        "cx_mm_flag_bytes": (i64, []),
+        "cx_mm_counter_bytes": (i64, []),
+        "cx_mm_allreduce": (i32, [i32, vp, vp, vp, vp, i64, i64, i32, i32, C.c_float, i32, i64, u64,
+                                  P(C.c_void_p), vp, vp, u64, vp]),
         "cx_forward": (i32, [i32, P(Endpoint), u64, P(Targets), u64, u32, vp, vp, u64, vp]),
         "cx_dense_send": (i32, [i32, i32, vp, vp, i64, u64, P(Targets), P(i64), P(i64), vp, u32, vp]),
         "cx_dense_reduce": (i32, [i32, i32, vp, vp, i64, P(Sources), f32, P(Targets), u64, P(i64), P(i64),

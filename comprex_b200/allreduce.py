@@ -72,6 +72,18 @@ def _cap_for(n: int, size_factor: float) -> int:
     return max(int(n * 4 * size_factor - 8) // 8, 1)
 
 
+def _use_switch(env, nbytes: int) -> bool:
+    """Dense vectors go through the NVSwitch's in-switch reduction when the heap is bound to a
+    multicast object, from ``COMPREX_MM_MIN_RANKS`` ranks (default 4: with two ranks the switch
+    saves no traffic over plain peer stores) and ``COMPREX_MM_MIN_BYTES`` bytes (default 256 KiB:
+    below that the two-launch peer-store schedule has the lower latency)."""
+    if env.ranks < int(os.environ.get("COMPREX_MM_MIN_RANKS", 4)):
+        return False
+    if nbytes < int(os.environ.get("COMPREX_MM_MIN_BYTES", 256 << 10)):
+        return False
+    return env.nvls
+
+
 class _OpSeq:
     """A launch sequence built once (an array of CxOp) and run with one native call per step.
 
@@ -135,6 +147,12 @@ class _AllreduceBase:
 
     def getSize(self):
         return self.size
+
+    @property
+    def first_phase_waits(self) -> bool:
+        """True when already the first phase of ``_plan_apply`` waits for the peers (the
+        single-kernel allreduce through the switch); otherwise the first phase only sends."""
+        return getattr(self, "_mm", None) is not None
 
     def _setup_common(self, size: int, dtype: torch.dtype) -> None:
         if self.size is not None:
@@ -258,7 +276,8 @@ class AllToOneAllreduce(_AllreduceBase):
         def reduce():
             if me == chief:
                 src = P.make_sources([self._rs[w][par].endpoint(env) for w in workers], [seq] * len(workers))
-                push = P.make_targets([self._bc[par].endpoint(env, w) for w in workers])
+                push = P.make_targets([self._bc[par].endpoint(env, w) for w in workers],
+                                      mc=self._bc[par].mc_endpoint(env))
                 P.dense_reduce(env, t, t, self.size, src, self._status, scale=self.result_scale, push=push,
                                push_seq=seq, counters=self._counters)
 
@@ -270,12 +289,21 @@ class AllToOneAllreduce(_AllreduceBase):
 
 
 class RingAllreduce(_AllreduceBase):
-    """Reduce-scatter + allgather over P chunks (src/allreduce.tpp:273-351), two-shot."""
+    """Reduce-scatter + allgather over P chunks (src/allreduce.tpp:273-351), two-shot.
+
+    Where the heap is bound to an NVSwitch multicast object (``env.nvls``) both shots happen in
+    the switch: every rank pulls the sum of its chunk with ``multimem.ld_reduce`` and broadcasts
+    it with ``multimem.st``, one kernel per call; ``COMPREX_NVLS=0`` keeps the peer-store kernels."""
 
     def setup_connections(self, size, tag=0, dtype=torch.float32):
         self._setup_common(size, dtype)
         env = self._env
         self.segment_sizes, self.segment_starts = _chunks(size, env.ranks)
+        self._mm = None
+        if _use_switch(env, size * torch.empty(0, dtype=dtype).element_size()):
+            # the switch reduces and broadcasts: one kernel per rank (csrc/nvls.cu)
+            self._mm = P.MultimemAllreduce(env, size, dtype)
+            return
         nb = max(self.segment_sizes) * torch.empty(0, dtype=dtype).element_size()
         self._rs = [[P.DenseSlot.create(env, nb) for _ in range(2)] for _ in range(env.ranks)]
         self._ag = [[P.DenseSlot.create(env, nb) for _ in range(2)] for _ in range(env.ranks)]
@@ -287,6 +315,8 @@ class RingAllreduce(_AllreduceBase):
         env, me, nr = self._env, self._env.rank, self._env.ranks
         self._step += 1
         seq, par = self._step, self._step & 1
+        if self._mm is not None:
+            return [lambda: self._mm.run(t, seq, self.result_scale, self._status)]
         mine = (me + 1) % nr
         others = [c for c in range(nr) if c != mine]
         peers = [r for r in range(nr) if r != me]
@@ -332,6 +362,11 @@ class BigRingAllreduce(_AllreduceBase):
         if two_shot_bytes is None:
             two_shot_bytes = int(os.environ.get("COMPREX_TWO_SHOT_BYTES", 1 << 20))
         self._two_shot = None
+        self._mm = None
+        if _use_switch(env, nb):
+            # through the switch: one-shot for small vectors, reduce-scatter + broadcast above
+            self._mm = P.MultimemAllreduce(env, size, dtype)
+            return
         if env.ranks > 2 and nb > two_shot_bytes:
             self._two_shot = RingAllreduce(self.gaspi_env)
             self._two_shot.setup_connections(size, tag, dtype)
@@ -339,6 +374,10 @@ class BigRingAllreduce(_AllreduceBase):
         self._slots = [[P.DenseSlot.create(env, nb) for _ in range(2)] for _ in range(env.ranks)]
 
     def _plan_apply(self, t):
+        if self._mm is not None:
+            self._step += 1
+            seq = self._step
+            return [lambda: self._mm.run(t, seq, self.result_scale, self._status)]
         if self._two_shot is not None:
             self._two_shot._step = self._step          # one step counter: sequence numbers and parity agree
             self._two_shot.result_scale = self.result_scale
@@ -460,7 +499,12 @@ class Comprex_BigRingAllreduce(_ComprexAllreduceBase):
     def _send_targets(self, par):
         env, me = self._env, self._env.rank
         dests = [r for r in range(env.ranks) if r != me or self.consistent]
-        return self._cached_targets(("tg", par), lambda: [self._slots[me][par].endpoint(env, r) for r in dests])
+        cache = self.__dict__.setdefault("_desc_cache", {})
+        tg = cache.get(("tg", par))
+        if tg is None:      # one multicast store reaches all peers' slots where the switch offers it
+            tg = cache[("tg", par)] = P.make_targets([self._slots[me][par].endpoint(env, r) for r in dests],
+                                                     mc=self._slots[me][par].mc_endpoint(env))
+        return tg
 
     def _plan_common(self, t, g, fixed_thr, rounds=1, recv_args=None):
         env = self._env
@@ -711,7 +755,8 @@ class Comprex_RingAllreduce(_ComprexAllreduceBase):
                     self._comp.threshold_topk(mv, r, n, self.compression_ratio)
                 dests = everyone if self.consistent else peers
                 self._comp.compress(mv, r, n, self.cap, seq,
-                                    P.make_targets([self._ag[me][par].endpoint(env, j) for j in dests]))
+                                    P.make_targets([self._ag[me][par].endpoint(env, j) for j in dests],
+                                                   mc=self._ag[me][par].mc_endpoint(env)))
 
             def gather(seq=seq, par=par, last=(rnd == rounds - 1)):
                 if flush and not last:
@@ -914,7 +959,8 @@ class Comprex_AllToOneAllreduce(_ComprexAllreduceBase):
                 self._comp.threshold_topk(t, self.rests, self.size, self.compression_ratio,
                                           self._subsamples, self._sample_factor)
                 self._comp.compress(t, self.rests, self.size, self.cap, seq,
-                                    P.make_targets([self._bc[par].endpoint(env, w) for w in workers]))
+                                    P.make_targets([self._bc[par].endpoint(env, w) for w in workers],
+                                                   mc=self._bc[par].mc_endpoint(env)))
 
             def recv(seq=seq, par=par):
                 if me == chief or flush:
@@ -992,8 +1038,6 @@ class AutoAllreduce(_AllreduceBase):
         env = self._env
         es = torch.empty(0, dtype=dtype).element_size()
         self.choice = select_schedule(int(size), float(compression_ratio), env.ranks, es)
-        if dtype != torch.float32:
-            self.choice = "bigring"           # compressed schedules exchange fp32 vectors
         self.size, self.dtype = int(size), dtype
         if self.choice == "bigring":
             self.impl = BigRingAllreduce(self.gaspi_env)

@@ -36,6 +36,7 @@ struct ApplyParams {
   int64_t n;
   uint32_t nsub;
   uint32_t vec;  // every dense pointer is 16-byte aligned
+  uint32_t batch;  // sub-tiles with few pairs take the one-round-trip path
   uint32_t* status;
   uint64_t timeout_ns;
   const uint64_t* seq_cell;  // non-NULL inside a captured graph: the waits use its value
@@ -75,14 +76,66 @@ __device__ __forceinline__ bool wait_sources(const ApplyParams& p, uint32_t* s_n
   return bad == 0;
 }
 
+// ---- one memory round trip for all sources of a sub-tile ------------------------------------
+// Walking the sources one after the other costs one dependent load (pairs) or two (pairs, then
+// the addressed elements) per source.  When the sub-tile's pairs of ALL sources fit four per
+// lane, they are fetched in one go instead: the segments [a_j, b_j) are laid end to end, lane l
+// takes the pairs l, l + 32, ... of that sequence, and only the cheap part (the additions, in
+// shared memory) runs source after source, which keeps the order of every sum.
+constexpr int kBatch = 4;                       // pairs per lane
+constexpr uint32_t kBatchMax = 32 * kBatch;      // pairs per sub-tile the batched path takes
+
+struct Gathered {
+  CxPair pr[kBatch];
+  int src[kBatch];   // source of the pair, -1: none
+};
+
+// a / b: lane j holds source j's segment.  total: sum of all segment lengths (<= kBatchMax).
+__device__ __forceinline__ void gather_pairs(const ApplyParams& p, int lane, uint32_t a, uint32_t b,
+                                             uint32_t pre, Gathered& g) {
+  uint32_t off[kBatch];
+#pragma unroll
+  for (int k = 0; k < kBatch; ++k) { g.src[k] = -1; off[k] = 0; }
+  for (int j = 0; j < p.src.count; ++j) {
+    const uint32_t pj = __shfl_sync(0xffffffffu, pre, j);
+    const uint32_t aj = __shfl_sync(0xffffffffu, a, j);
+    const uint32_t cj = __shfl_sync(0xffffffffu, b, j) - aj;
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+      const uint32_t f = (uint32_t)(k * 32 + lane);
+      if (f - pj < cj) { g.src[k] = j; off[k] = aj + (f - pj); }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kBatch; ++k) {
+    g.pr[k].idx = 0;
+    g.pr[k].val = 0;
+    if (g.src[k] >= 0) g.pr[k] = ld_pair(p.src.ep[g.src[k]].pairs + off[k]);
+  }
+}
+
+__device__ __forceinline__ void segment_prefix(int lane, uint32_t a, uint32_t b, uint32_t& pre, uint32_t& total) {
+  const uint32_t cnt = b - a;
+  uint32_t incl = cnt;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += t;
+  }
+  pre = incl - cnt;
+  total = __shfl_sync(0xffffffffu, incl, 31);
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(kThreads) apply_sparse_kernel(const ApplyParams p) {
   __shared__ uint32_t s_nnz[CX_MAX_PEERS];
+  __shared__ float s_acc[kWarps][CX_SUBTILE];
   if (!wait_sources(p, s_nnz)) return;
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const uint32_t nwarps = gridDim.x * kWarps;
   const float scale = p.a.op == CX_OP_SGD ? -p.a.scale : p.a.scale;
+  float* acc = s_acc[warp];
   uint32_t bad = 0;
   for (uint32_t sub = blockIdx.x * kWarps + warp; sub < p.nsub; sub += nwarps) {
     const uint32_t lo = sub * CX_SUBTILE;
@@ -92,6 +145,60 @@ __global__ void __launch_bounds__(kThreads) apply_sparse_kernel(const ApplyParam
       a = entry.x;
       b = min(entry.x + min(entry.y, (uint32_t)CX_SUBTILE), p.src.cap[lane]);  // never beyond the slot
       a = min(a, b);
+    }
+    uint32_t pre, total;
+    segment_prefix(lane, a, b, pre, total);
+    if (total == 0) continue;
+    if (p.batch && total <= kBatchMax) {
+      // all pairs in one round trip, the addressed elements in a second one; the sums are formed
+      // in shared memory, source after source and rounded like the element-by-element path
+      Gathered g;
+      gather_pairs(p, lane, a, b, pre, g);
+      uint32_t d[kBatch];
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) {
+        d[k] = (uint32_t)g.pr[k].idx - lo;
+        if (g.src[k] >= 0 && !(d[k] < CX_SUBTILE && (int64_t)g.pr[k].idx < p.n)) { bad = CX_ST_BAD_INDEX; g.src[k] = -1; }
+      }
+      if (p.a.op == CX_OP_SGD) {
+        const float* w = reinterpret_cast<const float*>(p.a.out);
+        float cur[kBatch];
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) cur[k] = g.src[k] >= 0 ? w[g.pr[k].idx] : 0.f;
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) if (g.src[k] >= 0) acc[d[k]] = cur[k];
+      } else {
+        const TO* o = reinterpret_cast<const TO*>(p.a.out);
+        float cur[kBatch];
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) cur[k] = g.src[k] >= 0 ? cx::Elem<TO>::to_f(o[g.pr[k].idx]) : 0.f;
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) if (g.src[k] >= 0) acc[d[k]] = cur[k];
+      }
+      __syncwarp();
+      for (int j = 0; j < p.src.count; ++j) {
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+          if (g.src[k] == j) {
+            const float nv = acc[d[k]] + scale * __uint_as_float(g.pr[k].val);
+            acc[d[k]] = p.a.op == CX_OP_SGD ? nv : cx::Elem<TO>::to_f(cx::Elem<TO>::from_f(nv));
+          }
+        }
+        __syncwarp();
+      }
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) {
+        if (g.src[k] < 0) continue;
+        const float nv = acc[d[k]];
+        if (p.a.op == CX_OP_SGD) {
+          reinterpret_cast<float*>(p.a.out)[g.pr[k].idx] = nv;
+          if (p.a.shadow) reinterpret_cast<TO*>(p.a.shadow)[g.pr[k].idx] = cx::Elem<TO>::from_f(nv);
+        } else {
+          reinterpret_cast<TO*>(p.a.out)[g.pr[k].idx] = cx::Elem<TO>::from_f(nv);
+        }
+      }
+      __syncwarp();
+      continue;
     }
     for (int j = 0; j < p.src.count; ++j) {
       const uint32_t aj = __shfl_sync(0xffffffffu, a, j);
@@ -214,10 +321,30 @@ __device__ __forceinline__ uint32_t accumulate_subtile(const ApplyParams& p, uin
     b = min(entry.x + min(entry.y, (uint32_t)CX_SUBTILE), p.src.cap[lane]);  // never beyond the slot
     a = min(a, b);
   }
+  uint32_t pre, total;
+  segment_prefix(lane, a, b, pre, total);
+  Gathered g;
+  const bool batched = p.batch && total <= kBatchMax;
+  if (batched && total) gather_pairs(p, lane, a, b, pre, g);      // the loads fly while the accumulator is cleared
 #pragma unroll
   for (int q = 0; q < CX_SUBTILE / 128; ++q)
     *reinterpret_cast<float4*>(acc + q * 128 + lane * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
   __syncwarp();
+  if (total == 0) return 0;
+  if (batched) {
+    for (int j = 0; j < p.src.count; ++j) {
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k) {
+        if (g.src[k] == j) {
+          const uint32_t d = (uint32_t)g.pr[k].idx - lo;
+          if (d < CX_SUBTILE && (int64_t)g.pr[k].idx < p.n) acc[d] += __uint_as_float(g.pr[k].val);
+          else bad = CX_ST_BAD_INDEX;
+        }
+      }
+      __syncwarp();
+    }
+    return bad;
+  }
   for (int j = 0; j < p.src.count; ++j) {
     const uint32_t aj = __shfl_sync(0xffffffffu, a, j);
     const uint32_t bj = __shfl_sync(0xffffffffu, b, j);
@@ -652,6 +779,10 @@ int cx_apply_cuda(const CxSources* src, int64_t n, const CxApplyArgs* a, uint32_
   p.src = *src; p.a = *a; p.n = n;
   p.nsub = (uint32_t)((n + CX_SUBTILE - 1) / CX_SUBTILE);
   p.status = status; p.timeout_ns = timeout_ns; p.seq_cell = cx_seq_cell();
+  {
+    const char* e = getenv("COMPREX_APPLY_BATCH");       // 0: always walk the sources one by one
+    p.batch = (e && e[0] == '0') ? 0u : 1u;
+  }
   const bool update = a->op != CX_OP_ADD && a->op != CX_OP_SET;
   if (update && a->op != CX_OP_SGD && !a->m) return cx_set_error("cx_apply: momentum buffer missing", 0);
   if (a->op == CX_OP_ADAMW && !a->v) return cx_set_error("cx_apply: second-moment buffer missing", 0);

@@ -8,14 +8,16 @@
 //     r += g ; if |r| > thr { emit (i, r) ; r = 0 }
 //
 // Work is warp-granular and free of block-wide barriers: a warp owns one
-// 1024-element sub-tile at a time, loads it with 16-byte accesses (32
-// elements per lane, all loads in flight together), ranks the survivors with
-// one warp scan, reserves room for them in the pair list with ONE atomicAdd
-// on a counter in this GPU's memory, and stores them through a small shared
-// staging buffer as coalesced 8-byte (index, value) pairs straight into the
-// receive slots of up to CX_MAX_PEERS targets (peer GPUs' memory mapped over
-// NVLink, or local slots).  No warp ever waits for another one, so the kernel
-// has no spin loop at all.
+// 1024-element sub-tile at a time, streams it twice with 16-byte accesses
+// (classify; then, with the second read served from cache, write the residual
+// and pick the survivors up; only a 32-bit survivor mask stays in registers),
+// ranks the survivors with one warp scan, reserves room for them in the pair
+// list with ONE atomicAdd on a counter in this GPU's memory, and stores them
+// through a small shared staging buffer as coalesced 8-byte (index, value)
+// pairs straight into the receive
+// slots of up to CX_MAX_PEERS targets (peer GPUs' memory mapped over NVLink,
+// or local slots), or once through the switch's multicast mapping.  No warp
+// ever waits for another one, so the kernel has no spin loop at all.
 //
 // The pairs of one sub-tile are contiguous in the list; sub-tiles land in the
 // list in the order of their reservations.  Next to the pairs every target
@@ -29,14 +31,26 @@
 // residual, which error feedback makes safe; the count is reported.  The CTA
 // that finishes last writes the header and publishes the notification
 // (st.release.sys) after every CTA's stores were fenced at system scope.
+#include <stdlib.h>
+#include <string.h>
+
 #include "cx_device.cuh"
 
 namespace {
 
 #ifndef CX_COMPRESS_MIN_BLOCKS
-#define CX_COMPRESS_MIN_BLOCKS 3  // CTAs per SM the register budget is tuned for (measured best of 2..5)
+#define CX_COMPRESS_MIN_BLOCKS 5  // CTAs per SM the register budget is set for (48 registers, no spills)
 #endif
 
+// chunks (two 16-byte loads per lane each) in flight in the classifying and in the writing pass
+#ifndef CX_COMPRESS_UNROLL1
+#define CX_COMPRESS_UNROLL1 4
+#endif
+#ifndef CX_COMPRESS_UNROLL2
+#define CX_COMPRESS_UNROLL2 2
+#endif
+
+constexpr int kUnroll1 = CX_COMPRESS_UNROLL1, kUnroll2 = CX_COMPRESS_UNROLL2;
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kChunks = CX_SUBTILE / 128;  // 128 elements = 32 lanes x 4
@@ -60,62 +74,37 @@ struct CompressParams {
   CxTargets tg;
 };
 
-// One sub-tile, one warp.  Lane L holds elements {c*128 + 4L + e}; FULL means
-// "aligned and entirely inside the vector" and takes the unguarded vector path.
-template <typename T, bool HAS_G, bool HAS_R, bool FULL>
-__device__ __forceinline__ void compress_subtile(const CompressParams& p, const uint32_t sub,
-                                                 const int lane, const float thr,
-                                                 const T* __restrict__ g, float* __restrict__ r,
-                                                 CxPair* stage) {
+// One aligned, complete sub-tile, one warp; lane L holds elements {c*128 + 4L + e}.  Two passes
+// with 16-byte accesses and nothing but a 32-bit survivor mask kept in between: the first pass
+// only classifies (r + g against the threshold), the second one, after the reservation, loads
+// the same lines again (they sit in L1/L2), writes the residual (zero for what is sent, the sum
+// for the rest) and hands the survivors over chunk by chunk.  Four values per lane are live at
+// any time instead of thirty-two, so the kernel runs without spills at 48 registers and five
+// CTAs per SM; DRAM traffic is the same as for a single pass.
+template <typename T, bool HAS_G, bool HAS_R, bool MC>
+__device__ __forceinline__ void compress_subtile_stream(const CompressParams& p, const uint32_t sub,
+                                                        const int lane, const float thr,
+                                                        const T* __restrict__ g, float* __restrict__ r,
+                                                        CxPair* stage) {
   const int64_t sub_base = (int64_t)sub * CX_SUBTILE;
   const T* gp = g + sub_base + lane * 4;
   float* rp = r + sub_base + lane * 4;
-  const int left = (int)min((int64_t)CX_SUBTILE, p.n - sub_base) - lane * 4;  // my elements e < left - c*128
-
-  // ---- load, add -------------------------------------------------------------
-  float v[kChunks][4];
-#pragma unroll
-  for (int c = 0; c < kChunks; ++c) {
-#pragma unroll
-    for (int e = 0; e < 4; ++e) v[c][e] = 0.f;
-    if (HAS_R) {
-      if (FULL) {
-        cx::load4(rp + c * 128, v[c]);
-      } else {
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-          if (c * 128 + e < left) v[c][e] = rp[c * 128 + e];
-      }
-    }
-  }
-  if (HAS_G) {
-#pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
-      float b[4] = {0.f, 0.f, 0.f, 0.f};
-      if (FULL) {
-        cx::load4(gp + c * 128, b);
-      } else {
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-          if (c * 128 + e < left) b[e] = cx::Elem<T>::to_f(gp[c * 128 + e]);
-      }
-#pragma unroll
-      for (int e = 0; e < 4; ++e) v[c][e] = v[c][e] + b[e];
-    }
-  }
-
-  // ---- classify: bit c*4+e of mask, strict '>' like the reference --------------
   uint32_t mask = 0;
-#pragma unroll
+#pragma unroll kUnroll1
   for (int c = 0; c < kChunks; ++c) {
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (HAS_R) cx::load4(rp + c * 128, v);
+    if (HAS_G) {
+      float b[4];
+      cx::load4(gp + c * 128, b);
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const bool sel = fabsf(v[c][e]) > thr && (FULL || c * 128 + e < left);
-      mask |= (sel ? 1u : 0u) << (4 * c + e);
+      for (int e = 0; e < 4; ++e) v[e] = v[e] + b[e];
     }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) mask |= (fabsf(v[e]) > thr ? 1u : 0u) << (4 * c + e);
   }
 
-  // ---- rank: lanes in order, each lane's survivors consecutive --------------------
+  // ---- rank: lanes in order, each lane's survivors consecutive; reserve; table entry ------------
   const uint32_t mine = __popc(mask);
   uint32_t incl = mine;
 #pragma unroll
@@ -124,9 +113,7 @@ __device__ __forceinline__ void compress_subtile(const CompressParams& p, const 
     if (lane >= d) incl += t;
   }
   const uint32_t count = __shfl_sync(0xffffffffu, incl, 31);
-  const uint32_t first = incl - mine;  // position of my first survivor inside the sub-tile
-
-  // ---- reserve room in the pair list ----------------------------------------------
+  const uint32_t first = incl - mine;
   // The list is cut into nregions equal regions with one counter each, neighbouring
   // sub-tiles use different regions: atomics on one address are serialised by the L2.
   const uint32_t region = sub & (p.nregions - 1);
@@ -137,86 +124,141 @@ __device__ __forceinline__ void compress_subtile(const CompressParams& p, const 
   }
   const uint32_t emit = base >= p.region_size ? 0u : min(count, p.region_size - base);  // pairs that fit
   base += region * p.region_size;
-  if (lane < p.tg.count) {
+  {
     uint2 entry;
     entry.x = emit ? base : 0u;
     entry.y = emit;
-    reinterpret_cast<uint2*>(p.tg.ep[lane].table)[sub] = entry;
+    if (MC) {
+      if (lane == 0) cx::mm_st_b64(reinterpret_cast<uint2*>(p.tg.ep[p.tg.count].table) + sub, entry);
+    } else if (lane < p.tg.count) {
+      reinterpret_cast<uint2*>(p.tg.ep[lane].table)[sub] = entry;
+    }
   }
+  if (count == 0 && !(HAS_R && HAS_G)) return;   // nothing to send and nothing to write back
 
-  // ---- stage in shared memory, store coalesced to every target ------------------------
+  // ---- second pass: residual out, survivors to the staging buffer (or straight to the slots) ---
+  const bool staged = emit <= (uint32_t)kStage;    // a denser sub-tile stores its pairs lane by lane
   const int32_t idx0 = (int32_t)sub_base + lane * 4;
-  for (uint32_t w0 = 0; w0 < emit; w0 += kStage) {   // one pass unless the sub-tile is dense
-    uint32_t pos = first - w0;                        // wraps below the window: fails the test
+  uint32_t pos = first;
+#pragma unroll kUnroll2
+  for (int c = 0; c < kChunks; ++c) {
+    const uint32_t m = (mask >> (4 * c)) & 0xfu;
+    if (!(HAS_R && HAS_G) && m == 0) continue;     // nothing changes in this chunk
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (HAS_R) cx::load4(rp + c * 128, v);
+    if (HAS_G) {
+      float b[4];
+      cx::load4(gp + c * 128, b);
 #pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
+      for (int e = 0; e < 4; ++e) v[e] = v[e] + b[e];
+    }
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        if (mask & (1u << (4 * c + e))) {
-          if (pos < (uint32_t)kStage) {
-            CxPair pr;
-            pr.idx = idx0 + c * 128 + e;
-            pr.val = __float_as_uint(v[c][e]);
+    for (int e = 0; e < 4; ++e) {
+      if (m & (1u << e)) {
+        if (pos < emit) {     // survivors beyond the slot's room stay in the residual
+          CxPair pr;
+          pr.idx = idx0 + c * 128 + e;
+          pr.val = __float_as_uint(v[e]);
+          if (staged) {
             stage[pos] = pr;
+          } else if (MC) {
+            cx::mm_st_b64(p.tg.ep[p.tg.count].pairs + base + pos, make_uint2((uint32_t)pr.idx, pr.val));
+          } else {
+            for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].pairs[base + pos] = pr;
           }
-          ++pos;
+          v[e] = 0.f;
         }
+        ++pos;
       }
     }
-    __syncwarp();
-    const uint32_t lim = min((uint32_t)kStage, emit - w0);
-    for (uint32_t i = lane; i < lim; i += 32) {
+    if (HAS_R) cx::store4(rp + c * 128, v);
+  }
+  if (!staged || emit == 0) return;
+  __syncwarp();
+  if (MC) {
+    // one store per pair into the multicast mapping: the switch writes every target's slot
+    CxPair* mc = p.tg.ep[p.tg.count].pairs + base;
+    for (uint32_t i = lane; i < emit; i += 32) {
       const CxPair pr = stage[i];
-      for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].pairs[base + w0 + i] = pr;
+      cx::mm_st_b64(mc + i, make_uint2((uint32_t)pr.idx, pr.val));
     }
-    __syncwarp();
-  }
-
-  // ---- residual: zero what was emitted, keep the rest ---------------------------------------
-  if (HAS_R) {
-    if (emit < count) {  // the slot is full: survivors from position emit on stay in the residual
-      uint32_t pos = first;
-#pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          if (mask & (1u << (4 * c + e))) {
-            if (pos >= emit) mask &= ~(1u << (4 * c + e));
-            ++pos;
-          }
-        }
-      }
-    }
-#pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
-      const uint32_t m = (mask >> (4 * c)) & 0xfu;
-      if (!HAS_G && m == 0) continue;  // nothing changed in this vector
-      float out[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) out[e] = (m & (1u << e)) ? 0.f : v[c][e];
-      if (FULL) {
-        cx::store4(rp + c * 128, out);
-      } else {
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-          if (c * 128 + e < left) rp[c * 128 + e] = out[e];
-      }
+  } else {
+    for (uint32_t i = lane; i < emit; i += 32) {
+      const CxPair pr = stage[i];
+      for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].pairs[base + i] = pr;
     }
   }
+  __syncwarp();
 }
 
-// The guarded path (unaligned views, the last partial sub-tile) is kept out of line
-// so that its register needs do not weigh on the fast path.
-template <typename T, bool HAS_G, bool HAS_R>
-__device__ __noinline__ void compress_subtile_guarded(const CompressParams& p, const uint32_t sub,
-                                                      const int lane, const float thr, const T* g,
-                                                      float* r, CxPair* stage) {
-  compress_subtile<T, HAS_G, HAS_R, false>(p, sub, lane, thr, g, r, stage);
+// Sub-tiles that are partial or not aligned for 16-byte accesses (the last one of a vector, views
+// at odd offsets): one element per lane and step, survivors found with warp ballots.  Two passes
+// like above (sum into the residual and count; then read back, emit, zero), a handful of
+// registers, and no assumption about alignment or length.
+template <typename T, bool HAS_G, bool HAS_R, bool MC>
+__device__ __forceinline__ void compress_subtile_edge(const CompressParams& p, const uint32_t sub,
+                                                      const int lane, const float thr,
+                                                      const T* __restrict__ g, float* __restrict__ r) {
+  const int64_t sub_base = (int64_t)sub * CX_SUBTILE;
+  const int len = (int)min((int64_t)CX_SUBTILE, p.n - sub_base);
+  uint32_t count = 0;
+  for (int c = 0; c < len; c += 32) {
+    const int i = c + lane;
+    float v = 0.f;
+    if (i < len) {
+      if (HAS_R) v = r[sub_base + i];
+      if (HAS_G) v = v + cx::Elem<T>::to_f(g[sub_base + i]);
+      if (HAS_R && HAS_G) r[sub_base + i] = v;
+    }
+    count += __popc(__ballot_sync(0xffffffffu, i < len && fabsf(v) > thr));
+  }
+  const uint32_t region = sub & (p.nregions - 1);
+  uint32_t base = 0;
+  if (count) {
+    if (lane == 0) base = atomicAdd(&p.ctr->region[region][0], count);
+    base = __shfl_sync(0xffffffffu, base, 0);
+  }
+  const uint32_t emit = base >= p.region_size ? 0u : min(count, p.region_size - base);
+  base += region * p.region_size;
+  {
+    uint2 entry;
+    entry.x = emit ? base : 0u;
+    entry.y = emit;
+    if (MC) {
+      if (lane == 0) cx::mm_st_b64(reinterpret_cast<uint2*>(p.tg.ep[p.tg.count].table) + sub, entry);
+    } else if (lane < p.tg.count) {
+      reinterpret_cast<uint2*>(p.tg.ep[lane].table)[sub] = entry;
+    }
+  }
+  if (emit == 0) return;
+  uint32_t seen = 0;                       // survivors in the chunks before this one
+  for (int c = 0; c < len && seen < emit; c += 32) {
+    const int i = c + lane;
+    float v = 0.f;
+    if (i < len) v = HAS_R ? r[sub_base + i] : cx::Elem<T>::to_f(g[sub_base + i]);
+    const bool sel = i < len && fabsf(v) > thr;
+    const uint32_t bal = __ballot_sync(0xffffffffu, sel);
+    const uint32_t pos = seen + __popc(bal & ((1u << lane) - 1u));
+    if (sel && pos < emit) {
+      CxPair pr;
+      pr.idx = (int32_t)(sub_base + i);
+      pr.val = __float_as_uint(v);
+      if (MC) {
+        cx::mm_st_b64(p.tg.ep[p.tg.count].pairs + base + pos, make_uint2((uint32_t)pr.idx, pr.val));
+      } else {
+        for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].pairs[base + pos] = pr;
+      }
+      if (HAS_R) r[sub_base + i] = 0.f;
+    }
+    seen += __popc(bal);
+  }
 }
 
 // T: element type of g.  HAS_G / HAS_R select compress_add_update (both),
-// compress_update (r only) and compress (g only).
-template <typename T, bool HAS_G, bool HAS_R>
+// compress_update (r only) and compress (g only).  MC: table and pairs go out once through
+// the multicast endpoint tg.ep[tg.count] (multimem.st) instead of once per target; headers and
+// notifications are still written target by target.
+template <typename T, bool HAS_G, bool HAS_R, bool MC>
 __global__ void __launch_bounds__(kThreads, CX_COMPRESS_MIN_BLOCKS)
 compress_kernel(const __grid_constant__ CompressParams p) {
   __shared__ CxPair s_stage[kWarps][kStage];
@@ -226,16 +268,31 @@ compress_kernel(const __grid_constant__ CompressParams p) {
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const float thr = *p.thr;
   const T* __restrict__ g = reinterpret_cast<const T*>(p.g);
   float* __restrict__ r = p.r;
+  // Launched with programmatic stream serialization, this grid may be resident while the
+  // threshold kernel in front of it still runs: pull the warp's first sub-tile towards L2, then
+  // wait for that kernel to finish before reading its result or touching the residual.
+  {
+    const uint32_t sub0 = blockIdx.x * kWarps + (tid >> 5);
+    if (sub0 < p.nsub && (tid & 31) < 2 * kChunks) {
+      const int c = (tid & 31) >> 1;
+      const int64_t e0 = (int64_t)sub0 * CX_SUBTILE + c * 128;
+      if (e0 < p.n) {
+        const void* a = (tid & 1) ? (HAS_R ? (const void*)(r + e0) : nullptr) : (HAS_G ? (const void*)(g + e0) : nullptr);
+        if (a) asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+      }
+    }
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const float thr = *p.thr;
   CxPair* stage = s_stage[warp];
   const uint32_t nwarps = gridDim.x * kWarps;
   const uint32_t nfull = p.vec ? (uint32_t)(p.n / CX_SUBTILE) : 0u;  // sub-tiles on the fast path
 
   for (uint32_t sub = blockIdx.x * kWarps + warp; sub < p.nsub; sub += nwarps) {
-    if (sub < nfull) compress_subtile<T, HAS_G, HAS_R, true>(p, sub, lane, thr, g, r, stage);
-    else compress_subtile_guarded<T, HAS_G, HAS_R>(p, sub, lane, thr, g, r, stage);
+    if (sub < nfull) compress_subtile_stream<T, HAS_G, HAS_R, MC>(p, sub, lane, thr, g, r, stage);
+    else compress_subtile_edge<T, HAS_G, HAS_R, MC>(p, sub, lane, thr, g, r);
   }
 
   // ---- completion: the CTA that arrives last publishes -------------------------------
@@ -301,11 +358,43 @@ __global__ void compress_empty_kernel(const CompressParams p) {
   }
 }
 
+// The kernel is launched so that it may overlap the tail of the kernel in front of it on the
+// stream (programmatic dependent launch); it synchronises with that kernel itself, see above.
+// Not inside a graph capture, and not with COMPREX_PDL=0.
+template <typename K>
+void launch_pdl(K kernel, const CompressParams& p, int grid, cudaStream_t s) {
+  static const bool off = [] { const char* e = getenv("COMPREX_PDL"); return e && e[0] == '0'; }();
+  if (off || p.seq_cell) {
+    kernel<<<grid, kThreads, 0, s>>>(p);
+    return;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) {
+    cudaGetLastError();                       // e.g. a driver without the feature: plain launch
+    kernel<<<grid, kThreads, 0, s>>>(p);
+  }
+}
+
+template <typename T, bool MC>
+void launch_mode_mc(const CompressParams& p, int grid, cudaStream_t s) {
+  if (p.g && p.r) launch_pdl(compress_kernel<T, true, true, MC>, p, grid, s);
+  else if (p.r) launch_pdl(compress_kernel<T, false, true, MC>, p, grid, s);
+  else launch_pdl(compress_kernel<T, true, false, MC>, p, grid, s);
+}
+
 template <typename T>
 void launch_mode(const CompressParams& p, int grid, cudaStream_t s) {
-  if (p.g && p.r) compress_kernel<T, true, true><<<grid, kThreads, 0, s>>>(p);
-  else if (p.r) compress_kernel<T, false, true><<<grid, kThreads, 0, s>>>(p);
-  else compress_kernel<T, true, false><<<grid, kThreads, 0, s>>>(p);
+  if (p.tg.pad & CX_TG_MULTICAST) launch_mode_mc<T, true>(p, grid, s);
+  else launch_mode_mc<T, false>(p, grid, s);
 }
 
 }  // namespace
@@ -322,6 +411,8 @@ int cx_compress_cuda(int gdtype, const void* g, float* r, int64_t n, const float
   if (!g && !r) return cx_set_error("cx_compress: g and r are both NULL", 0);
   if (n < 0 || n > 0x7fffffffLL) return cx_set_error("cx_compress: n out of range", 0);
   if (tg->count < 0 || tg->count > CX_MAX_PEERS) return cx_set_error("cx_compress: bad target count", 0);
+  if ((tg->pad & CX_TG_MULTICAST) && tg->count >= CX_MAX_PEERS)
+    return cx_set_error("cx_compress: no room for the multicast endpoint", 0);
   if (ws_bytes < cx_workspace_bytes(n)) return cx_set_error("cx_compress: workspace too small", 0);
   CompressParams p;
   p.g = g; p.r = r; p.n = n; p.thr = thr; p.cap = cap;

@@ -79,9 +79,15 @@ typedef struct CxEndpoint {
   CxPair* pairs;  /* for dense slots: start of the n x T data region */
 } CxEndpoint;
 
+/* CxTargets::pad flag: ep[count] is the multicast alias of the targets' slots (the same block on
+ * every rank, mapped through an NVSwitch multicast object).  Kernels then store payload data
+ * once with multimem.st instead of once per target; headers and notifications stay per target.
+ * CUDA only; needs count < CX_MAX_PEERS. */
+#define CX_TG_MULTICAST 1
+
 typedef struct CxTargets {
   int32_t count;
-  int32_t pad;
+  int32_t pad;   /* flags: CX_TG_MULTICAST */
   CxEndpoint ep[CX_MAX_PEERS];
 } CxTargets;
 
@@ -190,6 +196,22 @@ int cx_dense_reduce(int dev, int dtype, void* out, const void* own, int64_t n,
                     const int64_t* lens, void* counters, uint32_t src_rank,
                     uint32_t* status, uint64_t timeout_ns, void* stream);
 
+/* Dense allreduce through the switch (multimem.ld_reduce + multimem.st), one kernel per rank;
+ * CUDA only.  `stage` is this rank's block of the symmetric heap and `stage_mc` its multicast
+ * alias; with in == NULL the vector (n elements, a multiple of 16 bytes) lives in the block
+ * itself and nothing is copied, otherwise `in` is copied in and the sum written to `out`.
+ * one_shot: every rank pulls the whole sum itself (small vectors); the block then holds two
+ * copies `stage_stride` bytes apart, used alternately.  slab_bytes: pipeline granularity
+ * (<= 0: one slab).  flag_ptrs[r]: rank r's flag block (cx_mm_flag_bytes, zeroed once, same
+ * offset of the symmetric heap on every rank); counters: local scratch (cx_mm_counter_bytes,
+ * zeroed once).  The result is `scale` times the sum, identical bits on every rank. */
+int64_t cx_mm_flag_bytes(void);
+int64_t cx_mm_counter_bytes(void);
+int cx_mm_allreduce(int dtype, void* out, const void* in, void* stage, void* stage_mc,
+                    int64_t stage_stride, int64_t n, int rank, int ranks, float scale, int one_shot,
+                    int64_t slab_bytes, uint64_t seq, void* const* flag_ptrs, void* counters,
+                    uint32_t* status, uint64_t timeout_ns, void* stream);
+
 /* Optimizer fold (keras/comprex_optimizer.py:101-115): per-tensor L2 clip to `clip`
  * (<= 0: off) and u = mu*u + lr*coef*g, read straight from the gradient tensors
  * (seg_ptr, one pointer per tensor) into the flat fp32 vector u.  The item arrays
@@ -256,6 +278,9 @@ int cx_host_free(void* p);
 #define CX_OPK_DENSE_SEND 4
 #define CX_OPK_DENSE_REDUCE 5
 #define CX_OPK_UPDATE 6        /* cx_update_dense: g, n, apply */
+#define CX_OPK_MM_ALLREDUCE 7  /* cx_mm_allreduce: out, own (= in), g (= stage), r (= stage_mc), starts[0] = stride,
+                                  starts[1] = one_shot, starts[2] = slab bytes, lens[r] = rank r's flag block,
+                                  src_rank, cap (= ranks), workspace (= counters), scale, status */
 
 typedef struct CxOp {
   int32_t kind;

@@ -48,6 +48,20 @@ __device__ __forceinline__ bool wait_seq(const uint64_t* seq_ptr, uint64_t want,
   return false;
 }
 
+// Stores through the multicast mapping of a block: the switch writes the same offset in every
+// GPU that is bound to the multicast object (multimem.st), one store instead of one per peer.
+__device__ __forceinline__ void mm_st_v4(void* mc, const uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void mm_st_b64(void* mc, const uint2 v) {
+  const uint64_t w = ((uint64_t)v.y << 32) | v.x;
+  asm volatile("multimem.st.relaxed.sys.global.b64 [%0], %1;" ::"l"(mc), "l"(w) : "memory");
+}
+__device__ __forceinline__ void mm_st_b32(void* mc, const uint32_t v) {
+  asm volatile("multimem.st.relaxed.sys.global.b32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
+
 template <typename T>
 struct Elem;
 template <>

@@ -8,9 +8,10 @@
 extern "C" {
 #endif
 
-/* Largest amount of scratch the entry point below can use: the size of the
- * static device array it owns.  Every GPU on which the library is loaded keeps
- * this much memory until the process exits. */
+/* Size of the static device array the entry point below keeps its scratch in.
+ * The array is part of the library's device code: the CUDA runtime sets it up on a
+ * GPU when the entry point is first called there (see "first call" below), and
+ * from then on that GPU holds these bytes until the process exits. */
 #define CX_NOALLOC_SCRATCH_BYTES 8192
 
 /* Same operation as cx_compress() on a CUDA device (r += g, select |r| > *thr,
@@ -26,17 +27,20 @@ extern "C" {
  * cx_compress(); the device that owns them must be the current device and
  * `stream` must belong to it.
  *
- * The first call on a device looks the array's address up (once per device) and
- * should therefore be made before any stream capture is started.
+ * The first call on a device is also the set-up: it asks the runtime for the
+ * array's device address (once per device), and with lazy module loading that is
+ * the moment the runtime places the array on the GPU.  Make that first call early
+ * - a call with n = 0 and no targets does - before the surrounding runtime claims
+ * the rest of the GPU's memory and before any stream capture is started.
  *
  * All calls share the one array per device.  It is cleared on the stream before
  * each use, but two calls whose kernels overlap on the GPU (different streams
  * without an ordering between them, or different host threads) race on it: keep
  * calls on one device ordered.
  *
- * Returns 0, or a negative value with the reason in cx_last_error(): n outside
- * 0 .. 2^31-1, more than CX_MAX_PEERS targets, or a vector whose scratch need,
- * cx_workspace_bytes(n), is larger than CX_NOALLOC_SCRATCH_BYTES. */
+ * Limits: vectors of 0 .. 2^31-1 elements, at most CX_MAX_PEERS targets.  Returns 0,
+ * or a negative value with the reason in cx_last_error() when a limit is exceeded
+ * (nothing is launched then). */
 int cx_compress_noalloc(int gdtype, const void* g, float* r, int64_t n, const float* thr,
                         uint32_t cap, uint64_t seq, const CxTargets* tg, CxStats* stats,
                         uint32_t src_rank, void* stream);

@@ -68,6 +68,21 @@ __device__ __forceinline__ void publish_dense(const CxTargets& tg, int k, int64_
   cx::st_release_sys(&h->seq, seq);
 }
 
+// four elements through the multicast mapping (16 bytes of fp32, 8 bytes of a 16-bit type)
+__device__ __forceinline__ void mc_store4(float* mc, const float (&v)[4]) {
+  cx::mm_st_v4(mc, make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3])));
+}
+__device__ __forceinline__ void mc_store4(__nv_bfloat16* mc, const float (&v)[4]) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]);
+  __nv_bfloat162 b = __floats2bfloat162_rn(v[2], v[3]);
+  cx::mm_st_b64(mc, make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b)));
+}
+__device__ __forceinline__ void mc_store4(__half* mc, const float (&v)[4]) {
+  __half2 a = __floats2half2_rn(v[0], v[1]);
+  __half2 b = __floats2half2_rn(v[2], v[3]);
+  cx::mm_st_b64(mc, make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b)));
+}
+
 template <typename T, bool HAS_R>
 __global__ void __launch_bounds__(kThreads) dense_send_kernel(const SendParams p) {
   __shared__ uint32_t s_last;
@@ -78,6 +93,8 @@ __global__ void __launch_bounds__(kThreads) dense_send_kernel(const SendParams p
     // same vector to every target, 4 elements per thread and step
     const bool vec = (reinterpret_cast<uintptr_t>(g) & (4 * sizeof(T) - 1)) == 0 &&
                      (!HAS_R || (reinterpret_cast<uintptr_t>(p.r) & 15) == 0);
+    // with a multicast endpoint the aligned body goes out once for all targets
+    const bool mc = (p.tg.pad & CX_TG_MULTICAST) != 0;
     const int64_t nv = (p.n + 3) / 4;
     for (int64_t q = gtid; q < nv; q += gsz) {
       const int64_t i = q * 4;
@@ -92,8 +109,12 @@ __global__ void __launch_bounds__(kThreads) dense_send_kernel(const SendParams p
           for (int e = 0; e < 4; ++e) x[e] += rr[e];
           cx::store4(p.r + i, z);
         }
-        for (int k = 0; k < p.tg.count; ++k)
-          cx::store4(reinterpret_cast<T*>(p.tg.ep[k].pairs) + i, x);
+        if (mc) {
+          mc_store4(reinterpret_cast<T*>(p.tg.ep[p.tg.count].pairs) + i, x);
+        } else {
+          for (int k = 0; k < p.tg.count; ++k)
+            cx::store4(reinterpret_cast<T*>(p.tg.ep[k].pairs) + i, x);
+        }
       } else {
         for (int e = 0; e < 4 && i + e < p.n; ++e) {
           float xe = cx::Elem<T>::to_f(g[i + e]);
@@ -298,9 +319,14 @@ __global__ void __launch_bounds__(kThreads) dense_reduce_kernel(const ReducePara
       if (p.scale != 1.f)
         for (int e = 0; e < 4; ++e) acc[e] *= p.scale;
       cx::store4(out + i, acc);
-      if (p.has_push)
-        for (int k = 0; k < p.push.count; ++k)
-          cx::store4(reinterpret_cast<T*>(p.push.ep[k].pairs) + i, acc);
+      if (p.has_push) {
+        if (p.push.pad & CX_TG_MULTICAST) {
+          mc_store4(reinterpret_cast<T*>(p.push.ep[p.push.count].pairs) + i, acc);
+        } else {
+          for (int k = 0; k < p.push.count; ++k)
+            cx::store4(reinterpret_cast<T*>(p.push.ep[k].pairs) + i, acc);
+        }
+      }
     } else {
       for (int e = 0; e < 4 && i + e < p.n; ++e) {
         float acc = 0.f;

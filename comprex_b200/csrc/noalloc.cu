@@ -47,6 +47,9 @@ extern "C" int cx_compress_noalloc(int gdtype, const void* g, float* r, int64_t 
     return cx_set_error("cx_compress_noalloc: n must be between 0 and 2^31-1 elements", 0);
   if (!tg || tg->count < 0 || tg->count > CX_MAX_PEERS)
     return cx_set_error("cx_compress_noalloc: between 0 and CX_MAX_PEERS targets are supported", 0);
+  // The kernel's scratch is a fixed block of counters today, well inside the array, so this
+  // guard cannot fire; it stays so that a kernel whose need grows with n is refused here
+  // instead of running past the array.
   const int64_t need = cx_workspace_bytes(n);
   if (need > CX_NOALLOC_SCRATCH_BYTES)
     return cx_set_error("cx_compress_noalloc: this vector needs more scratch than the static "
@@ -54,6 +57,7 @@ extern "C" int cx_compress_noalloc(int gdtype, const void* g, float* r, int64_t 
   void* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);
   if (rc) return rc;
+  if (n == 0 && tg->count == 0) return 0;   // the warm-up call: set-up only, nothing to send
   // the counters must start at zero; whatever an earlier call left behind is wiped on the stream
   const cudaError_t e = cudaMemsetAsync(scratch, 0, (size_t)need, reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cx_set_error("cx_compress_noalloc: cudaMemsetAsync", (int)e);

@@ -55,6 +55,8 @@ int cx_fold_host(int, const void* const*, const int64_t*, const int64_t*, const 
                  const int32_t*, int, float*, float*, float, float, float);
 int cx_axpy_host(int, void*, int, const void*, float, int64_t);
 int cx_update_dense_cuda(const float*, int64_t, const CxApplyArgs*, void*);
+int cx_mm_allreduce_cuda(int, void*, const void*, void*, void*, int64_t, int64_t, int, int, float, int, int64_t,
+                         uint64_t, void* const*, void*, uint32_t*, uint64_t, void*);
 int cx_update_dense_host(const float*, int64_t, const CxApplyArgs*);
 
 // ---- errors and accounting -------------------------------------------------------
@@ -117,6 +119,13 @@ int cx_apply(int dev, const CxSources* src, int64_t n, const CxApplyArgs* a, uin
 
 int cx_update_dense(int dev, const float* g, int64_t n, const CxApplyArgs* a, void* stream) {
   return dev == CX_DEV_CUDA ? cx_update_dense_cuda(g, n, a, stream) : cx_update_dense_host(g, n, a);
+}
+
+int cx_mm_allreduce(int dtype, void* out, const void* in, void* stage, void* stage_mc, int64_t stage_stride,
+                    int64_t n, int rank, int ranks, float scale, int one_shot, int64_t slab_bytes, uint64_t seq,
+                    void* const* flag_ptrs, void* counters, uint32_t* status, uint64_t timeout_ns, void* stream) {
+  return cx_mm_allreduce_cuda(dtype, out, in, stage, stage_mc, stage_stride, n, rank, ranks, scale, one_shot,
+                              slab_bytes, seq, flag_ptrs, counters, status, timeout_ns, stream);
 }
 
 int cx_forward(int dev, const CxEndpoint* from, uint64_t expect_seq, const CxTargets* tg,
@@ -215,6 +224,13 @@ int run_one(CxOp& o, uint64_t seq, void* stream) {
                              o.has_push ? &o.tg : nullptr, seq, o.has_ranges ? o.starts : nullptr,
                              o.has_ranges ? o.lens : nullptr, o.workspace, o.src_rank, o.status,
                              o.timeout_ns, stream);
+    case CX_OPK_MM_ALLREDUCE: {
+      void* flags[CX_MAX_PEERS];
+      for (int r = 0; r < CX_MAX_PEERS; ++r) flags[r] = reinterpret_cast<void*>(o.lens[r]);
+      return cx_mm_allreduce(o.dtype, o.out, o.own, const_cast<void*>(o.g), o.r, o.starts[0], o.n, (int)o.src_rank,
+                             (int)o.cap, o.scale, (int)o.starts[1], o.starts[2], seq, flags, o.workspace, o.status,
+                             o.timeout_ns, stream);
+    }
     case CX_OPK_UPDATE:
       return cx_update_dense(o.dev, reinterpret_cast<const float*>(o.g), o.n, &o.apply, stream);
     default:

@@ -59,6 +59,9 @@ constexpr int kGather = 4;  // loads of one thread that are in flight together
 template <typename T>
 __global__ void __launch_bounds__(kThreads) threshold_kernel(const ThreshParams p) {
   namespace cg = cooperative_groups;
+  // the compress kernel queued behind this one may start its prologue now; it waits (for this
+  // grid to finish) before it reads the threshold or writes the residual
+  asm volatile("griddepcontrol.launch_dependents;");
   __shared__ uint32_t s_keys[kSmemKeys];
   __shared__ uint32_t s_hist[256];
   __shared__ uint32_t s_sel[2];  // chosen digit, remaining rank

@@ -47,6 +47,15 @@ class SparseSlot:
         ep.cap = self.cap   # travels to make_sources: receivers never read beyond their slot
         return ep
 
+    def mc_endpoint(self, env: GaspiEnvironment):
+        """The slot through the multicast mapping (a store there lands in every rank's copy of the
+        slot), or None where the heap has none."""
+        base = env.mc_ptr(self.alloc)
+        if not base:
+            return None
+        nsub = (self.n + _lib.SUBTILE - 1) // _lib.SUBTILE
+        return Endpoint(base, base + HEADER_BYTES, base + HEADER_BYTES + _round_up(8 * max(nsub, 1), 16))
+
 
 @dataclass(frozen=True)
 class DenseSlot:
@@ -62,8 +71,15 @@ class DenseSlot:
         base = env.ptr(self.alloc, rank)
         return Endpoint(base, 0, base + HEADER_BYTES)
 
+    def mc_endpoint(self, env: GaspiEnvironment):
+        base = env.mc_ptr(self.alloc)
+        return Endpoint(base, 0, base + HEADER_BYTES) if base else None
 
-def make_targets(eps) -> Targets:
+
+def make_targets(eps, mc=None) -> Targets:
+    """Target descriptor.  ``mc`` is the multicast endpoint of the targets' slot (the same block on
+    every rank): payload data then goes out once through the switch instead of once per target.
+    It is only used for two or more targets (with one target a plain store moves the same bytes)."""
     eps = list(eps)
     if len(eps) > _lib.MAX_PEERS:
         raise ComprexError("too many targets")
@@ -71,6 +87,9 @@ def make_targets(eps) -> Targets:
     t.count = len(eps)
     for i, e in enumerate(eps):
         t.ep[i] = e
+    if mc is not None and 2 <= len(eps) < _lib.MAX_PEERS:
+        t.pad = _lib.TG_MULTICAST
+        t.ep[len(eps)] = mc
     return t
 
 
@@ -343,3 +362,60 @@ def dense_reduce(env: GaspiEnvironment, out: torch.Tensor, own, n: int, sources:
 def axpy(env: GaspiEnvironment, y: torch.Tensor, x: torch.Tensor, a: float, n: int) -> None:
     _lib.check(env.lib.cx_axpy(env.dev, _lib.dtype_code(y.dtype), y.data_ptr(), _lib.dtype_code(x.dtype),
                                x.data_ptr(), a, n, _lib.stream_ptr(env.device)), "cx_axpy")
+
+
+class MultimemAllreduce:
+    """Staging block, flags and counters of one dense allreduce through the switch
+    (csrc/nvls.cu: ``multimem.ld_reduce`` + ``multimem.st``, one kernel per rank and call).
+
+    Construction is collective (symmetric allocations).  ``one_shot_bytes``: vectors up to that
+    size are reduced by every rank itself in one exchange (double-buffered staging); larger ones
+    use reduce-scatter + broadcast inside the switch, pipelined in slabs of ``slab_bytes``.  A
+    vector that lives in the symmetric heap (``env.empty``) and is a multiple of 16 bytes is
+    reduced in place, without the staging copies."""
+
+    def __init__(self, env: GaspiEnvironment, size: int, dtype: torch.dtype, one_shot_bytes=None, slab_bytes=None):
+        import os
+        if not env.nvls:
+            raise ComprexError("the heap has no multicast mapping")
+        self.env, self.size, self.dtype = env, int(size), dtype
+        es = torch.empty(0, dtype=dtype).element_size()
+        nbytes = _round_up(max(self.size, 1) * es, 16)
+        if one_shot_bytes is None:
+            one_shot_bytes = int(os.environ.get("COMPREX_MM_ONE_SHOT_BYTES", 512 << 10))
+        if slab_bytes is None:
+            slab_bytes = int(os.environ.get("COMPREX_MM_SLAB_BYTES", 32 << 20))
+        self.one_shot = nbytes <= one_shot_bytes
+        self.slab_bytes = int(slab_bytes)
+        self.stride = _round_up(nbytes, 256)
+        self.stage = env.alloc(self.stride * (2 if self.one_shot else 1), 256)
+        self.flags = env.alloc(int(env.lib.cx_mm_flag_bytes()), 256)
+        self.counters = env.scratch(int(env.lib.cx_mm_counter_bytes()))
+        self._flag_list = [env.ptr(self.flags, r) for r in range(env.ranks)]
+        self.flag_ptrs = (C.c_void_p * _lib.MAX_PEERS)(*(self._flag_list + [None] * (_lib.MAX_PEERS - env.ranks)))
+
+    def run(self, t: torch.Tensor, seq: int, scale: float, status) -> None:
+        """In-place allreduce of ``t`` (``scale`` times the sum, the same bits on every rank)."""
+        env = self.env
+        if t.dtype != self.dtype or t.numel() != self.size:
+            raise ComprexError("vector does not match the allreduce")
+        es = t.element_size()
+        blk = env.heap_block(t)
+        if blk is not None and not self.one_shot and (self.size * es) % 16 == 0 and env.mc_ptr(blk):
+            out, src, stage, stage_mc, slab = 0, 0, env.ptr(blk), env.mc_ptr(blk), 0     # in place
+        else:
+            out, src, stage, stage_mc, slab = t.data_ptr(), t.data_ptr(), env.ptr(self.stage), env.mc_ptr(self.stage), self.slab_bytes
+        if _recording(env):
+            op = _new_op(env, _lib.OPK_MM_ALLREDUCE, _lib.dtype_code(t.dtype), self.size)
+            op.out, op.own, op.g, op.r = out, src, stage, stage_mc
+            op.starts[0], op.starts[1], op.starts[2] = self.stride, int(self.one_shot), slab
+            for r, ptr in enumerate(self._flag_list):
+                op.lens[r] = ptr
+            op.src_rank, op.cap, op.workspace, op.scale = env.rank, env.ranks, self.counters.data_ptr(), scale
+            op.status, op.timeout_ns = status.dev_ptr, env.timeout_ns
+            env._rec.append(op)
+            return
+        _lib.check(env.lib.cx_mm_allreduce(_lib.dtype_code(t.dtype), out, src, stage, stage_mc, self.stride, self.size,
+                                           env.rank, env.ranks, scale, int(self.one_shot), slab, seq, self.flag_ptrs,
+                                           self.counters.data_ptr(), status.dev_ptr, env.timeout_ns,
+                                           _lib.stream_ptr(env.device)), "cx_mm_allreduce")

@@ -378,8 +378,9 @@ class ComprexOptimizer(torch.optim.Optimizer):
             elif b.kind == "phased":
                 b.xbuf.copy_(u)
                 b.plan = b.ar._plan_apply(b.xbuf)
-                if b.plan:
-                    b.plan[0]()                 # the first phase of every schedule only sends
+                if b.plan and not b.ar.first_phase_waits:
+                    b.plan[0]()                 # a first phase that only sends goes out right away
+                    b.plan = b.plan[1:]
             else:
                 b.u = u
         b.sent = True
@@ -394,7 +395,7 @@ class ComprexOptimizer(torch.optim.Optimizer):
                 b.ar.recv_fast(b.xbuf, b.seq, b.par,
                                lambda c, start, size: self._args(b.start + start, size, lr, mu, wd, 1.0 / env.ranks))
             elif b.kind == "phased":
-                for phase in b.plan[1:]:
+                for phase in b.plan:
                     phase()
                 b.plan = None
                 P.update_dense(env, b.xbuf, n, self._args(b.start, n, lr, mu, wd, 1.0 / env.ranks))

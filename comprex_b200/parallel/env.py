@@ -48,6 +48,23 @@ class SymmAlloc:
     nbytes: int
 
 
+class _RawCuda:
+    """CUDA array interface over raw device memory, so that torch can wrap a heap block."""
+
+    def __init__(self, ptr: int, nbytes: int, owner):
+        self.owner = owner
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def _tensor_at(ptr: int, n: int, dtype, device, owner) -> torch.Tensor:
+    es = torch.empty(0, dtype=dtype).element_size()
+    if device.type == "cuda":
+        raw = torch.as_tensor(_RawCuda(ptr, max(n, 1) * es, owner), device=device)
+    else:
+        raw = torch.frombuffer((C.c_char * (max(n, 1) * es)).from_address(ptr), dtype=torch.uint8)
+    return raw.view(dtype)[:n]
+
+
 class _PinnedBlock:
     """Status words and statistics: host memory that kernels can write."""
 
@@ -157,7 +174,12 @@ class GaspiEnvironment:
         self._status_words: list[tuple[StatusWord, str]] = []
         self._uid = None
         self._closed = False
+        self._heap_tensors: dict[int, SymmAlloc] = {}
         self.sync_check = self.dev == _lib.DEV_HOST or os.environ.get("COMPREX_SYNC_CHECK", "0") == "1"
+        # NVSwitch multicast (multimem stores / in-switch reduction): used where the heap can be
+        # bound to a multicast object; COMPREX_NVLS=0 keeps every transfer on plain peer stores
+        self.want_nvls = (self.dev == _lib.DEV_CUDA and _world is None and self.ranks > 1
+                          and os.environ.get("COMPREX_NVLS", "1") != "0")
 
     # ---- reference surface (gpi.py:147-174) ---------------------------------
     def get_rank(self) -> int:
@@ -192,7 +214,7 @@ class GaspiEnvironment:
 
     def __del__(self):
         try:
-            self.close()
+            self.close(collective=False)
         except Exception:
             pass
 
@@ -261,8 +283,13 @@ class GaspiEnvironment:
         hosts = self._exchange(socket.gethostname())
         if len(set(hosts)) != 1:
             raise ComprexError("all ranks of an environment must share one NVLink domain (one host)")
-        mode = os.environ.get("COMPREX_HEAP", "ipc")
+        mode = os.environ.get("COMPREX_HEAP", "symm" if self.want_nvls else "ipc")
         err = None
+        if mode == "symm":
+            seg = self._new_symm_segment(nbytes)
+            if seg is not None:
+                return seg
+            mode = "ipc"
         if mode == "ipc":
             base = self.lib.cx_cuda_malloc(nbytes)
             handle = (C.c_char * 64)()
@@ -288,16 +315,34 @@ class GaspiEnvironment:
             if base:
                 self.lib.cx_cuda_free(base)
         # symmetric memory of torch.distributed as the second way to map peers
+        seg = self._new_symm_segment(nbytes)
+        if seg is None:
+            raise ComprexError(f"cannot map peer memory (CUDA IPC: {err}; symmetric memory: {self._symm_error})")
+        return seg
+
+    def _new_symm_segment(self, nbytes: int):
+        """A segment from torch's symmetric memory: peers are mapped like with CUDA IPC, and where
+        the NVSwitch supports it the block is also bound to a multicast object, whose address
+        (``mc``) lets one ``multimem`` instruction reach the same offset on every rank.  Returns
+        None (on every rank alike) when any rank fails."""
+        seg, self._symm_error = None, None
         try:
             import torch.distributed._symmetric_memory as symm
             t = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
             t.zero_()
             hdl = symm.rendezvous(t, self.group.group_name if self.group is not None else dist.group.WORLD.group_name)
             bases = [int(p) for p in hdl.buffer_ptrs]
+            mc = int(hdl.multicast_ptr) if (self.want_nvls and getattr(hdl, "has_multicast_support", False)) else 0
             torch.cuda.synchronize(self.device)
-            return {"bases": bases, "size": nbytes, "used": 0, "keep": ("symm", t, hdl)}
-        except Exception as exc:
-            raise ComprexError(f"cannot map peer memory (CUDA IPC: {err}; symmetric memory: {exc})") from exc
+            seg = {"bases": bases, "size": nbytes, "used": 0, "keep": ("symm", t, hdl), "mc": mc}
+        except Exception as exc:           # noqa: BLE001 - any failure means "use the other mapping"
+            self._symm_error = exc
+        oks = self._exchange((seg is not None, bool(seg and seg["mc"])))
+        if not all(ok for ok, _ in oks):
+            return None
+        if not all(m for _, m in oks):
+            seg["mc"] = 0
+        return seg
 
     def _new_shm_segment(self, idx: int, nbytes: int) -> dict:
         if self._uid is None:
@@ -342,6 +387,35 @@ class GaspiEnvironment:
         r = self.rank if rank is None else rank
         return self._segments[a.seg]["bases"][r] + a.offset + offset
 
+    def mc_ptr(self, a: SymmAlloc, offset: int = 0) -> int:
+        """Multicast address of the block (a store there lands in every rank's copy), 0 if none."""
+        base = self._segments[a.seg].get("mc", 0)
+        return base + a.offset + offset if base else 0
+
+    @property
+    def nvls(self) -> bool:
+        """True when blocks of the heap have a multicast address (allocates the first segment)."""
+        if not self.want_nvls:
+            return False
+        if not self._segments:
+            self._new_segment(self.segment_size)
+        return bool(self._segments[-1].get("mc", 0))
+
+    def empty(self, n: int, dtype=torch.float32):
+        """A vector of ``n`` elements inside the symmetric heap (collective: every rank allocates
+        the same sizes in the same order).  Collectives that find their argument in the heap work
+        on it in place, without staging copies; the reference requires the same of its buffers
+        (they live in the registered GASPI segment, src/gaspiEx.tpp:127-135)."""
+        es = torch.empty(0, dtype=dtype).element_size()
+        a = self.alloc(max(n, 1) * es, 256)
+        t = _tensor_at(self.ptr(a), n, dtype, self.device, self)
+        self._heap_tensors[t.data_ptr()] = a
+        return t
+
+    def heap_block(self, t: torch.Tensor):
+        """The SymmAlloc a tensor made by :meth:`empty` lives in (None for any other tensor)."""
+        return self._heap_tensors.get(t.data_ptr()) if t is not None else None
+
     def heap_mark(self):
         """Snapshot of the allocator; pass to :meth:`heap_release` (collective)."""
         return (len(self._segments), self._segments[-1]["used"] if self._segments else 0)
@@ -353,6 +427,8 @@ class GaspiEnvironment:
         blocks that are about to be zeroed and handed out again."""
         nseg, used = mark
         self.barrier()
+        self._heap_tensors = {k: a for k, a in self._heap_tensors.items()
+                              if a.seg < nseg - 1 or (a.seg == nseg - 1 and a.offset + a.nbytes <= used)}
         while len(self._segments) > max(nseg, 1):
             self._free_segment(self._segments.pop(), collective=True)
         if self._segments and nseg >= 1:
@@ -383,17 +459,23 @@ class GaspiEnvironment:
         elif kind == "shm":
             for p in seg["bases"]:
                 self.lib.cx_shm_close(p, keep[1])
-        seg["keep"] = None
+        seg["keep"] = None            # "symm": torch frees the block when the last reference goes
 
-    def close(self) -> None:
+    def close(self, collective: bool = True) -> None:
+        """Free the heap.  With multicast-bound segments an explicit close first waits for all
+        ranks: no rank unbinds its memory while a peer's kernel may still address it."""
         if self._closed:
             return
         self._closed = True
         try:
             if self.dev == _lib.DEV_CUDA and torch.cuda.is_available():
                 torch.cuda.synchronize(self.device)
+            if (collective and self.group is not None and dist.is_initialized()
+                    and any(seg.get("mc", 0) for seg in self._segments)):
+                dist.barrier(group=self.group)
         except Exception:
             pass
+        self._heap_tensors = {}
         for seg in self._segments:
             self._free_segment(seg)
         self._segments = []

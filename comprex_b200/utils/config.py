@@ -18,7 +18,7 @@ import dataclasses
 import os
 from dataclasses import dataclass
 
-_TOPOLOGIES = ("comprex_bigring", "comprex_ring", "comprex_alltoone", "bigring", "ring", "alltoone")
+_TOPOLOGIES = ("comprex_bigring", "comprex_ring", "comprex_alltoone", "bigring", "ring", "alltoone", "auto")
 
 
 @dataclass
@@ -46,6 +46,7 @@ class ComprexConfig:
     pre_clipnorm: float = 5.0
     bucket_cap_mb: float = 25.0
     overlap: bool = True
+    aggregate_blob: bool = True              # False: one allreducer per tensor (keras/comprex_optimizer.py:77-96)
     # runtime
     segment_bytes: int = 1 << 30             # symmetric heap per rank
     timeout_ms: int = 10000                  # budget of every device-side wait
@@ -146,12 +147,16 @@ class ComprexConfig:
         from .. import allreduce as A
         cls = {"comprex_bigring": A.Comprex_BigRingAllreduce, "comprex_ring": A.Comprex_RingAllreduce,
                "comprex_alltoone": A.Comprex_AllToOneAllreduce, "bigring": A.BigRingAllreduce,
-               "ring": A.RingAllreduce, "alltoone": A.AllToOneAllreduce}[self.topology]
+               "ring": A.RingAllreduce, "alltoone": A.AllToOneAllreduce, "auto": A.AutoAllreduce}[self.topology]
         ar = cls(env)
         if self.topology == "comprex_bigring":
             ar.setup_connections(size, tag, self.compression_ratio, self.size_factor, consistent=self.consistent)
+        elif self.topology == "auto":
+            ar.setup_connections(size, tag, self.compression_ratio, self.size_factor, consistent=self.consistent)
         elif self.topology == "comprex_ring":
-            ar.setup_connections(size, tag, self.compression_ratio, self.size_factor, consistent=self.consistent,
+            # the hop-by-hop ring is the reference's schedule with the reference's semantics
+            ar.setup_connections(size, tag, self.compression_ratio, self.size_factor,
+                                 consistent=self.consistent and self.ring_schedule == "direct",
                                  schedule=self.ring_schedule)
         elif self.topology == "comprex_alltoone":
             ar.setup_connections(size, tag, 0, self.compression_ratio, self.size_factor, stale=self.stale)
@@ -162,16 +167,15 @@ class ComprexConfig:
         else:
             ar.setup_connections(size, tag)
         if self.exact_topk and ar.compressed:
-            ar.set_exact_topk(True)
+            getattr(ar, "impl", ar).set_exact_topk(True)
         return ar
 
     def optimizer(self, params, env, **kwargs):
         from ..optim import ComprexOptimizer
-        fused = self.topology == "comprex_bigring"
         args = dict(compression_ratio=self.compression_ratio, allreduce_type=self.topology,
                     size_factor=self.size_factor, pre_clipnorm=self.pre_clipnorm,
-                    local_momentum=self.local_momentum, rule=self.rule,
-                    bucket_cap_mb=self.bucket_cap_mb if fused else None, overlap=self.overlap and fused)
+                    local_momentum=self.local_momentum, rule=self.rule, consistent=self.consistent,
+                    bucket_cap_mb=self.bucket_cap_mb, overlap=self.overlap, aggregate_blob=self.aggregate_blob)
         args.update(kwargs)
         return ComprexOptimizer(params, env, **args)
 

@@ -42,6 +42,10 @@ def test_noalloc_entry_matches_regular_entry_twice(n, dtype):
                    C.POINTER(_lib.Targets), C.c_void_p, C.c_uint32, C.c_void_p]
     torch.manual_seed(11)
     env = cx.GaspiEnvironment(32 << 20, device="cuda")
+    # warm-up as the header asks: an empty call sets the static array up on this device
+    none = _lib.Targets()
+    assert fn(_lib.F32, None, None, 0, torch.zeros(1, device="cuda").data_ptr(), 0, 0, C.byref(none), None, 0,
+              torch.cuda.current_stream().cuda_stream) == 0, _lib.last_error()
     cap = n // 4
     slot_a, slot_b = P.SparseSlot.create(env, n, cap), P.SparseSlot.create(env, n, cap)
     comp = P.Compressor(env, n)                       # regular entry: scratch from the caller
@@ -54,9 +58,14 @@ def test_noalloc_entry_matches_regular_entry_twice(n, dtype):
         comp.thr.copy_(thr)
         comp.compress(g, r_a, n, cap, call, P.make_targets([slot_a.endpoint(env)]))
         tg = P.make_targets([slot_b.endpoint(env)])
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = fn(_lib.dtype_code(dtype), g.data_ptr(), r_b.data_ptr(), n, thr.data_ptr(), cap, call,
                 C.byref(tg), None, 0, stream)
         assert rc == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        if call == 2:      # the property in the name: once set up, a call takes no device memory
+            assert torch.cuda.mem_get_info()[0] == free_before
         env.flush()
         ha, ia, va, ca = _canonical(env, slot_a)
         hb, ib, vb, cb = _canonical(env, slot_b)
