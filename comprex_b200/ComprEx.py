@@ -115,6 +115,7 @@ class ThresholdTopK(_Threshold):
         self.default_subsamples = int(default_subsamples)
         self.subsample_factor = float(subsample_factor)
         self._cell = None
+        self._ws = None
 
     def getTopK(self) -> float:
         return self.topK
@@ -131,10 +132,14 @@ class ThresholdTopK(_Threshold):
         ref = g if g is not None else r
         out = torch.zeros(1, dtype=torch.float32, device=ref.device)
         gd = _lib.dtype_code(g.dtype) if g is not None else _lib.F32
-        _lib.check(lib.cx_threshold_topk(_lib.dev_code(ref), gd, g.data_ptr() if g is not None else 0,
-                                         r.data_ptr() if r is not None else 0, ref.numel(), self.topK,
-                                         self.default_subsamples, self.subsample_factor, out.data_ptr(),
-                                         _lib.stream_ptr(ref.device)), "cx_threshold_topk")
+        ws_bytes = int(lib.cx_threshold_workspace_bytes()) if self.exact else 0
+        if self.exact and (self._ws is None or self._ws.device != ref.device):
+            self._ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=ref.device)   # grid-wide exact selection
+        _lib.check(lib.cx_threshold_select(_lib.dev_code(ref), gd, g.data_ptr() if g is not None else 0,
+                                           r.data_ptr() if r is not None else 0, ref.numel(), self.topK,
+                                           self.default_subsamples, self.subsample_factor, out.data_ptr(),
+                                           self._ws.data_ptr() if self.exact else 0, ws_bytes,
+                                           _lib.stream_ptr(ref.device)), "cx_threshold_select")
         self._cell = out
 
     def prepare(self, vec) -> None:

@@ -99,7 +99,12 @@ class GaspiEx(AbstractExchange):
             seqs.append(seq)
         if len(set(seqs)) != 1:
             raise ComprexError("destinations of one multi-target write must have seen the same number of writes")
-        return P.make_targets(eps), seqs[0]
+        # Several destinations share one payload: where the heap is bound to a multicast object the
+        # vector crosses the sender's link once (connectTx_sameBufferAs, src/gaspiEx.tpp:142-153).
+        # A multicast store also lands in the sender's own copy of the slot, so it is only used by
+        # an engine that does not receive (a broadcasting chief).
+        mc = self._slots[seqs[0] & 1].mc_endpoint(self._env) if self._src is None else None
+        return P.make_targets(eps, mc=mc), seqs[0]
 
     def writeRemote(self, vector=None, size: int | None = None) -> None:
         """Send ``vector`` to the connected rank.  Without a vector, re-send the

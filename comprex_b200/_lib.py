@@ -99,6 +99,8 @@ def _declare(lib) -> None:
         "cx_workspace_bytes": (i64, [i64]),
         "cx_threshold_plan": (None, [i64, f32, i32, f32, P(C.c_int32), P(C.c_int32), P(f32), P(C.c_int32)]),
         "cx_threshold_topk": (i32, [i32, i32, vp, vp, i64, f32, i32, f32, vp, vp]),
+        "cx_threshold_workspace_bytes": (i64, []),
+        "cx_threshold_select": (i32, [i32, i32, vp, vp, i64, f32, i32, f32, vp, vp, i64, vp]),
         "cx_compress": (i32, [i32, i32, vp, vp, i64, vp, u32, u64, P(Targets), vp, i64, vp, u32, vp]),
         "cx_apply": (i32, [i32, P(Sources), i64, P(ApplyArgs), vp, u64, vp]),
         "cx_update_dense": (i32, [i32, vp, i64, P(ApplyArgs), vp]),

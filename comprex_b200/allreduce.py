@@ -555,6 +555,7 @@ class Comprex_BigRingAllreduce(_ComprexAllreduceBase):
             thr.r = cmp_.r = self.rests.data_ptr()
             thr.thr = cmp_.thr = comp.thr.data_ptr()
             thr.default_subsamples, thr.subsample_factor = self._subsamples, self._sample_factor
+            thr.workspace, thr.ws_bytes = comp.thr_ws.data_ptr(), comp.thr_ws_bytes
             cmp_.cap, cmp_.src_rank = self.cap, env.rank
             cmp_.workspace, cmp_.ws_bytes, cmp_.stats = comp.workspace.data_ptr(), comp.ws_bytes, comp.stats.dev_ptr
             cmp_.tg = self._send_targets(par)

@@ -143,6 +143,7 @@ struct Compressor {   // scratch, threshold cell and statistics of one sparse se
   void* workspace;
   int64_t ws_bytes;
   float* thr;
+  void* thr_ws;        // scratch of the exact (whole-vector) threshold selection
   CxStats* stats;
 };
 
@@ -185,8 +186,9 @@ bool make_compressor(CxComm* c, Compressor* k) {
   k->ws_bytes = cx_workspace_bytes(0);
   k->workspace = c->local_alloc(k->ws_bytes);
   k->thr = reinterpret_cast<float*>(c->local_alloc(64));
+  k->thr_ws = c->local_alloc(cx_threshold_workspace_bytes());
   k->stats = reinterpret_cast<CxStats*>(c->local_alloc(sizeof(CxStats)));
-  return k->workspace && k->thr && k->stats;
+  return k->workspace && k->thr && k->thr_ws && k->stats;
 }
 
 CxOp blank(const CxAllreduce* ar, int kind, int dtype, int64_t n, int lane) {
@@ -208,6 +210,7 @@ CxOp op_threshold(const CxAllreduce* ar, const void* g, int gdtype, float* r, in
   CxOp o = blank(ar, CX_OPK_THRESHOLD, gdtype, n, lane);
   o.g = g; o.r = r; o.thr = k.thr; o.ratio = ar->ratio;
   o.default_subsamples = subsamples; o.subsample_factor = factor;
+  o.workspace = k.thr_ws; o.ws_bytes = cx_threshold_workspace_bytes();
   return o;
 }
 

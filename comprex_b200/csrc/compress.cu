@@ -8,13 +8,12 @@
 //     r += g ; if |r| > thr { emit (i, r) ; r = 0 }
 //
 // Work is warp-granular and free of block-wide barriers: a warp owns one
-// 1024-element sub-tile at a time, streams it twice with 16-byte accesses
-// (classify; then, with the second read served from cache, write the residual
-// and pick the survivors up; only a 32-bit survivor mask stays in registers),
-// ranks the survivors with one warp scan, reserves room for them in the pair
-// list with ONE atomicAdd on a counter in this GPU's memory, and stores them
-// through a small shared staging buffer as coalesced 8-byte (index, value)
-// pairs straight into the receive
+// 1024-element sub-tile at a time, loads it with 16-byte accesses (32
+// elements per lane, all loads in flight together, the next sub-tile already
+// on its way into L2), ranks the survivors with one warp scan, reserves room
+// for them in the pair list with ONE atomicAdd on a counter in this GPU's
+// memory, and stores them through a small shared staging buffer as coalesced
+// 8-byte (index, value) pairs straight into the receive
 // slots of up to CX_MAX_PEERS targets (peer GPUs' memory mapped over NVLink,
 // or local slots), or once through the switch's multicast mapping.  No warp
 // ever waits for another one, so the kernel has no spin loop at all.
@@ -39,18 +38,12 @@
 namespace {
 
 #ifndef CX_COMPRESS_MIN_BLOCKS
-#define CX_COMPRESS_MIN_BLOCKS 5  // CTAs per SM the register budget is set for (48 registers, no spills)
+#define CX_COMPRESS_MIN_BLOCKS 3  // CTAs per SM the register budget is tuned for
+#endif
+#ifndef CX_COMPRESS_PREFETCH
+#define CX_COMPRESS_PREFETCH 1    // L2 prefetch of the warp's next sub-tile
 #endif
 
-// chunks (two 16-byte loads per lane each) in flight in the classifying and in the writing pass
-#ifndef CX_COMPRESS_UNROLL1
-#define CX_COMPRESS_UNROLL1 4
-#endif
-#ifndef CX_COMPRESS_UNROLL2
-#define CX_COMPRESS_UNROLL2 2
-#endif
-
-constexpr int kUnroll1 = CX_COMPRESS_UNROLL1, kUnroll2 = CX_COMPRESS_UNROLL2;
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kChunks = CX_SUBTILE / 128;  // 128 elements = 32 lanes x 4
@@ -74,37 +67,63 @@ struct CompressParams {
   CxTargets tg;
 };
 
-// One aligned, complete sub-tile, one warp; lane L holds elements {c*128 + 4L + e}.  Two passes
-// with 16-byte accesses and nothing but a 32-bit survivor mask kept in between: the first pass
-// only classifies (r + g against the threshold), the second one, after the reservation, loads
-// the same lines again (they sit in L1/L2), writes the residual (zero for what is sent, the sum
-// for the rest) and hands the survivors over chunk by chunk.  Four values per lane are live at
-// any time instead of thirty-two, so the kernel runs without spills at 48 registers and five
-// CTAs per SM; DRAM traffic is the same as for a single pass.
+// One aligned, complete sub-tile, one warp, one pass: lane L holds elements {c*128 + 4L + e} in
+// registers from the loads to the write-back of the residual.
 template <typename T, bool HAS_G, bool HAS_R, bool MC>
-__device__ __forceinline__ void compress_subtile_stream(const CompressParams& p, const uint32_t sub,
-                                                        const int lane, const float thr,
-                                                        const T* __restrict__ g, float* __restrict__ r,
-                                                        CxPair* stage) {
+__device__ __forceinline__ void compress_subtile_regs(const CompressParams& p, const uint32_t sub,
+                                                 const int lane, const float thr,
+                                                 const T* __restrict__ g, float* __restrict__ r,
+                                                 CxPair* stage) {
+  constexpr bool FULL = true;
   const int64_t sub_base = (int64_t)sub * CX_SUBTILE;
   const T* gp = g + sub_base + lane * 4;
   float* rp = r + sub_base + lane * 4;
-  uint32_t mask = 0;
-#pragma unroll kUnroll1
+  const int left = (int)min((int64_t)CX_SUBTILE, p.n - sub_base) - lane * 4;  // my elements e < left - c*128
+
+  // ---- load, add -------------------------------------------------------------
+  float v[kChunks][4];
+#pragma unroll
   for (int c = 0; c < kChunks; ++c) {
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    if (HAS_R) cx::load4(rp + c * 128, v);
-    if (HAS_G) {
-      float b[4];
-      cx::load4(gp + c * 128, b);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) v[e] = v[e] + b[e];
+    for (int e = 0; e < 4; ++e) v[c][e] = 0.f;
+    if (HAS_R) {
+      if (FULL) {
+        cx::load4(rp + c * 128, v[c]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (c * 128 + e < left) v[c][e] = rp[c * 128 + e];
+      }
     }
+  }
+  if (HAS_G) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) mask |= (fabsf(v[e]) > thr ? 1u : 0u) << (4 * c + e);
+    for (int c = 0; c < kChunks; ++c) {
+      float b[4] = {0.f, 0.f, 0.f, 0.f};
+      if (FULL) {
+        cx::load4(gp + c * 128, b);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (c * 128 + e < left) b[e] = cx::Elem<T>::to_f(gp[c * 128 + e]);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[c][e] = v[c][e] + b[e];
+    }
   }
 
-  // ---- rank: lanes in order, each lane's survivors consecutive; reserve; table entry ------------
+  // ---- classify: bit c*4+e of mask, strict '>' like the reference --------------
+  uint32_t mask = 0;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const bool sel = fabsf(v[c][e]) > thr && (FULL || c * 128 + e < left);
+      mask |= (sel ? 1u : 0u) << (4 * c + e);
+    }
+  }
+
+  // ---- rank: lanes in order, each lane's survivors consecutive --------------------
   const uint32_t mine = __popc(mask);
   uint32_t incl = mine;
 #pragma unroll
@@ -113,7 +132,9 @@ __device__ __forceinline__ void compress_subtile_stream(const CompressParams& p,
     if (lane >= d) incl += t;
   }
   const uint32_t count = __shfl_sync(0xffffffffu, incl, 31);
-  const uint32_t first = incl - mine;
+  const uint32_t first = incl - mine;  // position of my first survivor inside the sub-tile
+
+  // ---- reserve room in the pair list ----------------------------------------------
   // The list is cut into nregions equal regions with one counter each, neighbouring
   // sub-tiles use different regions: atomics on one address are serialised by the L2.
   const uint32_t region = sub & (p.nregions - 1);
@@ -134,61 +155,75 @@ __device__ __forceinline__ void compress_subtile_stream(const CompressParams& p,
       reinterpret_cast<uint2*>(p.tg.ep[lane].table)[sub] = entry;
     }
   }
-  if (count == 0 && !(HAS_R && HAS_G)) return;   // nothing to send and nothing to write back
 
-  // ---- second pass: residual out, survivors to the staging buffer (or straight to the slots) ---
-  const bool staged = emit <= (uint32_t)kStage;    // a denser sub-tile stores its pairs lane by lane
+  // ---- stage in shared memory, store coalesced to every target ------------------------
   const int32_t idx0 = (int32_t)sub_base + lane * 4;
-  uint32_t pos = first;
-#pragma unroll kUnroll2
-  for (int c = 0; c < kChunks; ++c) {
-    const uint32_t m = (mask >> (4 * c)) & 0xfu;
-    if (!(HAS_R && HAS_G) && m == 0) continue;     // nothing changes in this chunk
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    if (HAS_R) cx::load4(rp + c * 128, v);
-    if (HAS_G) {
-      float b[4];
-      cx::load4(gp + c * 128, b);
+  for (uint32_t w0 = 0; w0 < emit; w0 += kStage) {   // one pass unless the sub-tile is dense
+    uint32_t pos = first - w0;                        // wraps below the window: fails the test
 #pragma unroll
-      for (int e = 0; e < 4; ++e) v[e] = v[e] + b[e];
-    }
+    for (int c = 0; c < kChunks; ++c) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      if (m & (1u << e)) {
-        if (pos < emit) {     // survivors beyond the slot's room stay in the residual
-          CxPair pr;
-          pr.idx = idx0 + c * 128 + e;
-          pr.val = __float_as_uint(v[e]);
-          if (staged) {
+      for (int e = 0; e < 4; ++e) {
+        if (mask & (1u << (4 * c + e))) {
+          if (pos < (uint32_t)kStage) {
+            CxPair pr;
+            pr.idx = idx0 + c * 128 + e;
+            pr.val = __float_as_uint(v[c][e]);
             stage[pos] = pr;
-          } else if (MC) {
-            cx::mm_st_b64(p.tg.ep[p.tg.count].pairs + base + pos, make_uint2((uint32_t)pr.idx, pr.val));
-          } else {
-            for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].pairs[base + pos] = pr;
           }
-          v[e] = 0.f;
+          ++pos;
         }
-        ++pos;
       }
     }
-    if (HAS_R) cx::store4(rp + c * 128, v);
-  }
-  if (!staged || emit == 0) return;
-  __syncwarp();
-  if (MC) {
-    // one store per pair into the multicast mapping: the switch writes every target's slot
-    CxPair* mc = p.tg.ep[p.tg.count].pairs + base;
-    for (uint32_t i = lane; i < emit; i += 32) {
-      const CxPair pr = stage[i];
-      cx::mm_st_b64(mc + i, make_uint2((uint32_t)pr.idx, pr.val));
+    __syncwarp();
+    const uint32_t lim = min((uint32_t)kStage, emit - w0);
+    if (MC) {
+      // one store per pair into the multicast mapping: the switch writes every target's slot
+      CxPair* mc = p.tg.ep[p.tg.count].pairs + base + w0;
+      for (uint32_t i = lane; i < lim; i += 32) {
+        const CxPair pr = stage[i];
+        cx::mm_st_b64(mc + i, make_uint2((uint32_t)pr.idx, pr.val));
+      }
+    } else {
+      for (uint32_t i = lane; i < lim; i += 32) {
+        const CxPair pr = stage[i];
+        for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].pairs[base + w0 + i] = pr;
+      }
     }
-  } else {
-    for (uint32_t i = lane; i < emit; i += 32) {
-      const CxPair pr = stage[i];
-      for (int k = 0; k < p.tg.count; ++k) p.tg.ep[k].pairs[base + i] = pr;
+    __syncwarp();
+  }
+
+  // ---- residual: zero what was emitted, keep the rest ---------------------------------------
+  if (HAS_R) {
+    if (emit < count) {  // the slot is full: survivors from position emit on stay in the residual
+      uint32_t pos = first;
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (mask & (1u << (4 * c + e))) {
+            if (pos >= emit) mask &= ~(1u << (4 * c + e));
+            ++pos;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+      const uint32_t m = (mask >> (4 * c)) & 0xfu;
+      if (!HAS_G && m == 0) continue;  // nothing changed in this vector
+      float out[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) out[e] = (m & (1u << e)) ? 0.f : v[c][e];
+      if (FULL) {
+        cx::store4(rp + c * 128, out);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (c * 128 + e < left) rp[c * 128 + e] = out[e];
+      }
     }
   }
-  __syncwarp();
 }
 
 // Sub-tiles that are partial or not aligned for 16-byte accesses (the last one of a vector, views
@@ -291,7 +326,17 @@ compress_kernel(const __grid_constant__ CompressParams p) {
   const uint32_t nfull = p.vec ? (uint32_t)(p.n / CX_SUBTILE) : 0u;  // sub-tiles on the fast path
 
   for (uint32_t sub = blockIdx.x * kWarps + warp; sub < p.nsub; sub += nwarps) {
-    if (sub < nfull) compress_subtile_stream<T, HAS_G, HAS_R, MC>(p, sub, lane, thr, g, r, stage);
+#if CX_COMPRESS_PREFETCH
+    // the warp's next sub-tile starts its way from DRAM to L2 now (one 128-byte line per lane
+    // and vector): its loads then find it there, without holding a register in the meantime
+    if ((uint64_t)sub + nwarps < nfull) {
+      const int64_t e0 = ((int64_t)sub + nwarps) * CX_SUBTILE;
+      if (HAS_R) asm volatile("prefetch.global.L2 [%0];" ::"l"(r + e0 + lane * 32));
+      if (HAS_G && lane * (128 / (int)sizeof(T)) < CX_SUBTILE)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(g + e0 + lane * (128 / (int)sizeof(T))));
+    }
+#endif
+    if (sub < nfull) compress_subtile_regs<T, HAS_G, HAS_R, MC>(p, sub, lane, thr, g, r, stage);
     else compress_subtile_edge<T, HAS_G, HAS_R, MC>(p, sub, lane, thr, g, r);
   }
 

@@ -155,6 +155,14 @@ int cx_threshold_topk(int dev, int gdtype, const void* g, const float* r,
                       int64_t n, float ratio, int default_subsamples,
                       float subsample_factor, float* thr_out, void* stream);
 
+/* The same with scratch (cx_threshold_workspace_bytes, zeroed once, left zeroed): when sampling
+ * is switched off (every element is a sample, e.g. default_subsamples = 2^31 - 128) the CUDA
+ * back end then selects over the whole vector with grid-wide radix passes instead of one CTA. */
+int64_t cx_threshold_workspace_bytes(void);
+int cx_threshold_select(int dev, int gdtype, const void* g, const float* r, int64_t n, float ratio,
+                        int default_subsamples, float subsample_factor, float* thr_out, void* workspace,
+                        int64_t ws_bytes, void* stream);
+
 /* IndexPairs compress_add_update / compress_update / compress
  * (src/compressor.hxx:556-611) fused with the transfer: survivors are
  * stored into every target slot, the residual is updated in the same pass,

@@ -20,7 +20,7 @@
 #include "cx_common.h"
 
 // ---- forward declarations of the two back ends --------------------------------
-int cx_threshold_topk_cuda(int, const void*, const float*, int64_t, float, int, float, float*, void*);
+int cx_threshold_topk_cuda(int, const void*, const float*, int64_t, float, int, float, float*, void*, int64_t, void*);
 int cx_threshold_topk_host(int, const void*, const float*, int64_t, float, int, float, float*);
 int cx_compress_cuda(int, const void*, float*, int64_t, const float*, uint32_t, uint64_t,
                      const CxTargets*, void*, int64_t, CxStats*, uint32_t, void*);
@@ -96,11 +96,19 @@ uint64_t cx_launch_count(void) { return g_launches.load(); }
 void cx_reset_launch_count(void) { g_launches.store(0); }
 int cx_version(void) { return 1; }
 
+int cx_threshold_select(int dev, int gdtype, const void* g, const float* r, int64_t n, float ratio,
+                        int default_subsamples, float subsample_factor, float* thr_out, void* workspace,
+                        int64_t ws_bytes, void* stream) {
+  return dev == CX_DEV_CUDA
+             ? cx_threshold_topk_cuda(gdtype, g, r, n, ratio, default_subsamples, subsample_factor, thr_out,
+                                      workspace, ws_bytes, stream)
+             : cx_threshold_topk_host(gdtype, g, r, n, ratio, default_subsamples, subsample_factor, thr_out);
+}
+
 int cx_threshold_topk(int dev, int gdtype, const void* g, const float* r, int64_t n, float ratio,
                       int default_subsamples, float subsample_factor, float* thr_out, void* stream) {
-  return dev == CX_DEV_CUDA
-             ? cx_threshold_topk_cuda(gdtype, g, r, n, ratio, default_subsamples, subsample_factor, thr_out, stream)
-             : cx_threshold_topk_host(gdtype, g, r, n, ratio, default_subsamples, subsample_factor, thr_out);
+  return cx_threshold_select(dev, gdtype, g, r, n, ratio, default_subsamples, subsample_factor, thr_out, nullptr, 0,
+                             stream);
 }
 
 int cx_compress(int dev, int gdtype, const void* g, float* r, int64_t n, const float* thr,
@@ -207,8 +215,8 @@ namespace {
 int run_one(CxOp& o, uint64_t seq, void* stream) {
   switch (o.kind) {
     case CX_OPK_THRESHOLD:
-      return cx_threshold_topk(o.dev, o.dtype, o.g, o.r, o.n, o.ratio, o.default_subsamples,
-                               o.subsample_factor, o.thr, stream);
+      return cx_threshold_select(o.dev, o.dtype, o.g, o.r, o.n, o.ratio, o.default_subsamples,
+                                 o.subsample_factor, o.thr, o.workspace, o.ws_bytes, stream);
     case CX_OPK_COMPRESS:
       return cx_compress(o.dev, o.dtype, o.g, o.r, o.n, o.thr, o.cap, seq, &o.tg, o.workspace,
                          o.ws_bytes, o.stats, o.src_rank, stream);

@@ -166,7 +166,132 @@ __global__ void __launch_bounds__(kThreads) threshold_kernel(const ThreshParams 
   if (tid == 0) *p.thr_out = __uint_as_float(prefix);
 }
 
+// ---- exact selection over the whole vector, grid-wide ----------------------------------------
+// With sampling switched off (every element is a sample) the single CTA above would walk the
+// vector four times on its own.  Here every radix pass is a grid-wide histogram instead: each
+// CTA replays the digits chosen so far from the global histograms of the earlier passes (256
+// counters each), counts the next digit of the keys that still match into shared memory and
+// adds its counts to the global histogram of this pass.  Four such launches and a one-warp
+// finish read the vector four times at full bandwidth.  The result is the key of rank topk_pos
+// in descending order, the same value the single CTA finds.
+constexpr int kExactThreads = 256;
+
+struct ExactParams {
+  const void* g;
+  const float* r;
+  int64_t n;
+  uint32_t topk_pos;
+  int pass;            // 0..3: digit at shift 24 - 8 * pass; 4: finish
+  uint32_t* hist;      // [4][256], zero before the first pass; the finish zeroes it again
+  float* thr_out;
+  uint32_t vec;        // 16-byte accesses are possible
+};
+
+// One warp: the digit of `hist` (256 bins, walked from the top) that holds rank `rank`, and the
+// rank inside that bin.  All lanes return the same values.
+__device__ __forceinline__ uint32_t pick_digit(const uint32_t* hist, uint32_t& rank, int lane) {
+  uint32_t h[8], gsum = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { h[j] = hist[255 - 8 * lane - j]; gsum += h[j]; }
+  uint32_t incl = gsum;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += t;
+  }
+  const uint32_t before = incl - gsum;
+  uint32_t digit = 0, left = 0;
+  const bool mine = rank >= before && rank < incl;   // exactly one lane (rank < number of keys)
+  if (mine) {
+    uint32_t cum = before;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (rank >= cum && rank < cum + h[j]) { digit = 255 - 8 * lane - j; left = rank - cum; }
+      cum += h[j];
+    }
+  }
+  const uint32_t who = __ffs(__ballot_sync(0xffffffffu, mine)) - 1;
+  digit = __shfl_sync(0xffffffffu, digit, who & 31);
+  rank = __shfl_sync(0xffffffffu, left, who & 31);
+  return digit;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kExactThreads) exact_select_kernel(const ExactParams p) {
+  __shared__ uint32_t s_hist[256];
+  __shared__ uint32_t s_prefix;
+  const int tid = threadIdx.x, lane = tid & 31;
+  s_hist[tid] = 0;
+  if (tid < 32) {      // the decisions of the earlier passes
+    uint32_t prefix = 0, rank = p.topk_pos;
+    for (int q = 0; q < p.pass && q < 4; ++q) prefix |= pick_digit(p.hist + 256 * q, rank, lane) << (24 - 8 * q);
+    if (tid == 0) s_prefix = prefix;
+  }
+  __syncthreads();
+  const uint32_t prefix = s_prefix;
+  if (p.pass >= 4) {   // finish: the key of that rank is the threshold; leave the scratch clean
+    if (blockIdx.x == 0) {
+      if (tid == 0) *p.thr_out = __uint_as_float(prefix);
+      for (int i = tid; i < 4 * 256; i += kExactThreads) p.hist[i] = 0;
+    }
+    return;
+  }
+  const int shift = 24 - 8 * p.pass;
+  const uint32_t prefmask = p.pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+  const T* g = reinterpret_cast<const T*>(p.g);
+  auto count = [&](float x, bool valid) {
+    const uint32_t k = __float_as_uint(fabsf(x));
+    const uint32_t digit = (valid && (k & prefmask) == prefix) ? ((k >> shift) & 255u) : 0xffffffffu;
+    const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+    if (digit != 0xffffffffu && lane == __ffs(peers) - 1) atomicAdd(&s_hist[digit], __popc(peers));
+  };
+  const int64_t gsz = (int64_t)gridDim.x * kExactThreads;
+  const int64_t nv = (p.n + 3) / 4;
+  const int64_t rounds = (nv + gsz - 1) / gsz;      // every lane runs every round: the counting is warp-wide
+  for (int64_t it = 0; it < rounds; ++it) {
+    const int64_t i = (it * gsz + (int64_t)blockIdx.x * kExactThreads + tid) * 4;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (p.vec && i + 3 < p.n) {
+      if (p.r) cx::load4(p.r + i, v);
+      if (g) {
+        float b[4];
+        cx::load4(g + i, b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = v[e] + b[e];
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (i + e < p.n) {
+          if (p.r) v[e] = p.r[i + e];
+          if (g) v[e] = v[e] + cx::Elem<T>::to_f(g[i + e]);
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) count(v[e], i + e < p.n);
+  }
+  __syncthreads();
+  if (s_hist[tid]) atomicAdd(&p.hist[256 * p.pass + tid], s_hist[tid]);
+}
+
+template <typename T>
+int launch_exact(const ExactParams& base, cudaStream_t s) {
+  int grid = cx_sm_count() * 6;
+  const int64_t need = ((base.n + 3) / 4 + kExactThreads - 1) / kExactThreads;
+  if (grid > need) grid = (int)need;
+  for (int pass = 0; pass <= 4; ++pass) {
+    ExactParams p = base;
+    p.pass = pass;
+    exact_select_kernel<T><<<pass < 4 ? grid : 1, kExactThreads, 0, s>>>(p);
+    cx_note_launch();
+  }
+  return cx_check_launch("exact_select_kernel");
+}
+
 }  // namespace
+
+extern "C" int64_t cx_threshold_workspace_bytes(void) { return 4 * 256 * (int64_t)sizeof(uint32_t); }
 
 // Host-side part of the rule, in the reference's float arithmetic.
 // sample count, stride and rank of the estimate (defined with the host back end)
@@ -176,7 +301,7 @@ extern "C" void cx_threshold_plan(int64_t n, float ratio, int default_subsamples
 
 int cx_threshold_topk_cuda(int gdtype, const void* g, const float* r, int64_t n, float ratio,
                            int default_subsamples, float subsample_factor, float* thr_out,
-                           void* stream) {
+                           void* workspace, int64_t ws_bytes, void* stream) {
   if (!g && !r) return cx_set_error("cx_threshold_topk: g and r are both NULL", 0);
   ThreshParams p;
   p.g = g; p.r = r; p.n = n; p.thr_out = thr_out;
@@ -184,6 +309,20 @@ int cx_threshold_topk_cuda(int gdtype, const void* g, const float* r, int64_t n,
                     &p.stepsize, &p.topk_pos);
   if (n <= 0) { p.samples = 0; p.topk_pos = 0; }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (p.use_all && p.topk_pos > 0 && n > kSmemKeys && workspace && ws_bytes >= cx_threshold_workspace_bytes()) {
+    // exact selection over a vector that does not fit one CTA's shared memory: grid-wide passes
+    ExactParams e;
+    e.g = g; e.r = r; e.n = n; e.topk_pos = (uint32_t)p.topk_pos; e.pass = 0;
+    e.hist = reinterpret_cast<uint32_t*>(workspace); e.thr_out = thr_out;
+    const size_t esz = gdtype == CX_F32 ? 4 : 2;
+    e.vec = (!r || (reinterpret_cast<uintptr_t>(r) & 15) == 0) && (!g || (reinterpret_cast<uintptr_t>(g) & (4 * esz - 1)) == 0);
+    switch (gdtype) {
+      case CX_F32: return launch_exact<float>(e, s);
+      case CX_BF16: return launch_exact<__nv_bfloat16>(e, s);
+      case CX_F16: return launch_exact<__half>(e, s);
+      default: return cx_set_error("cx_threshold_topk: unsupported dtype on CUDA", 0);
+    }
+  }
   // a cluster of 8 CTAs gathers large samples (their keys must fit the first CTA's shared memory)
   const unsigned ncta = (p.samples > 2048 && p.samples <= kSmemKeys) ? 8u : 1u;
   cudaLaunchConfig_t cfg;

@@ -181,6 +181,8 @@ class Compressor:
         self.ws_bytes = int(env.lib.cx_workspace_bytes(n))
         self.workspace = env.scratch(self.ws_bytes)
         self.thr = torch.zeros(1, dtype=torch.float32, device=env.device)
+        self.thr_ws_bytes = int(env.lib.cx_threshold_workspace_bytes())    # exact selection: grid-wide histograms
+        self.thr_ws = env.scratch(self.thr_ws_bytes)
         self.stats = env.new_stats()
 
     def set_threshold(self, value: float) -> None:
@@ -196,11 +198,12 @@ class Compressor:
             op = _new_op(env, _lib.OPK_THRESHOLD, gd, n)
             op.g, op.r, op.thr, op.ratio = _ptr(g), _ptr(r), self.thr.data_ptr(), ratio
             op.default_subsamples, op.subsample_factor = int(default_subsamples), float(subsample_factor)
+            op.workspace, op.ws_bytes = self.thr_ws.data_ptr(), self.thr_ws_bytes
             env._rec.append(op)
             return
-        _lib.check(env.lib.cx_threshold_topk(env.dev, gd, _ptr(g), _ptr(r), n, ratio, int(default_subsamples),
-                                             float(subsample_factor), self.thr.data_ptr(),
-                                             _lib.stream_ptr(env.device)), "cx_threshold_topk")
+        _lib.check(env.lib.cx_threshold_select(env.dev, gd, _ptr(g), _ptr(r), n, ratio, int(default_subsamples),
+                                               float(subsample_factor), self.thr.data_ptr(), self.thr_ws.data_ptr(),
+                                               self.thr_ws_bytes, _lib.stream_ptr(env.device)), "cx_threshold_select")
 
     def compress(self, g, r, n: int, cap: int, seq: int, targets: Targets) -> None:
         """r += g; emit |r| > thr into every target; zero what was emitted."""

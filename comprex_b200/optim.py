@@ -244,6 +244,7 @@ class ComprexOptimizer(torch.optim.Optimizer):
         self._v = torch.zeros(n, dtype=torch.float32, device=dev) if rule == "adamw" else None
         self.comprex_allreducers = {}
         self._comm = None
+        self._trace = None
         # with a single bucket there is nothing to overlap with: its last gradient appears when
         # backward ends, and the hooks and the side stream would only add latency
         self.overlap = bool(overlap) and dev.type == "cuda" and len(self._buckets) > 1 and not self._local
@@ -320,6 +321,9 @@ class ComprexOptimizer(torch.optim.Optimizer):
                 p.grad = None
             elif p.grad is not None:
                 p.grad.zero_()
+        if getattr(self, "_trace", None) is not None:
+            self._trace.clear()
+            self._mark(("origin",))             # the step's timeline starts here
 
     # ---- the step ---------------------------------------------------------------------------------
     def _fold(self, b: _Bucket, lr: float, mu: float) -> torch.Tensor:
@@ -365,9 +369,44 @@ class ComprexOptimizer(torch.optim.Optimizer):
             self._comm = torch.cuda.Stream(self._env.device, priority=-1)
         return self._comm
 
+    # ---- per-bucket timeline (CUDA events; for the overlap evidence, off by default) --------------
+    def enable_timeline(self, on: bool = True) -> None:
+        """Record CUDA events around every bucket's send and receive half and at the start of
+        ``step`` (where backward has ended); :meth:`timeline` turns the last step's events into
+        milliseconds.  Costs a few event records per bucket and step."""
+        self._trace = {} if on and self._env.device.type == "cuda" else None
+
+    def _mark(self, key) -> None:
+        if getattr(self, "_trace", None) is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream(self._env.device))
+            self._trace[key] = ev
+
+    def timeline(self) -> dict:
+        """Milliseconds since the first recorded event of the last step: per bucket
+        ``send_start`` (its last gradient exists and the comm stream picks it up), ``send_end``,
+        ``recv_start``, ``recv_end``; ``backward_end`` is the compute stream at the entry of
+        ``step``, ``step_end`` the compute stream after it joined the comm stream."""
+        tr = getattr(self, "_trace", None)
+        if not tr:
+            return {}
+        torch.cuda.synchronize(self._env.device)
+        origin = tr.get(("origin",)) or next(iter(tr.values()))     # zero_grad() marks the start of a step
+        out = {"buckets": [dict(index=i, mbytes=round((b.end - b.start) * 4 / 2 ** 20, 2), kind=b.kind)
+                           for i, b in enumerate(self._buckets)]}
+        for key, ev in tr.items():
+            ms = round(origin.elapsed_time(ev), 3)
+            if len(key) == 2:
+                out["buckets"][key[1]][key[0]] = ms
+            elif key != ("origin",):
+                out[key[0]] = ms
+        return out
+
     def _send(self, b: _Bucket) -> None:
         """First half of a bucket's exchange: fold, then everything that waits for nobody."""
         lr, mu, _ = self._hyper()
+        idx = self._buckets.index(b) if getattr(self, "_trace", None) is not None else -1
+        self._mark(("send_start", idx))
         with nvtx_range("comprex.fold+send"):
             u = self._fold(b, lr, mu)
             if b.kind == "bigring":
@@ -383,6 +422,7 @@ class ComprexOptimizer(torch.optim.Optimizer):
                     b.plan = b.plan[1:]
             else:
                 b.u = u
+        self._mark(("send_end", idx))
         b.sent = True
 
     def _recv(self, b: _Bucket, lr, mu, wd) -> None:
@@ -455,6 +495,7 @@ class ComprexOptimizer(torch.optim.Optimizer):
         first = not self._armed
         self._ensure_allreducers()
         use_side = self.overlap and not first
+        self._mark(("backward_end",))
         if use_side:
             comm = self._comm_stream()
             comm.wait_stream(torch.cuda.current_stream(self._env.device))
@@ -466,11 +507,14 @@ class ComprexOptimizer(torch.optim.Optimizer):
             for b in self._buckets:          # everything that the hooks did not send yet
                 if not b.sent:
                     self._send(b)
-            for b in self._buckets:          # then receive: all peers' payloads are on their way
+            for i, b in enumerate(self._buckets):   # then receive: all peers' payloads are on their way
+                self._mark(("recv_start", i))
                 self._recv(b, lr, mu, wd)
+                self._mark(("recv_end", i))
                 b.sent, b.ready = False, 0
         if use_side:
             torch.cuda.current_stream(self._env.device).wait_stream(comm)
+        self._mark(("step_end",))
         self._env.maybe_check()
         return loss
 

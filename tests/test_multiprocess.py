@@ -28,16 +28,18 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _entry(rank, world, port, backend, fn_name, q, args):
+def _entry(rank, world, port, backend, fn_name, q, args, env):
     try:
         sys.path.insert(0, ROOT)
         sys.path.insert(0, os.path.join(ROOT, "tests"))
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
                           WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+        os.environ.update(env or {})
         if backend == "nccl":
             os.environ["NCCL_NVLS_ENABLE"] = "0"
             torch.cuda.set_device(rank)
-        dist.init_process_group(backend, rank=rank, world_size=world)
+        import datetime
+        dist.init_process_group(backend, rank=rank, world_size=world, timeout=datetime.timedelta(seconds=180))
         if ":" in fn_name:   # "module:function" for scenarios that live in another test file
             import importlib
             mod, name = fn_name.split(":")
@@ -55,13 +57,19 @@ def _entry(rank, world, port, backend, fn_name, q, args):
             pass
 
 
-def run_ranks(world, fn_name, backend="gloo", args=(), timeout=240):
+def gpu_world(default=2):
+    """Ranks of the multi-GPU tests: COMPREX_TEST_RANKS (default 2), at most one per device."""
+    have = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    return max(2, min(have, int(os.environ.get("COMPREX_TEST_RANKS", default))))
+
+
+def run_ranks(world, fn_name, backend="gloo", args=(), timeout=240, env=None):
     """Run a scenario on ``world`` spawned ranks.  The first rank that reports an error ends the
     wait (its peers may be blocked in a collective with it) and its traceback is the failure."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, backend, fn_name, q, args)) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(r, world, port, backend, fn_name, q, args, env)) for r in range(world)]
     for p in procs:
         p.start()
     results, failure = {}, None
@@ -393,28 +401,114 @@ def _gpus():
 @pytest.mark.gpu
 @pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
 def test_config1_two_gpus():
-    run_ranks(2, "scenario_config1", backend="nccl", args=(1 << 20, 20, 0.01))
+    run_ranks(gpu_world(), "scenario_config1", backend="nccl", args=(1 << 20, 20, 0.01))
 
 
 @pytest.mark.gpu
 @pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
 def test_allreduce_variants_gpus():
-    run_ranks(min(_gpus(), 4), "scenario_allreduce_variants", backend="nccl")
+    run_ranks(gpu_world(min(_gpus(), 4)), "scenario_allreduce_variants", backend="nccl")
 
 
 @pytest.mark.gpu
 @pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
 def test_allreduce_ops_gpus():
-    assert all(run_ranks(2, "scenario_allreduce_ops", backend="nccl"))
+    assert all(run_ranks(gpu_world(), "scenario_allreduce_ops", backend="nccl"))
 
 
 @pytest.mark.gpu
 @pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
 def test_replay_and_two_shot_gpus():
-    assert all(run_ranks(min(_gpus(), 4), "scenario_replay_and_two_shot", backend="nccl"))
+    assert all(run_ranks(gpu_world(min(_gpus(), 4)), "scenario_replay_and_two_shot", backend="nccl"))
 
 
 @pytest.mark.gpu
 @pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
 def test_missing_sender_times_out_gpus():
-    assert run_ranks(2, "scenario_missing_sender", backend="nccl")[0] is True
+    # a failure scenario: plain peer stores only, no multicast-bound memory
+    assert run_ranks(2, "scenario_missing_sender", backend="nccl", env={"COMPREX_NVLS": "0"})[0] is True
+
+
+def scenario_nvls_paths(rank, world, device):
+    """The paths through the NVSwitch's multicast object against the plain peer-store paths.
+    Dense: in-switch reduction (one-shot, two-shot, in place on a heap vector) against the fp32
+    sum of all ranks' vectors, identical bits on every rank.  Compressed: payloads stored once with
+    multimem.st give bit for bit the results of one store per peer.  Every rank leaves through the
+    same barriers; nothing here times out on purpose."""
+    import comprex_b200 as cx
+    os.environ["COMPREX_MM_MIN_RANKS"], os.environ["COMPREX_MM_MIN_BYTES"] = "2", "0"
+    env = cx.GaspiEnvironment(32 << 20, device=device, timeout_ms=5000)
+    if not env.nvls:
+        env.close()
+        return "no multicast"
+    os.environ["COMPREX_NVLS"] = "0"
+    plain = cx.GaspiEnvironment(32 << 20, device=device, timeout_ms=5000)
+    os.environ["COMPREX_NVLS"] = "1"
+    assert not plain.nvls
+    for dt in (torch.float32, torch.bfloat16, torch.float16):
+        for n in (1, 7, 1000, 70001, (1 << 20) + 3):
+            for cls in (cx.BigRingAllreduce, cx.RingAllreduce):
+                torch.manual_seed(100 + rank + n)
+                x = torch.randn(n, device=device).to(dt)
+                parts = [torch.empty_like(x) for _ in range(world)]
+                dist.all_gather(parts, x)
+                ref = sum(t.float() for t in parts)
+                mark = env.heap_mark()
+                ar = cls(env)
+                ar.setup_connections(n, 1, dtype=dt)
+                assert ar.first_phase_waits          # the single-kernel path is the one under test
+                ar.result_scale = 0.5
+                for _ in range(3):                   # parity of the staging buffers, flag reuse
+                    y = x.clone()
+                    ar.apply(y)
+                env.flush()
+                tol = 1e-5 if dt == torch.float32 else 2e-2
+                assert float((y.float() - 0.5 * ref).abs().max()) <= tol * max(float(ref.abs().max()), 1.0), (cls, dt, n)
+                got = [torch.empty_like(y) for _ in range(world)]
+                dist.all_gather(got, y)
+                assert all(torch.equal(got[0], t) for t in got), "ranks disagree"
+                del ar
+                env.heap_release(mark)
+    n = 1 << 20                                      # in place on a vector that lives in the heap
+    h = env.empty(n)
+    torch.manual_seed(5 + rank)
+    x = torch.randn(n, device=device)
+    h.copy_(x)
+    parts = [torch.empty_like(x) for _ in range(world)]
+    dist.all_gather(parts, x)
+    ar = cx.RingAllreduce(env)
+    ar.setup_connections(n, 1)
+    ar.apply(h)
+    env.flush()
+    assert float((h - sum(parts)).abs().max()) <= 1e-5 * float(sum(parts).abs().max())
+    for cls, kw in ((cx.Comprex_BigRingAllreduce, dict(consistent=True)), (cx.Comprex_RingAllreduce, dict(consistent=True)),
+                    (cx.Comprex_AllToOneAllreduce, {})):
+        outs = {}
+        for name, e in (("multicast", env), ("plain", plain)):
+            ar = cls(e)
+            if cls is cx.Comprex_AllToOneAllreduce:
+                ar.setup_connections(n, 1, 0, 0.02, 0.1)
+            else:
+                ar.setup_connections(n, 1, 0.02, 0.1, **kw)
+            torch.manual_seed(77 + rank)
+            x = torch.randn(n, device=device)
+            res = []
+            for _ in range(3):
+                y = x.clone()
+                ar.apply(y)
+                res.append(y)
+            e.flush()
+            outs[name] = res
+        assert all(torch.equal(a, b) for a, b in zip(outs["multicast"], outs["plain"])), cls.__name__
+    env.barrier()
+    plain.barrier()
+    plain.close()
+    env.close()
+    return "ok"
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_switch_paths_match_plain_paths_gpus():
+    out = run_ranks(gpu_world(), "scenario_nvls_paths", backend="nccl")
+    assert all(o in ("ok", "no multicast") for o in out)

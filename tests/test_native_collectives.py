@@ -13,7 +13,7 @@ import comprex_b200 as cx
 from comprex_b200 import _lib, build
 from comprex_b200.native import NativeAllreduce
 
-from test_multiprocess import run_ranks
+from test_multiprocess import gpu_world, run_ranks
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REF = os.environ.get("COMPREX_REFERENCE")
@@ -122,4 +122,4 @@ def test_native_schedules_match_python_cpu(world):
 @pytest.mark.gpu
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_native_schedules_match_python_gpus():
-    assert all(run_ranks(2, "test_native_collectives:scenario_native_matches_python", backend="nccl"))
+    assert all(run_ranks(gpu_world(), "test_native_collectives:scenario_native_matches_python", backend="nccl"))

@@ -12,7 +12,7 @@ import comprex_b200 as cx
 from comprex_b200.models.lenet import LeNet5
 from comprex_b200.optim import ComprexOptimizer
 
-from test_multiprocess import run_ranks
+from test_multiprocess import gpu_world, run_ranks
 
 
 def _const_grad_model(device, seed=0):
@@ -576,13 +576,21 @@ def _gpus():
 @pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("overlap", [False, True])
 def test_optimizer_replicas_stay_identical_gpus(overlap):
-    run_ranks(2, "test_optimizer:scenario_optimizer_ranks", backend="nccl", args=(overlap,))
+    run_ranks(gpu_world(), "test_optimizer:scenario_optimizer_ranks", backend="nccl", args=(overlap,))
 
 
 @pytest.mark.gpu
 @pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
 def test_ddp_hook_gpus():
-    run_ranks(2, "test_optimizer:scenario_ddp_hook", backend="nccl")
+    run_ranks(gpu_world(), "test_optimizer:scenario_ddp_hook", backend="nccl")
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("kind", ["comprex_ring", "auto", "ring"])
+def test_every_collective_runs_bucketed_gpus(kind):
+    out = run_ranks(gpu_world(), "test_optimizer:scenario_optimizer_kinds", backend="nccl", args=(kind, True, True))
+    assert all(last < first for first, last in out)
 
 
 @pytest.mark.gpu
