@@ -27,9 +27,9 @@ The default arm (``ours``) also runs that dense arm afterwards in the same invoc
 same batches, for the same steps and warm-up: the reference publishes no number, so
 ``vs_baseline`` is ``value`` divided by the dense arm's value and ``baseline`` holds the dense
 arm's figures (``--skip-baseline`` leaves both out).  With N > 1 the line also carries an
-``allreduce`` block: compressed BigRing and Ring of one 2^24-element fp32 vector at top-k 1 %
-(achieved sent fraction stated) next to ``torch.distributed.all_reduce`` of the same tensor,
-CUDA-event microseconds, max over ranks.
+``allreduce`` block: compressed BigRing, compressed Ring and the automatic choice for one
+2^24-element fp32 vector at top-k 1 % (achieved sent fraction stated) next to
+``torch.distributed.all_reduce`` of the same tensor, CUDA-event microseconds, max over ranks.
 """
 import argparse
 import json
@@ -338,7 +338,8 @@ def allreduce_block(rank, world, local, log2n=24, ratio=0.01, reps=10, warmup=3)
              "nccl_all_reduce_us": round(time_op(lambda: dist.all_reduce(work)), 2)}
     sf = max(4.0 * ratio, 2e-3)
     for name, cls, kw in (("comprex_bigring", cx.Comprex_BigRingAllreduce, {"consistent": True}),
-                          ("comprex_ring", cx.Comprex_RingAllreduce, {})):
+                          ("comprex_ring", cx.Comprex_RingAllreduce, {"consistent": True, "chunk_align": 4}),
+                          ("auto", cx.AutoAllreduce, {})):
         mark = env.heap_mark()
         ar = cls(env)
         ar.setup_connections(n, 1, ratio, sf, **kw)
@@ -346,8 +347,10 @@ def allreduce_block(rank, world, local, log2n=24, ratio=0.01, reps=10, warmup=3)
         # the input is not reset between repetitions: the residual carries what was not sent, as in training
         us = time_op(lambda: ar.apply(buf))
         st = ar.stats()
-        block[name] = {"us": round(us, 2), "sent_fraction": round(st["nnz"] / max(st["n"], 1), 5),
+        block[name] = {"us": round(us, 2), "sent_fraction": round(st["nnz"] / max(st["n"], 1), 5) if st else None,
                        "speedup_vs_nccl": round(block["nccl_all_reduce_us"] / us, 2)}
+        if name == "auto":
+            block[name]["chosen"] = ar.choice
         del ar, buf
         env.heap_release(mark)
     env.barrier()

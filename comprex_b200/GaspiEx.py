@@ -12,6 +12,14 @@ calls only record the peer, the tag is kept for interface parity.
 
 Vectors may be ``torch`` tensors on the environment's device or NumPy arrays
 (copied to the device and, for in-place calls, back).
+
+Flow control: the receive slot is double-buffered by the parity of the message
+number and nothing is acknowledged, so a sender may be at most two writes ahead
+of its receiver's reads; a third write overwrites a slot that may not have been
+read yet.  Exchanges in which both sides send and receive every step (the
+allreduce schedules) keep within that by construction; a one-directional stream
+of writes has to be paced by the caller (a barrier, or a message back), as in the
+reference, whose transport has no flow control either (src/gaspiEx.tpp:70-88).
 """
 from __future__ import annotations
 

@@ -130,7 +130,7 @@ template <typename TO>
 __global__ void __launch_bounds__(kThreads) apply_sparse_kernel(const ApplyParams p) {
   __shared__ uint32_t s_nnz[CX_MAX_PEERS];
   __shared__ float s_acc[kWarps][CX_SUBTILE];
-  if (!wait_sources(p, s_nnz)) return;
+  if (!wait_sources(p, s_nnz)) { cx::pdl_wait(); return; }
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const uint32_t nwarps = gridDim.x * kWarps;
@@ -226,6 +226,7 @@ __global__ void __launch_bounds__(kThreads) apply_sparse_kernel(const ApplyParam
     }
   }
   if (bad && p.status) atomicOr(p.status, bad);
+  cx::pdl_wait();   // launched early behind its sender: do not complete before that grid has
 }
 
 // The update rule on four elements held in registers (g = scale * sum of the payloads).
@@ -468,7 +469,7 @@ __global__ void __launch_bounds__(kBulkMaxThreads, 1) apply_dense_bulk_kernel(co
   constexpr int NARR = StateArrays<OP>::n;
   constexpr uint32_t kTileBytes = CX_SUBTILE * sizeof(float);
   constexpr uint32_t kWarpBytes = (1 + STAGES * NARR) * kTileBytes;
-  if (!wait_sources(p, s_nnz)) return;
+  if (!wait_sources(p, s_nnz)) { cx::pdl_wait(); return; }
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const uint32_t nw = blockDim.x >> 5;
@@ -565,7 +566,7 @@ template <int OP, typename TO>
 __global__ void __launch_bounds__(kThreads) apply_dense_kernel(const ApplyParams p) {
   __shared__ uint32_t s_nnz[CX_MAX_PEERS];
   __shared__ __align__(16) float s_acc[kWarps][CX_SUBTILE];
-  if (!wait_sources(p, s_nnz)) return;
+  if (!wait_sources(p, s_nnz)) { cx::pdl_wait(); return; }
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const uint32_t nwarps = gridDim.x * kWarps;
@@ -586,6 +587,7 @@ __global__ void __launch_bounds__(kThreads) apply_dense_kernel(const ApplyParams
     __syncwarp();
   }
   if (bad && p.status) atomicOr(p.status, bad);
+  cx::pdl_wait();   // launched early behind its sender: do not complete before that grid has
 }
 
 // ---- dense update: the averaged gradient is a plain vector -------------------------------
@@ -756,11 +758,12 @@ int launch_apply(const ApplyParams& p, int grid, cudaStream_t s) {
     if (op == CX_OP_MOMENTUM) return launch_bulk<CX_OP_MOMENTUM, TO>(p, s);
     if (op == CX_OP_ADAMW) return launch_bulk<CX_OP_ADAMW, TO>(p, s);
   }
-  if (sparse) apply_sparse_kernel<TO><<<grid, kThreads, 0, s>>>(p);
-  else if (op == CX_OP_SET) apply_dense_kernel<CX_OP_SET, TO><<<grid, kThreads, 0, s>>>(p);
-  else if (op == CX_OP_SGD) apply_dense_kernel<CX_OP_SGD, TO><<<grid, kThreads, 0, s>>>(p);
-  else if (op == CX_OP_MOMENTUM) apply_dense_kernel<CX_OP_MOMENTUM, TO><<<grid, kThreads, 0, s>>>(p);
-  else if (op == CX_OP_ADAMW) apply_dense_kernel<CX_OP_ADAMW, TO><<<grid, kThreads, 0, s>>>(p);
+  const bool cap = p.seq_cell != nullptr;
+  if (sparse) cx_launch_pdl(apply_sparse_kernel<TO>, grid, kThreads, 0, s, p, cap);
+  else if (op == CX_OP_SET) cx_launch_pdl(apply_dense_kernel<CX_OP_SET, TO>, grid, kThreads, 0, s, p, cap);
+  else if (op == CX_OP_SGD) cx_launch_pdl(apply_dense_kernel<CX_OP_SGD, TO>, grid, kThreads, 0, s, p, cap);
+  else if (op == CX_OP_MOMENTUM) cx_launch_pdl(apply_dense_kernel<CX_OP_MOMENTUM, TO>, grid, kThreads, 0, s, p, cap);
+  else if (op == CX_OP_ADAMW) cx_launch_pdl(apply_dense_kernel<CX_OP_ADAMW, TO>, grid, kThreads, 0, s, p, cap);
   else return cx_set_error("cx_apply: unknown op", 0);
   return 0;
 }

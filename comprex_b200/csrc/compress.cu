@@ -9,8 +9,7 @@
 //
 // Work is warp-granular and free of block-wide barriers: a warp owns one
 // 1024-element sub-tile at a time, loads it with 16-byte accesses (32
-// elements per lane, all loads in flight together, the next sub-tile already
-// on its way into L2), ranks the survivors with one warp scan, reserves room
+// elements per lane, all loads in flight together), ranks the survivors with one warp scan, reserves room
 // for them in the pair list with ONE atomicAdd on a counter in this GPU's
 // memory, and stores them through a small shared staging buffer as coalesced
 // 8-byte (index, value) pairs straight into the receive
@@ -37,11 +36,15 @@
 
 namespace {
 
+// Two CTAs (16 warps) per SM: each lane keeps a whole sub-tile share of 32 values in registers
+// with all its loads in flight, which needs ~100 registers; squeezing the kernel into three or
+// more CTAs per SM makes it spill and measured slower at every size (2^24 elements, 1 %: 55 us
+// with two, 69 us with three), and so did an L2 prefetch of the warp's next sub-tile.
 #ifndef CX_COMPRESS_MIN_BLOCKS
-#define CX_COMPRESS_MIN_BLOCKS 3  // CTAs per SM the register budget is tuned for
+#define CX_COMPRESS_MIN_BLOCKS 2
 #endif
 #ifndef CX_COMPRESS_PREFETCH
-#define CX_COMPRESS_PREFETCH 1    // L2 prefetch of the warp's next sub-tile
+#define CX_COMPRESS_PREFETCH 0
 #endif
 
 constexpr int kThreads = 256;
@@ -319,7 +322,7 @@ compress_kernel(const __grid_constant__ CompressParams p) {
       }
     }
   }
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  cx::pdl_wait();
   const float thr = *p.thr;
   CxPair* stage = s_stage[warp];
   const uint32_t nwarps = gridDim.x * kWarps;
@@ -340,6 +343,8 @@ compress_kernel(const __grid_constant__ CompressParams p) {
     else compress_subtile_edge<T, HAS_G, HAS_R, MC>(p, sub, lane, thr, g, r);
   }
 
+  // the receive kernel queued behind this one may become resident now: it polls its flags
+  cx::pdl_trigger();
   // ---- completion: the CTA that arrives last publishes -------------------------------
   __threadfence_system();
   __syncthreads();
@@ -403,30 +408,9 @@ __global__ void compress_empty_kernel(const CompressParams p) {
   }
 }
 
-// The kernel is launched so that it may overlap the tail of the kernel in front of it on the
-// stream (programmatic dependent launch); it synchronises with that kernel itself, see above.
-// Not inside a graph capture, and not with COMPREX_PDL=0.
 template <typename K>
 void launch_pdl(K kernel, const CompressParams& p, int grid, cudaStream_t s) {
-  static const bool off = [] { const char* e = getenv("COMPREX_PDL"); return e && e[0] == '0'; }();
-  if (off || p.seq_cell) {
-    kernel<<<grid, kThreads, 0, s>>>(p);
-    return;
-  }
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kernel, p) != cudaSuccess) {
-    cudaGetLastError();                       // e.g. a driver without the feature: plain launch
-    kernel<<<grid, kThreads, 0, s>>>(p);
-  }
+  cx_launch_pdl(kernel, grid, kThreads, 0, s, p, p.seq_cell != nullptr);
 }
 
 template <typename T, bool MC>

@@ -131,6 +131,40 @@ __device__ __forceinline__ uint64_t seq_of(const uint64_t* cell, uint64_t by_val
 // the cell for launches issued by this thread right now (NULL outside a graph capture)
 const uint64_t* cx_seq_cell();
 
+// ---- programmatic dependent launch ------------------------------------------------------------
+// A kernel launched with cx_launch_pdl may become resident while the kernel in front of it on the
+// stream is still finishing (as soon as all of that kernel's CTAs have called cx::pdl_trigger or
+// exited).  The late kernel synchronises itself: cx::pdl_wait blocks until the earlier grid has
+// completed and its writes are visible.  Used for threshold -> compress (the compress grid is
+// resident and its first loads are on their way when the threshold lands) and for
+// compress -> apply / send -> reduce (the receive kernel is already polling its flags when the
+// sender publishes).  Inside a graph capture, and with COMPREX_PDL=0, launches are plain.
+namespace cx {
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+}  // namespace cx
+
+bool cx_pdl_enabled();   // COMPREX_PDL != 0 (read once)
+
+template <typename K, typename P>
+void cx_launch_pdl(K kernel, int grid, int threads, size_t smem, cudaStream_t s, const P& params, bool capturing) {
+  if (!capturing && cx_pdl_enabled()) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3((unsigned)threads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kernel, params) == cudaSuccess) return;
+    cudaGetLastError();                        // e.g. a driver without the feature: plain launch
+  }
+  kernel<<<grid, threads, smem, s>>>(params);
+}
+
 // host-side launch bookkeeping shared by the .cu files
 void cx_note_launch();
 int cx_set_error(const char* where, int cuda_err);

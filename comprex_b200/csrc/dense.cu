@@ -160,6 +160,7 @@ __global__ void __launch_bounds__(kThreads) dense_send_kernel(const SendParams p
       }
     }
   }
+  cx::pdl_trigger();   // the reducing kernel queued behind this one may become resident and poll
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) s_last = (atomicAdd(&p.ctr->done, 1u) == gridDim.x - 1) ? 1u : 0u;
@@ -247,8 +248,11 @@ __device__ __forceinline__ float ldcg1<__half>(const __half* p) {
   return __half2float(__ushort_as_half(u));
 }
 
+// The arrival counter of a pushing reduce is pad[2] of the counter block, not `done`: the kernel
+// may be resident while the sending kernel in front of it (which counts in `done`, often in the
+// same block) has not finished its own count yet.  pad[0] is the failure mark.
 template <typename T>
-__global__ void __launch_bounds__(kThreads) dense_reduce_kernel(const ReduceParams p) {
+__device__ __forceinline__ void dense_reduce_body(const ReduceParams& p) {
   __shared__ uint32_t s_last;
   if (!wait_dense(p.src, p.timeout_ns, p.status, p.dtype, p.seq_cell)) {
     // The verdict is per CTA, the bookkeeping is per grid: a CTA that gave up still arrives at
@@ -258,10 +262,10 @@ __global__ void __launch_bounds__(kThreads) dense_reduce_kernel(const ReducePara
     if (threadIdx.x == 0) {
       atomicOr(&p.ctr->pad[0], 1u);
       __threadfence();
-      s_last = (atomicAdd(&p.ctr->done, 1u) == gridDim.x - 1) ? 1u : 0u;
+      s_last = (atomicAdd(&p.ctr->pad[2], 1u) == gridDim.x - 1) ? 1u : 0u;
     }
     __syncthreads();
-    if (s_last && threadIdx.x == 0) { p.ctr->pad[0] = 0; p.ctr->done = 0; }
+    if (s_last && threadIdx.x == 0) { p.ctr->pad[0] = 0; p.ctr->pad[2] = 0; }
     return;
   }
   T* out = reinterpret_cast<T*>(p.out);
@@ -346,7 +350,7 @@ __global__ void __launch_bounds__(kThreads) dense_reduce_kernel(const ReducePara
   if (!p.has_push) return;
   __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0) s_last = (atomicAdd(&p.ctr->done, 1u) == gridDim.x - 1) ? 1u : 0u;
+  if (threadIdx.x == 0) s_last = (atomicAdd(&p.ctr->pad[2], 1u) == gridDim.x - 1) ? 1u : 0u;
   __syncthreads();
   if (!s_last) return;
   __threadfence();
@@ -354,7 +358,13 @@ __global__ void __launch_bounds__(kThreads) dense_reduce_kernel(const ReducePara
   if (!failed && (int)threadIdx.x < p.push.count)
     publish_dense<T>(p.push, threadIdx.x, p.n, cx::seq_of(p.seq_cell, p.push_seq), p.src_rank, p.dtype);
   __syncthreads();
-  if (threadIdx.x == 0) { p.ctr->pad[0] = 0; p.ctr->done = 0; }
+  if (threadIdx.x == 0) { p.ctr->pad[0] = 0; p.ctr->pad[2] = 0; }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) dense_reduce_kernel(const ReduceParams p) {
+  dense_reduce_body<T>(p);
+  cx::pdl_wait();   // launched early behind the sending kernel: do not complete before that grid has
 }
 
 // ---- elementwise helpers ----------------------------------------------------
@@ -459,9 +469,9 @@ int cx_dense_reduce_cuda(int dtype, void* out, const void* own, int64_t n, const
   const int grid = grid_for(work, 6);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   switch (dtype) {
-    case CX_F32: dense_reduce_kernel<float><<<grid, kThreads, 0, s>>>(p); break;
-    case CX_BF16: dense_reduce_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(p); break;
-    case CX_F16: dense_reduce_kernel<__half><<<grid, kThreads, 0, s>>>(p); break;
+    case CX_F32: cx_launch_pdl(dense_reduce_kernel<float>, grid, kThreads, 0, s, p, p.seq_cell != nullptr); break;
+    case CX_BF16: cx_launch_pdl(dense_reduce_kernel<__nv_bfloat16>, grid, kThreads, 0, s, p, p.seq_cell != nullptr); break;
+    case CX_F16: cx_launch_pdl(dense_reduce_kernel<__half>, grid, kThreads, 0, s, p, p.seq_cell != nullptr); break;
     default: return cx_set_error("cx_dense_reduce: unsupported dtype on CUDA", 0);
   }
   cx_note_launch();

@@ -77,6 +77,10 @@ int cx_check_launch(const char* where) {
   const cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : cx_set_error(where, (int)e);
 }
+bool cx_pdl_enabled() {
+  static const bool on = [] { const char* e = getenv("COMPREX_PDL"); return !(e && e[0] == '0'); }();
+  return on;
+}
 int cx_sm_count() {
   static int sms[64] = {0};
   int dev = 0;

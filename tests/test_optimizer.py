@@ -260,11 +260,16 @@ def scenario_optimizer_kinds(rank, world, device, kind, aggregate_blob, overlap)
         g = torch.Generator().manual_seed(1000 * rank + i)
         x = torch.rand(32, 1, 28, 28, generator=g).to(device)
         y = (x.mean(dim=(1, 2, 3)) * 20).long().clamp(0, 9).to(device)
-        for model, opt in arms:
-            opt.zero_grad()
-            loss = torch.nn.functional.cross_entropy(model(x), y)
-            loss.backward()
-            opt.step()
+        model, opt = arms[0]
+        opt.zero_grad()
+        loss = torch.nn.functional.cross_entropy(model(x), y)
+        loss.backward()
+        if len(arms) == 2:      # the second arm gets the very same gradients (GPU convolutions are not
+            arms[1][1].zero_grad()   # bit-reproducible from one backward pass to the next)
+            for p0, p1 in zip(model.parameters(), arms[1][0].parameters()):
+                p1.grad = p0.grad.clone()
+        for _, o in arms:
+            o.step()
         first = first if first is not None else float(loss)
         last = float(loss)
         env.flush()
