@@ -21,7 +21,8 @@ timed region.
 
 ``--impl reference`` reports why the reference cannot run here.  ``--impl dense`` runs the
 comparison arm on the same model and data: stock DistributedDataParallel (dense NCCL allreduce)
-with the stock torch optimizer.
+with the stock torch optimizer; ``--impl hook`` the same with this package's compressed DDP
+communication hook in place of the NCCL allreduce.
 
 The default arm (``ours``) also runs that dense arm afterwards in the same invocation, on the
 same batches, for the same steps and warm-up: the reference publishes no number, so
@@ -53,7 +54,7 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "dense"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "dense", "hook"])
     ap.add_argument("--model", default="resnet50", choices=["resnet50", "gpt2", "lenet"])
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch (default: the named config)")
     ap.add_argument("--ratio", type=float, default=None)
@@ -182,7 +183,7 @@ def run_arm(args, impl, rank, world, local):
     broadcast_parameters(model, env, 0)
     # slots sized for 2x the expected survivors (what does not fit stays in the residual)
     size_factor = max(4.0 * ratio, 1e-3) + 1e-4
-    dense = impl == "dense"
+    dense = impl in ("dense", "hook")
     net = model
     if dense:
         # comparison arm: stock DistributedDataParallel (dense NCCL allreduce, 25 MB buckets) and
@@ -195,6 +196,11 @@ def run_arm(args, impl, rank, world, local):
             opt = torch.optim.SGD(model.parameters(), lr=opt_kw["lr"], momentum=opt_kw.get("momentum", 0.0))
         if world > 1:
             net = DDP(model, device_ids=[local], bucket_cap_mb=args.bucket_mb, gradient_as_bucket_view=True)
+            if impl == "hook":
+                # stock DDP and optimizer, the gradient buckets exchanged by this package's DDP hook
+                from comprex_b200.ddp_hook import ComprexHookState, comprex_hook
+                hook_state = ComprexHookState(env, compression_ratio=ratio)
+                net.register_comm_hook(hook_state, comprex_hook)
     else:
         opt = ComprexOptimizer(model.parameters(), env, compression_ratio=ratio, size_factor=size_factor,
                                bucket_cap_mb=args.bucket_mb, overlap=not args.no_overlap,
@@ -287,11 +293,13 @@ def run_arm(args, impl, rank, world, local):
     cfg.update({"parallelism": f"dp{world}", "per_gpu_batch": batch, "params": nparams,
                 "compression_ratio": None if dense else ratio, "bucket_mb": args.bucket_mb,
                 "overlap": not args.no_overlap,
-                "allreduce": ("dense NCCL allreduce (DistributedDataParallel), stock torch optimizer" if dense else
+                "allreduce": ("DistributedDataParallel with the compressed communication hook, stock torch optimizer"
+                              if impl == "hook" else
+                              "dense NCCL allreduce (DistributedDataParallel), stock torch optimizer" if dense else
                               getattr(opt, "describe", lambda: args.allreduce)()),
                 "cache": "inputs_larger_than_L2 (activations + weights per step exceed 126 MB)",
                 "first_bucket_nnz": stats.get("nnz"), "first_bucket_n": stats.get("n"), "final_loss": final_loss})
-    out = {"impl": "dense_nccl_ddp" if dense else "ours", "value": round(batch * world * args.steps / (ms / 1e3), 2),
+    out = {"impl": "ddp_comprex_hook" if impl == "hook" else "dense_nccl_ddp" if dense else "ours", "value": round(batch * world * args.steps / (ms / 1e3), 2),
            "ms_per_step": round(ms / args.steps, 3), "warm": warm, "config": cfg, "clocks": clocks, "e2e": e2e,
            "gpu_launches": int(launches), "final_loss": final_loss, "dtype": "fp32" if args.model == "lenet" else "bf16"}
     del opt, net, model, dev_batches

@@ -116,6 +116,7 @@ def main():
     ap.add_argument("--max-log2-onetoall", type=int, default=26,
                     help="largest size for the schedules that hold P full-size slots (dense BigRing, AllToOne)")
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--heap-gb", type=float, default=16.0, help="upper bound of the first heap segment")
     ap.add_argument("--no-p2p", action="store_true", help="skip the peer-store bandwidth measurement")
     ap.add_argument("--exact-control", action="store_true",
                     help="also run every compressed cell with the exact top-k threshold")
@@ -129,7 +130,11 @@ def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
-    env = cx.GaspiEnvironment(256 << 20, device=dev)
+    # one heap segment that holds the largest cell (2 P slots of 8 B x 0.2 n pairs for the compressed
+    # BigRing at 10 %): cells then reuse it instead of mapping fresh peer / multicast memory each time
+    nmax = 1 << max(args.log2_sizes)
+    heap = int(min(args.heap_gb * (1 << 30), max(256 << 20, 2 * world * 1.7 * nmax + 3 * 4 * nmax)))
+    env = cx.GaspiEnvironment(heap, device=dev)
     flush = None if args.no_flush else torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
     peak, how = hbm_gbs()
     rows = []

@@ -104,6 +104,7 @@ def _declare(lib) -> None:
         "cx_compress": (i32, [i32, i32, vp, vp, i64, vp, u32, u64, P(Targets), vp, i64, vp, u32, vp]),
         "cx_apply": (i32, [i32, P(Sources), i64, P(ApplyArgs), vp, u64, vp]),
         "cx_update_dense": (i32, [i32, vp, i64, P(ApplyArgs), vp]),
+        "cx_barrier": (i32, [i32, i32, i32, P(C.c_void_p), u64, vp, u64, vp]),
         "cx_mm_flag_bytes": (i64, []),
         "cx_mm_counter_bytes": (i64, []),
         "cx_mm_allreduce": (i32, [i32, vp, vp, vp, vp, i64, i64, i32, i32, C.c_float, i32, i64, u64,

@@ -356,8 +356,12 @@ class BigRingAllreduce(_AllreduceBase):
     the same bytes) the call runs the reduce-scatter + allgather schedule of
     ``RingAllreduce``: 2 (P-1)/P n elements, every rank ends with the same bits."""
 
-    def setup_connections(self, size, tag=0, dtype=torch.float32, two_shot_bytes=None):
+    def setup_connections(self, size, tag=0, dtype=torch.float32, two_shot_bytes=None, ordered=False):
+        """``ordered=True``: the one-shot form adds the vectors in rank order on every rank (the
+        reference adds them in the order the ring delivers them, which differs from rank to rank
+        in the last bits): all ranks then hold identical bits, like with the other schedules."""
         self._setup_common(size, dtype)
+        self.ordered = bool(ordered)
         env, nb = self._env, size * torch.empty(0, dtype=dtype).element_size()
         if two_shot_bytes is None:
             two_shot_bytes = int(os.environ.get("COMPREX_TWO_SHOT_BYTES", 1 << 20))
@@ -387,6 +391,8 @@ class BigRingAllreduce(_AllreduceBase):
         self._step += 1
         seq, par = self._step, self._step & 1
         arrival = [(me - k) % nr for k in range(1, nr)]  # the order the ring delivers in
+        if self.ordered:
+            arrival = [r for r in range(nr) if r != me]   # rank order, the own vector at position `me`
 
         def send():
             if nr > 1:
@@ -398,6 +404,7 @@ class BigRingAllreduce(_AllreduceBase):
             if nr > 1:
                 src = self._cached_sources(("src", par), lambda: [self._slots[j][par].endpoint(env) for j in arrival],
                                            seq)
+                src.pad = me if self.ordered else 0
                 P.dense_reduce(env, t, t, self.size, src, self._status, scale=self.result_scale)
         return [send, reduce]
 
@@ -1042,7 +1049,7 @@ class AutoAllreduce(_AllreduceBase):
         self.size, self.dtype = int(size), dtype
         if self.choice == "bigring":
             self.impl = BigRingAllreduce(self.gaspi_env)
-            self.impl.setup_connections(size, tag, dtype=dtype)
+            self.impl.setup_connections(size, tag, dtype=dtype, ordered=consistent)
         elif self.choice == "comprex_bigring":
             self.impl = Comprex_BigRingAllreduce(self.gaspi_env)
             self.impl.setup_connections(size, tag, compression_ratio, size_factor, consistent=consistent)

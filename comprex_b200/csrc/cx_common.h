@@ -93,7 +93,7 @@ typedef struct CxTargets {
 
 typedef struct CxSources {
   int32_t count;
-  int32_t pad;
+  int32_t pad;   /* dense reduce: position of the own vector among the operands (0 = first) */
   CxEndpoint ep[CX_MAX_PEERS];
   uint64_t seq[CX_MAX_PEERS];  /* wait until hdr->seq >= seq[j] */
   uint32_t cap[CX_MAX_PEERS];  /* pair capacity of slot j: no table entry may point beyond it */
@@ -203,6 +203,13 @@ int cx_dense_reduce(int dev, int dtype, void* out, const void* own, int64_t n,
                     uint64_t push_seq, const int64_t* starts,
                     const int64_t* lens, void* counters, uint32_t src_rank,
                     uint32_t* status, uint64_t timeout_ns, void* stream);
+
+/* Barrier over the symmetric heap (src/gaspiEnvironment.tpp:33-35): rank `rank` stores `seq` into
+ * its cell of every rank's flag block (flag_ptrs[r]: CX_MAX_PEERS x 8 bytes, zeroed once, the same
+ * heap offset on every rank) and waits, bounded, for all cells of its own block.  `seq` must grow
+ * from call to call.  On CUDA one small kernel on `stream`; a wait that runs out sets CX_ST_TIMEOUT. */
+int cx_barrier(int dev, int rank, int ranks, void* const* flag_ptrs, uint64_t seq, uint32_t* status,
+               uint64_t timeout_ns, void* stream);
 
 /* Dense allreduce through the switch (multimem.ld_reduce + multimem.st), one kernel per rank;
  * CUDA only.  `stage` is this rank's block of the symmetric heap and `stage_mc` its multicast

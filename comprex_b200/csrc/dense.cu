@@ -305,20 +305,23 @@ __device__ __forceinline__ void dense_reduce_body(const ReduceParams& p) {
   }
   const bool vec = (reinterpret_cast<uintptr_t>(out) & (4 * sizeof(T) - 1)) == 0 &&
                    (!own || (reinterpret_cast<uintptr_t>(own) & (4 * sizeof(T) - 1)) == 0);
+  // where the own vector enters the sum (CxSources::pad; 0 = first, the reference's order):
+  // with the sources in rank order and own_pos = this rank, every rank adds in the same order
+  const int own_pos = min(max(p.src.pad, 0), p.src.count);
   const int64_t nv = (p.n + 3) / 4;
   for (int64_t q = gtid; q < nv; q += gsz) {
     const int64_t i = q * 4;
     if (vec && i + 3 < p.n) {
       // start from the first operand instead of zero: a plain copy stays bit-exact
+      // operands in order: sources [0, own_pos), the own vector, sources [own_pos, count)
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      int j0 = 0;
-      if (own) cx::load4(own + i, acc);
-      else if (p.src.count > 0) { ldcg4<T>(reinterpret_cast<const T*>(p.src.ep[0].pairs) + i, acc); j0 = 1; }
-      for (int j = j0; j < p.src.count; ++j) {
+      const int nops = p.src.count + (own ? 1 : 0);
+      for (int k = 0; k < nops; ++k) {
         float x[4];
-        ldcg4<T>(reinterpret_cast<const T*>(p.src.ep[j].pairs) + i, x);
+        if (own && k == own_pos) cx::load4(own + i, x);
+        else ldcg4<T>(reinterpret_cast<const T*>(p.src.ep[(own && k > own_pos) ? k - 1 : k].pairs) + i, x);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) acc[e] += x[e];
+        for (int e = 0; e < 4; ++e) acc[e] = k == 0 ? x[e] : acc[e] + x[e];
       }
       if (p.scale != 1.f)
         for (int e = 0; e < 4; ++e) acc[e] *= p.scale;
@@ -334,11 +337,12 @@ __device__ __forceinline__ void dense_reduce_body(const ReduceParams& p) {
     } else {
       for (int e = 0; e < 4 && i + e < p.n; ++e) {
         float acc = 0.f;
-        int j0 = 0;
-        if (own) acc = cx::Elem<T>::to_f(own[i + e]);
-        else if (p.src.count > 0) { acc = ldcg1<T>(reinterpret_cast<const T*>(p.src.ep[0].pairs) + i + e); j0 = 1; }
-        for (int j = j0; j < p.src.count; ++j)
-          acc += ldcg1<T>(reinterpret_cast<const T*>(p.src.ep[j].pairs) + i + e);
+        const int nops = p.src.count + (own ? 1 : 0);
+        for (int k = 0; k < nops; ++k) {
+          const float x = (own && k == own_pos) ? cx::Elem<T>::to_f(own[i + e])
+                                                : ldcg1<T>(reinterpret_cast<const T*>(p.src.ep[(own && k > own_pos) ? k - 1 : k].pairs) + i + e);
+          acc = k == 0 ? x : acc + x;
+        }
         if (p.scale != 1.f) acc *= p.scale;
         const T o = cx::Elem<T>::from_f(acc);
         out[i + e] = o;

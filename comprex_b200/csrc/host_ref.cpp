@@ -15,6 +15,8 @@
 #include <time.h>
 
 #include <algorithm>
+#include <chrono>
+#include <thread>
 #include <vector>
 
 #include "cx_common.h"
@@ -381,10 +383,13 @@ int cx_dense_reduce_host(int dtype, void* out, const void* own, int64_t n, const
   }
   for (int64_t i = 0; i < n; ++i) {
     float acc = 0.f;
-    int j0 = 0;
-    if (own) acc = load_elem(dtype, own, i);
-    else if (src->count > 0) { acc = load_elem(dtype, src->ep[0].pairs, i); j0 = 1; }
-    for (int j = j0; j < src->count; ++j) acc += load_elem(dtype, src->ep[j].pairs, i);
+    const int own_pos = std::min(std::max(src->pad, 0), src->count);   // where the own vector enters the sum
+    const int nops = src->count + (own ? 1 : 0);
+    for (int k = 0; k < nops; ++k) {
+      const float x = (own && k == own_pos) ? load_elem(dtype, own, i)
+                                            : load_elem(dtype, src->ep[(own && k > own_pos) ? k - 1 : k].pairs, i);
+      acc = k == 0 ? x : acc + x;
+    }
     if (scale != 1.f) acc *= scale;
     store_elem(dtype, out, i, acc);
     if (has_push)
@@ -585,5 +590,23 @@ int cx_update_dense_host(const float* g, int64_t n, const CxApplyArgs* a) {
   if (a->op == CX_OP_ADAMW && !a->v) return cx_set_error("cx_update_dense: second-moment buffer missing", 0);
   float* w = reinterpret_cast<float*>(a->out);
   for (int64_t i = 0; i < n; ++i) rule_host(a, w, i, a->scale * g[i], a->shadow_dtype);
+  return 0;
+}
+
+// Barrier of host ranks over the shared-memory heap: the protocol of the CUDA barrier kernel.
+int cx_barrier_host(int rank, int ranks, void* const* flag_ptrs, uint64_t seq, uint32_t* status,
+                    uint64_t timeout_ns) {
+  if (ranks < 1 || ranks > CX_MAX_PEERS || rank < 0 || rank >= ranks) return cx_set_error("cx_barrier: bad rank", 0);
+  for (int r = 0; r < ranks; ++r)
+    __atomic_store_n(reinterpret_cast<uint64_t*>(flag_ptrs[r]) + rank, seq, __ATOMIC_RELEASE);
+  const auto t0 = std::chrono::steady_clock::now();
+  for (int r = 0; r < ranks; ++r) {
+    const uint64_t* cell = reinterpret_cast<const uint64_t*>(flag_ptrs[rank]) + r;
+    while (__atomic_load_n(cell, __ATOMIC_ACQUIRE) < seq) {
+      const auto dt = std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0).count();
+      if ((uint64_t)dt > timeout_ns) { if (status) *status |= CX_ST_TIMEOUT; return 0; }
+      std::this_thread::yield();
+    }
+  }
   return 0;
 }

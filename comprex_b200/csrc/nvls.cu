@@ -299,7 +299,42 @@ __global__ void __launch_bounds__(kThreads, 1) mm_allreduce_kernel(const MmParam
   leave();
 }
 
+// ---- barrier over the symmetric heap -------------------------------------------------------------
+// Every rank stores the barrier's number into its cell of every peer's flag block (release, system
+// scope) and waits, bounded, until all cells of its own block carry that number: the GASPI
+// barrier of the reference (src/gaspiEnvironment.tpp:33-35) as one small kernel on the caller's
+// stream, no library collective involved.
+struct BarrierParams {
+  uint64_t* flags;                       // local block, one cell per rank
+  uint64_t* peer_flags[CX_MAX_PEERS];
+  int32_t rank, ranks;
+  uint64_t seq;
+  uint32_t* status;
+  uint64_t timeout_ns;
+};
+
+__global__ void barrier_kernel(const BarrierParams p) {
+  const int t = threadIdx.x;
+  if (t < p.ranks) {
+    __threadfence_system();
+    cx::st_release_sys(p.peer_flags[t] + p.rank, p.seq);
+    if (!cx::wait_seq(p.flags + t, p.seq, p.timeout_ns) && p.status) atomicOr(p.status, (uint32_t)CX_ST_TIMEOUT);
+  }
+}
+
 }  // namespace
+
+int cx_barrier_cuda(int rank, int ranks, void* const* flag_ptrs, uint64_t seq, uint32_t* status,
+                    uint64_t timeout_ns, void* stream) {
+  if (ranks < 1 || ranks > CX_MAX_PEERS || rank < 0 || rank >= ranks) return cx_set_error("cx_barrier: bad rank", 0);
+  BarrierParams p;
+  p.flags = reinterpret_cast<uint64_t*>(flag_ptrs[rank]);
+  for (int r = 0; r < CX_MAX_PEERS; ++r) p.peer_flags[r] = r < ranks ? reinterpret_cast<uint64_t*>(flag_ptrs[r]) : nullptr;
+  p.rank = rank; p.ranks = ranks; p.seq = seq; p.status = status; p.timeout_ns = timeout_ns;
+  barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  cx_note_launch();
+  return cx_check_launch("barrier_kernel");
+}
 
 extern "C" int64_t cx_mm_counter_bytes(void) { return (int64_t)sizeof(uint32_t) * (2 + 2 * kMaxSlabs + 2); }
 extern "C" int64_t cx_mm_flag_bytes(void) { return (int64_t)sizeof(uint64_t) * 2 * CX_MAX_PEERS; }

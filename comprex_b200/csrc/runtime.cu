@@ -54,6 +54,8 @@ int cx_fold_cuda(int, const void* const*, const int64_t*, const int64_t*, const 
 int cx_fold_host(int, const void* const*, const int64_t*, const int64_t*, const int32_t*, const int32_t*,
                  const int32_t*, int, float*, float*, float, float, float);
 int cx_axpy_host(int, void*, int, const void*, float, int64_t);
+int cx_barrier_cuda(int, int, void* const*, uint64_t, uint32_t*, uint64_t, void*);
+int cx_barrier_host(int, int, void* const*, uint64_t, uint32_t*, uint64_t);
 int cx_update_dense_cuda(const float*, int64_t, const CxApplyArgs*, void*);
 int cx_mm_allreduce_cuda(int, void*, const void*, void*, void*, int64_t, int64_t, int, int, float, int, int64_t,
                          uint64_t, void* const*, void*, uint32_t*, uint64_t, void*);
@@ -131,6 +133,12 @@ int cx_apply(int dev, const CxSources* src, int64_t n, const CxApplyArgs* a, uin
 
 int cx_update_dense(int dev, const float* g, int64_t n, const CxApplyArgs* a, void* stream) {
   return dev == CX_DEV_CUDA ? cx_update_dense_cuda(g, n, a, stream) : cx_update_dense_host(g, n, a);
+}
+
+int cx_barrier(int dev, int rank, int ranks, void* const* flag_ptrs, uint64_t seq, uint32_t* status,
+               uint64_t timeout_ns, void* stream) {
+  return dev == CX_DEV_CUDA ? cx_barrier_cuda(rank, ranks, flag_ptrs, seq, status, timeout_ns, stream)
+                            : cx_barrier_host(rank, ranks, flag_ptrs, seq, status, timeout_ns);
 }
 
 int cx_mm_allreduce(int dtype, void* out, const void* in, void* stage, void* stage_mc, int64_t stage_stride,

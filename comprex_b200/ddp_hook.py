@@ -56,7 +56,7 @@ class ComprexHookState:
         if red is None:
             if n * torch.empty(0, dtype=dtype).element_size() < self.dense_fallback_bytes:
                 red = _ar.BigRingAllreduce(self.env)
-                red.setup_connections(n, 1, dtype=dtype)
+                red.setup_connections(n, 1, dtype=dtype, ordered=True)   # the same bits on every rank
                 red.result_scale = 1.0 / self.env.ranks        # the mean comes out of the reducing kernel
             else:
                 red = _ar.Comprex_BigRingAllreduce(self.env)

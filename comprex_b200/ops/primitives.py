@@ -93,12 +93,15 @@ def make_targets(eps, mc=None) -> Targets:
     return t
 
 
-def make_sources(eps, seqs) -> Sources:
+def make_sources(eps, seqs, own_pos: int = 0) -> Sources:
+    """Source descriptor.  ``own_pos``: dense reduce only, where the own vector enters the sum
+    (0 = first; with the sources in rank order and ``own_pos`` = this rank all ranks add alike)."""
     eps = list(eps)
     if len(eps) > _lib.MAX_PEERS:
         raise ComprexError("too many sources")
     s = Sources()
     s.count = len(eps)
+    s.pad = int(own_pos)
     for i, (e, q) in enumerate(zip(eps, seqs)):
         s.ep[i] = e
         s.seq[i] = q

@@ -274,6 +274,8 @@ class ComprexOptimizer(torch.optim.Optimizer):
             ar.setup_connections(size, 1, 0, self.compression_ratio, self.size_factor)
         elif name == "alltoone":
             ar.setup_connections(size, 1, 0)
+        elif name == "bigring":
+            ar.setup_connections(size, 1, ordered=self.consistent)     # identical bits on every rank
         else:
             ar.setup_connections(size, 1)
         return ar
@@ -298,7 +300,10 @@ class ComprexOptimizer(torch.optim.Optimizer):
             else:
                 b.kind = "phased"
             if b.kind != "bigring":
-                b.xbuf = torch.empty(n, dtype=torch.float32, device=dev)     # the exchange works in place on a copy
+                # the exchange works in place on a copy; for a dense allreduce through the switch the
+                # copy lives in the symmetric heap, so that it is reduced there without staging
+                in_heap = b.kind == "phased" and getattr(b.ar, "first_phase_waits", False)
+                b.xbuf = self._env.empty(n) if in_heap else torch.empty(n, dtype=torch.float32, device=dev)
         self._armed = True
 
     def describe(self) -> str:

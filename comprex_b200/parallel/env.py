@@ -175,6 +175,7 @@ class GaspiEnvironment:
         self._uid = None
         self._closed = False
         self._heap_tensors: dict[int, SymmAlloc] = {}
+        self._bar = None
         self.sync_check = self.dev == _lib.DEV_HOST or os.environ.get("COMPREX_SYNC_CHECK", "0") == "1"
         # NVSwitch multicast (multimem stores / in-switch reduction): used where the heap can be
         # bound to a multicast object; COMPREX_NVLS=0 keeps every transfer on plain peer stores
@@ -195,10 +196,34 @@ class GaspiEnvironment:
         return self
 
     def barrier(self) -> None:
-        """All ranks' earlier work is complete; raises pending kernel errors."""
+        """All ranks' earlier work is complete; raises pending kernel errors.
+
+        Between real ranks this is the library's own barrier over the symmetric heap (one small
+        kernel, or the host twin for CPU ranks: every rank stores the barrier's number into its
+        cell on every peer and waits, bounded, for all of its own cells; csrc/nvls.cu); no
+        ``torch.distributed`` collective is involved once the heap exists."""
         self.flush()
-        if self._world is None and self.group is not None and self.ranks > 1:
+        if self._world is not None or self.group is None or self.ranks == 1:
+            return
+        if os.environ.get("COMPREX_DIST_BARRIER", "0") == "1":
             dist.barrier(group=self.group)
+            return
+        self._ensure_barrier()
+        self._bar["seq"] += 1
+        _lib.check(self.lib.cx_barrier(self.dev, self.rank, self.ranks, self._bar["ptrs"], self._bar["seq"],
+                                       self._bar["status"].dev_ptr, self.timeout_ns, _lib.stream_ptr(self.device)),
+                   "cx_barrier")
+        self.flush()
+
+    def _ensure_barrier(self) -> None:
+        """Collective: the first barrier (or heap mark) allocates the barrier's flag block."""
+        if self._bar is not None or self._world is not None or self.group is None or self.ranks == 1:
+            return
+        blk = self.alloc(8 * _lib.MAX_PEERS, 256)
+        self._bar = {"ptrs": (C.c_void_p * _lib.MAX_PEERS)(*[self.ptr(blk, r) if r < self.ranks else None
+                                                           for r in range(_lib.MAX_PEERS)]),
+                     "seq": 0, "status": self.new_status("barrier")}
+        dist.barrier(group=self.group)          # every rank's cells exist (and are zero) before the first store
 
     def flush(self) -> None:
         """Wait for this rank's queued work (src/gaspiEnvironment.tpp:37-39)."""
@@ -418,6 +443,7 @@ class GaspiEnvironment:
 
     def heap_mark(self):
         """Snapshot of the allocator; pass to :meth:`heap_release` (collective)."""
+        self._ensure_barrier()          # the barrier's own block must not be part of what is released
         return (len(self._segments), self._segments[-1]["used"] if self._segments else 0)
 
     def heap_release(self, mark) -> None:

@@ -275,7 +275,7 @@ def scenario_optimizer_kinds(rank, world, device, kind, aggregate_blob, overlap)
         env.flush()
         if len(arms) == 2:
             assert torch.equal(arms[0][1]._master, arms[1][1]._master), "fused ring differs from the two-stage path"
-        if kind in ("comprex_bigring", "comprex_ring", "auto", "ring", "alltoone"):
+        if kind in ("comprex_bigring", "comprex_ring", "auto", "ring", "alltoone", "bigring"):
             got = [None] * world
             dist.all_gather_object(got, arms[0][1]._master.detach().cpu())
             for other in got[1:]:
@@ -462,7 +462,7 @@ def test_ddp_hook_cpu():
                                        ("ring", True), ("bigring", True), ("alltoone", True),
                                        ("comprex_bigring", False), ("comprex_ring", False)])
 def test_every_collective_runs_bucketed_cpu(kind, blob):
-    out = run_ranks(2 if kind != "comprex_ring" else 3, "test_optimizer:scenario_optimizer_kinds",
+    out = run_ranks(2 if kind not in ("comprex_ring", "auto", "bigring") else 3, "test_optimizer:scenario_optimizer_kinds",
                     args=(kind, blob, False))
     assert all(last < first for first, last in out)
 
