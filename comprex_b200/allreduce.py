@@ -991,33 +991,37 @@ class Comprex_AllToOneAllreduce(_ComprexAllreduceBase):
 # =====================================================================================
 # choice of schedule by size, ratio and number of ranks
 # =====================================================================================
-# Cost model behind ``select_schedule``: time = launch floor + bytes through HBM / HBM rate
-# + bytes over NVLink / link rate, with the rates this package's kernels reach on 8 B200 behind
-# an NVSwitch (measured with bench/allreduce_sweep.py; microseconds, bytes per microsecond).
+# Cost model behind ``select_schedule``: time = launch floor + bytes through HBM / HBM rate + bytes
+# into this GPU's port / link rate + pairs decoded x time per pair, with the rates this package's
+# kernels reach on 2-8 B200 behind an NVSwitch (bench/allreduce_sweep.py; microseconds, bytes per
+# microsecond).  The model ranks the schedules; its absolute times run ~15 % high for large vectors
+# because the phases overlap.
 _COST = {
     "floor_dense_us": 30.0,      # dense one-shot: two launches
-    "floor_two_shot_us": 60.0,   # dense reduce-scatter + allgather: three launches, two dependent exchanges
-    "floor_bigring_us": 42.0,    # threshold + compress + apply
-    "floor_ring_us": 135.0,      # 3 P launches on side streams, two dependent exchanges
-    "hbm_bpus": 5.0e6,           # streaming kernels: ~5 TB/s effective
-    "link_dense_bpus": 5.5e5,    # dense peer stores / multimem: ~550 GB/s per direction
-    "link_pairs_bpus": 2.6e5,    # 8-byte pairs stored to P-1 peers by one kernel: ~260 GB/s out
-    "scatter_bpus": 1.2e6,       # decode: 64 bytes of sector traffic per pair
+    "floor_two_shot_us": 55.0,   # dense reduce-scatter + allgather / through the switch
+    "floor_bigring_us": 40.0,    # threshold + compress + decode
+    "floor_ring_us": 50.0,       # 3 P launches on side streams (one graph), two dependent exchanges,
+    "floor_ring_per_rank_us": 9.0,   # ... plus this per rank
+    "hbm_bpus": 6.0e6,           # streaming kernels
+    "link_bpus": 5.5e5,          # into one GPU's port: peer stores and multicast stores alike
+    "dense_link_bpus": 4.3e5,    # dense allreduce of a vector outside the heap (staging copies included)
+    "pair_us": 4.0e-6,           # decode of one (index, value) pair
 }
 
 
 def schedule_costs(n: int, ratio: float, ranks: int, elem_bytes: int = 4) -> dict:
     """Modelled microseconds of the three schedules ``select_schedule`` chooses from."""
     c, p = _COST, max(int(ranks), 1)
-    pairs = 8.0 * ratio * n                                   # bytes of one rank's payload
-    one_shot = n * elem_bytes <= (1 << 20) or p <= 2
-    dense_link = (p - 1) * n * elem_bytes if one_shot else 2.0 * (p - 1) / p * n * elem_bytes
-    dense = ((c["floor_dense_us"] if one_shot else c["floor_two_shot_us"]) + dense_link / c["link_dense_bpus"]
-             + 3.0 * n * elem_bytes / c["hbm_bpus"])
-    bigring = (c["floor_bigring_us"] + 12.0 * n / c["hbm_bpus"] + (p - 1) * pairs / c["link_pairs_bpus"]
-               + (p - 1) * ratio * n * 64.0 / c["scatter_bpus"] / 8.0)
-    ring = (c["floor_ring_us"] + 12.0 * n / c["hbm_bpus"] + 2.0 * (p - 1) / p * pairs / c["link_pairs_bpus"]
-            + 2.0 * ratio * n * 64.0 / c["scatter_bpus"] / 8.0 + 8.0 * n / p / c["hbm_bpus"])
+    nb = n * elem_bytes
+    pairs = ratio * n                                         # pairs of one rank's payload
+    wire = 8.0 * pairs + 8.0 * n / 1024                       # its bytes: pairs + table
+    one_shot = nb <= (1 << 20) or p <= 2
+    dense = ((c["floor_dense_us"] + (p - 1) * nb / c["link_bpus"]) if one_shot else
+             (c["floor_two_shot_us"] + 2.0 * (p - 1) / p * nb / c["dense_link_bpus"])) + 3.0 * nb / c["hbm_bpus"]
+    bigring = (c["floor_bigring_us"] + (8.0 + elem_bytes) * n / c["hbm_bpus"] + (p - 1) * wire / c["link_bpus"]
+               + p * pairs * c["pair_us"] + nb / c["hbm_bpus"])
+    ring = (c["floor_ring_us"] + c["floor_ring_per_rank_us"] * p + (8.0 + elem_bytes) * n / c["hbm_bpus"]
+            + 2.0 * (p - 1) / p * wire / c["link_bpus"] + (2.0 * p - 1) / p * pairs * c["pair_us"] + nb / c["hbm_bpus"])
     return {"bigring": dense, "comprex_bigring": bigring, "comprex_ring": ring}
 
 
