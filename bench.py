@@ -391,12 +391,19 @@ def main():
 
     main_arm = run_arm(args, args.impl, rank, world, local)
     base = None
+    notes = {}
     if args.impl == "ours" and not args.skip_baseline:
         # the comparison arm in the same invocation, on the same batches: stock DDP + NCCL + torch optimizer
-        base = run_arm(args, "dense", rank, world, local)
+        try:
+            base = run_arm(args, "dense", rank, world, local)
+        except Exception as e:                               # the headline number stands without it
+            notes["baseline_error"] = f"{type(e).__name__}: {e}"[:300]
     ar_block = None
     if world > 1 and args.impl == "ours" and not args.skip_allreduce:
-        ar_block = allreduce_block(rank, world, local)
+        try:
+            ar_block = allreduce_block(rank, world, local)
+        except Exception as e:
+            notes["allreduce_error"] = f"{type(e).__name__}: {e}"[:300]
     if rank == 0:
         line = {"metric": "train samples/sec", "value": main_arm["value"], "unit": "samples/s", "n_gpus": world,
                 "steps": args.steps, "warmup": main_arm["warm"], "ms_per_step": main_arm["ms_per_step"],
@@ -414,6 +421,7 @@ def main():
             line["baseline"] = bl
         if ar_block is not None:
             line["allreduce"] = ar_block
+        line.update(notes)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

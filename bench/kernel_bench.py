@@ -6,6 +6,8 @@ after warm-up and with an L2 flush between iterations:
 * ``threshold``  - sampled top-k threshold estimate,
 * ``compress``   - fused residual add / select / per-sub-tile compaction / store into
                    ``--targets`` slots (local memory stands in for peers),
+* ``residual_add_torch`` - ``torch.add(r, g, out=r)``: the same dense traffic through torch's own
+                   elementwise kernel, as the size-matched reference for the compress rows,
 * ``apply_add``  - wait + scatter-add of ``--sources`` payloads,
 * ``apply_set``  - wait + dense result (sum of the payloads, zero elsewhere): the receive side of
                    the replica-consistent allreduce,
@@ -109,6 +111,11 @@ def main():
                     seq[0] += 1
                     comp.compress(g, r, n, cap, seq[0], tg)
 
+                def k_stream():
+                    # torch's elementwise kernel with the compress kernel's dense traffic (read g and r,
+                    # write r): what a plain streaming kernel reaches at this size, cold caches included
+                    torch.add(r, g, out=r)
+
                 def k_add():
                     src = P.make_sources([s.endpoint(env) for s in slots[: args.sources]], [1] * args.sources)
                     P.apply_sparse(env, src, n, P.args_add(out, 1.0 / 8), st)
@@ -132,6 +139,7 @@ def main():
                 kernels = {
                     "threshold": (k_thr, 0),
                     "compress": (k_comp, n * (gb + 8) + 8 * nnz * args.targets),
+                    "residual_add_torch": (k_stream, n * (gb + 8)),
                     "apply_add": (k_add, args.sources * nnz * (8 + 64)),
                     "apply_set": (k_set, args.sources * nnz * 8 + 4 * n),
                     "apply_sgd": (k_sgd, args.sources * nnz * (8 + 64)),
@@ -139,7 +147,7 @@ def main():
                 }
                 r0 = r.clone()
                 for name, (fn, nbytes) in kernels.items():
-                    if name != "compress" and dname != args.dtypes[0]:
+                    if name not in ("compress", "residual_add_torch") and dname != args.dtypes[0]:
                         continue   # only the compress kernel reads the gradient dtype
                     if args.kernels and name not in args.kernels:
                         continue

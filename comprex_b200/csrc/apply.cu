@@ -427,35 +427,12 @@ __device__ __forceinline__ void table_entry(const ApplyParams& p, uint32_t sub, 
 // sparse part of the sub-tile, so the state of up to STAGES sub-tiles per warp is in flight
 // without holding a register.  Every wait on an mbarrier is bounded.
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_load(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(smem_u32(dst_smem)), "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-// at most ~0.25 s: a copy that has not landed by then will not land
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-  for (uint32_t it = 0; it < (1u << 22); ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (it > 64) __nanosleep(64);
-  }
-  return false;
-}
+using cx::smem_u32;
+using cx::mbar_init;
+using cx::mbar_expect_tx;
+using cx::bulk_load;
+using cx::mbar_try_wait;
+using cx::mbar_wait_bounded;
 
 template <int OP>
 struct StateArrays { static constexpr int n = OP == CX_OP_SGD ? 1 : (OP == CX_OP_MOMENTUM ? 2 : 3); };

@@ -132,6 +132,41 @@ __device__ __forceinline__ uint64_t seq_of(const uint64_t* cell, uint64_t by_val
 const uint64_t* cx_seq_cell();
 
 // ---- programmatic dependent launch ------------------------------------------------------------
+// ---- bulk copies (the SM's copy engine) and the mbarriers that count their bytes ------------------
+// cp.async.bulk wants both addresses 16-byte aligned and a size that is a multiple of 16 bytes.
+// Every wait on an mbarrier is bounded.
+namespace cx {
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst_smem)), "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// at most ~0.25 s: a copy that has not landed by then will not land
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  for (uint32_t it = 0; it < (1u << 22); ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (it > 64) __nanosleep(64);
+  }
+  return false;
+}
+}  // namespace cx
+
 // A kernel launched with cx_launch_pdl may become resident while the kernel in front of it on the
 // stream is still finishing (as soon as all of that kernel's CTAs have called cx::pdl_trigger or
 // exited).  The late kernel synchronises itself: cx::pdl_wait blocks until the earlier grid has

@@ -140,14 +140,27 @@ __device__ __forceinline__ bool wait_all(const MmParams& p, int which, uint64_t 
   return ok;
 }
 
+#ifndef CX_MM_COPY_SHARE
+#define CX_MM_COPY_SHARE 10    // one CTA in this many copies in, one copies out
+#endif
+#ifndef CX_MM_COPY_UNROLL
+#define CX_MM_COPY_UNROLL 16   // 16-byte loads in flight per thread of a copy group
+#endif
+
+// The copy groups are small (most CTAs reduce), so each of their threads keeps many loads in
+// flight: with 4 per thread a CTA moved ~25 GB/s and the copies, not the switch, set the pace.
 __device__ __forceinline__ void copy_vec(uint4* dst, const uint4* src, int64_t nv, int64_t gtid, int64_t gsz,
                                          bool through_l2) {
   int64_t q = gtid;
-  for (; q + 3 * gsz < nv; q += 4 * gsz) {
-    uint4 a, b, c, d;
-    if (through_l2) { a = __ldcg(src + q); b = __ldcg(src + q + gsz); c = __ldcg(src + q + 2 * gsz); d = __ldcg(src + q + 3 * gsz); }
-    else { a = src[q]; b = src[q + gsz]; c = src[q + 2 * gsz]; d = src[q + 3 * gsz]; }
-    dst[q] = a; dst[q + gsz] = b; dst[q + 2 * gsz] = c; dst[q + 3 * gsz] = d;
+  for (; q + (CX_MM_COPY_UNROLL - 1) * gsz < nv; q += CX_MM_COPY_UNROLL * gsz) {
+    uint4 v[CX_MM_COPY_UNROLL];
+#pragma unroll
+    for (int u = 0; u < CX_MM_COPY_UNROLL; ++u) v[u] = through_l2 ? __ldcg(src + q + u * gsz) : __ldcs(src + q + u * gsz);
+#pragma unroll
+    for (int u = 0; u < CX_MM_COPY_UNROLL; ++u) {
+      if (through_l2) __stcs(dst + q + u * gsz, v[u]);
+      else dst[q + u * gsz] = v[u];
+    }
   }
   for (; q < nv; q += gsz) dst[q] = through_l2 ? __ldcg(src + q) : src[q];
 }
@@ -383,9 +396,9 @@ int cx_mm_allreduce_cuda(int dtype, void* out, const void* in, void* stage, void
   p.n_in = 0;
   p.n_red = grid;
   if (p.staged && !one_shot) {
-    // the copies run at HBM speed, the reduction at link speed: a quarter of the CTAs for each copy
+    // the copies run at HBM speed, the reduction at link speed: most CTAs reduce
     if (grid < 3) grid = 3;
-    int copy = grid / 4;
+    int copy = grid / CX_MM_COPY_SHARE;
     if (const char* e = getenv("COMPREX_MM_COPY_CTAS")) copy = atoi(e);
     if (copy < 1) copy = 1;
     if (2 * copy > grid - 1) copy = (grid - 1) / 2;

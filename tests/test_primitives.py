@@ -142,6 +142,61 @@ def test_compress_add_update(world, n, dtype):
     assert st["nnz"] == idx_w.numel() and st["status"] == 0
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [1024, 4097, 70001, (1 << 20) + 5])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mode", ["add_update", "update", "plain"])
+def test_compress_bulk_copy_kernel_matches_register_kernel(monkeypatch, n, dtype, mode):
+    """The opt-in compress kernel whose sub-tiles arrive through bulk copies into shared memory
+    (cp.async.bulk + mbarrier, a pipeline per warp) selects the same survivors, writes the same
+    table counts and leaves the same residual as the default kernel, for all three modes, on
+    sizes with a partial last sub-tile, and with a slot that overflows."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    results = []
+    for bulk in ("0", "1"):
+        monkeypatch.setenv("COMPREX_COMPRESS_BULK", bulk)
+        world = cx.LoopbackWorld(2, device="cuda", timeout_ms=2000)
+        e0, e1 = world.envs
+        gen = torch.Generator().manual_seed(n)
+        g = torch.randn(n, generator=gen).to(dtype).cuda()
+        r = (0.3 * torch.randn(n, generator=gen)).cuda()
+        out = []
+
+        def run(cap, rr, seq, slot, comp):
+            tg = P.make_targets([slot.endpoint(e0, 1)])
+            if mode == "add_update":
+                comp.compress(g, rr, n, cap, seq, tg)
+            elif mode == "update":
+                comp.compress(None, rr, n, cap, seq, tg)
+            else:
+                comp.compress(g, None, n, cap, seq, tg)
+            e0.flush()
+            hdr, idx, val, counts = read_pairs(e1, slot)
+            return hdr, idx, val, counts, comp.last_stats()
+
+        slot = P.SparseSlot.create(e1, n, n)
+        comp = P.Compressor(e0, n)
+        comp.set_threshold(1.0)
+        for seq in (1, 2):
+            hdr, idx, val, counts, st = run(n, r, seq, slot, comp)
+            assert hdr.nnz == hdr.nnz_found and st["status"] == 0
+            out.append((hdr.nnz, idx, val, counts, r.cpu().clone()))
+            r.add_(0.5)                               # something to send in the second round
+        # a slot that overflows: which sub-tiles find room is a matter of timing, the totals are not
+        cap = max(n // 64, 8)
+        slot = P.SparseSlot.create(e1, n, cap)
+        hdr, idx, val, counts, st = run(cap, r.clone(), 1, slot, comp)
+        assert hdr.nnz < hdr.nnz_found and st["status"] & _lib.ST_OVERFLOW
+        out.append((hdr.nnz, hdr.nnz_found))
+        results.append(out)
+        world.close()
+    for a, b in zip(*results):
+        assert len(a) == len(b)
+        for x, y in zip(a, b):
+            assert torch.equal(x, y) if isinstance(x, torch.Tensor) else x == y
+
+
 def test_compress_capacity_overflow_keeps_residual(world):
     e0, e1 = world.envs
     dev, n, cap = world.device, 20000, 100
