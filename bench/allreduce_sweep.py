@@ -133,7 +133,11 @@ def main():
     # one heap segment that holds the largest cell (2 P slots of 8 B x 0.2 n pairs for the compressed
     # BigRing at 10 %): cells then reuse it instead of mapping fresh peer / multicast memory each time
     nmax = 1 << max(args.log2_sizes)
-    heap = int(min(args.heap_gb * (1 << 30), max(256 << 20, 2 * world * 1.7 * nmax + 3 * 4 * nmax)))
+    # the dense AllToOne keeps 2 P + 2 full-size slots (two parities per sender at the chief, two for
+    # the broadcast): with --max-log2-onetoall raised, the heap has to hold them
+    n_one = 1 << min(max(args.log2_sizes), args.max_log2_onetoall)
+    need_one = (2 * world + 2) * 4 * n_one + 2 * 4 * n_one if "alltoone" in args.variants else 0
+    heap = int(min(args.heap_gb * (1 << 30), max(256 << 20, 2 * world * 1.7 * nmax + 3 * 4 * nmax, need_one)))
     env = cx.GaspiEnvironment(heap, device=dev)
     flush = None if args.no_flush else torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
     peak, how = hbm_gbs()

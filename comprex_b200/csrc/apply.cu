@@ -653,19 +653,13 @@ __global__ void __launch_bounds__(kThreads) forward_kernel(const ForwardParams p
       for (int k = 0; k < p.tg.count; ++k) *reinterpret_cast<uint2*>(p.tg.ep[k].pairs + v.x + i) = pr;
     }
   }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) s_last = (atomicAdd(&p.ctr->done, 1u) == gridDim.x - 1) ? 1u : 0u;
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
+  if (!cx::cta_arrive(&p.ctr->done, gridDim.x, &s_last)) return;
   const uint32_t failed = *reinterpret_cast<volatile uint32_t*>(&p.ctr->pad[0]);
   if (!failed && (int)threadIdx.x < p.tg.count) {
     CxHeader* o = p.tg.ep[threadIdx.x].hdr;
     o->bytes = 8ull + 8ull * nnz; o->n = h->n; o->nnz = nnz; o->nnz_found = h->nnz_found;
     o->kind = h->kind; o->threshold = h->threshold; o->nsub = nsub; o->src_rank = h->src_rank;
     o->dtype = h->dtype;
-    __threadfence_system();
     cx::st_release_sys(&o->seq, p.seq);
   }
   __syncthreads();

@@ -55,6 +55,24 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kChunks = CX_SUBTILE / 128;  // 128 elements = 32 lanes x 4
 constexpr int kStage = 128;                // pairs staged per warp and pass
 
+// -DCX_COMPRESS_TRACE: thread 0 of every CTA stamps %globaltimer at up to eight points of
+// compress_kernel (entry, before the loop, after the loop, after the arrival, and in the CTA that
+// arrives last: regions summed, headers published, end) into a device array that
+// cx_compress_trace copies out; a development aid for the fixed part of the kernel's time, not compiled by default.
+#ifdef CX_COMPRESS_TRACE
+__device__ unsigned long long g_cx_trace[8 * 2048];
+#define CX_TRACE(slot)                                                   \
+  do {                                                                   \
+    if (threadIdx.x == 0 && blockIdx.x < 2048) {                         \
+      unsigned long long t_;                                             \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));             \
+      g_cx_trace[blockIdx.x * 8 + (slot)] = t_;                          \
+    }                                                                    \
+  } while (0)
+#else
+#define CX_TRACE(slot) do { } while (0)
+#endif
+
 struct CompressParams {
   const void* g;
   float* r;
@@ -309,17 +327,13 @@ __device__ __forceinline__ void compress_finish(const CompressParams& p, const i
   cx::pdl_trigger();
   // ---- completion: the CTA that arrives last publishes -------------------------------
   if (failed) atomicOr(&p.ctr->pad[4], 1u);
-  __threadfence_system();
-  __syncthreads();
   if (tid == 0) {
-    const uint32_t prev = atomicAdd(&p.ctr->done, 1u);
-    s_last = (prev == gridDim.x - 1) ? 1u : 0u;
     s_found = 0;
     s_nnz = 0;
   }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
+  const bool last = cx::cta_arrive(&p.ctr->done, gridDim.x, &s_last);
+  CX_TRACE(3);
+  if (!last) return;
   const uint32_t any_failed = *reinterpret_cast<volatile uint32_t*>(&p.ctr->pad[4]);
   if ((uint32_t)tid < p.nregions) {
     const uint32_t f = *reinterpret_cast<volatile uint32_t*>(&p.ctr->region[tid][0]);
@@ -328,6 +342,7 @@ __device__ __forceinline__ void compress_finish(const CompressParams& p, const i
     p.ctr->region[tid][0] = 0;
   }
   __syncthreads();
+  CX_TRACE(4);
   const uint32_t found = s_found;  // survivors
   const uint32_t nnz = s_nnz;      // pairs stored
   if (tid < p.tg.count && !any_failed) {
@@ -341,9 +356,9 @@ __device__ __forceinline__ void compress_finish(const CompressParams& p, const i
     h->nsub = p.nsub;
     h->src_rank = p.src_rank;
     h->dtype = CX_F32;
-    __threadfence_system();
     cx::st_release_sys(&h->seq, cx::seq_of(p.seq_cell, p.seq));
   }
+  CX_TRACE(5);
   if (tid == 0) {
     if (p.stats) {
       p.stats->n = (uint32_t)p.n;
@@ -355,6 +370,7 @@ __device__ __forceinline__ void compress_finish(const CompressParams& p, const i
     p.ctr->done = 0;
     p.ctr->pad[4] = 0;
   }
+  CX_TRACE(6);
 }
 
 // T: element type of g.  HAS_G / HAS_R select compress_add_update (both),
@@ -373,6 +389,7 @@ compress_kernel(const __grid_constant__ CompressParams p) {
   const int warp = tid >> 5;
   const T* __restrict__ g = reinterpret_cast<const T*>(p.g);
   float* __restrict__ r = p.r;
+  CX_TRACE(0);
   // Launched with programmatic stream serialization, this grid may be resident while the
   // threshold kernel in front of it still runs: pull the warp's first sub-tile towards L2, then
   // wait for that kernel to finish before reading its result or touching the residual.
@@ -389,6 +406,7 @@ compress_kernel(const __grid_constant__ CompressParams p) {
   }
   cx::pdl_wait();
   const float thr = *p.thr;
+  CX_TRACE(1);
   CxPair* stage = s_stage[warp];
   const uint32_t nwarps = gridDim.x * kWarps;
   const uint32_t nfull = p.vec ? (uint32_t)(p.n / CX_SUBTILE) : 0u;  // sub-tiles on the fast path
@@ -411,6 +429,10 @@ compress_kernel(const __grid_constant__ CompressParams p) {
     else compress_subtile_edge<T, HAS_G, HAS_R, MC>(p, sub, lane, thr, g, r);
   }
 
+#ifdef CX_COMPRESS_TRACE
+  __syncthreads();   // the stamp marks the CTA's last warp leaving the loop
+#endif
+  CX_TRACE(2);
   compress_finish(p, tid, thr, false, s_last, s_found, s_nnz);
 }
 
@@ -595,6 +617,13 @@ int launch_bulk(const CompressParams& p, cudaStream_t s) {
 }
 
 }  // namespace
+
+#ifdef CX_COMPRESS_TRACE
+extern "C" int cx_compress_trace(unsigned long long* host, int n) {
+  if (n > 8 * 2048) n = 8 * 2048;
+  return (int)cudaMemcpyFromSymbol(host, g_cx_trace, sizeof(unsigned long long) * n);
+}
+#endif
 
 // The only scratch a compressor needs: one zero-initialised CxWorkCounters block.
 extern "C" int64_t cx_workspace_bytes(int64_t n) {

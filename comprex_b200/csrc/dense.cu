@@ -64,8 +64,7 @@ __device__ __forceinline__ void publish_dense(const CxTargets& tg, int k, int64_
   h->n = (uint32_t)n; h->nnz = (uint32_t)n; h->nnz_found = (uint32_t)n;
   h->kind = CX_KIND_DENSE; h->threshold = 0.f; h->nsub = 0; h->src_rank = src_rank;
   h->dtype = dtype;
-  __threadfence_system();
-  cx::st_release_sys(&h->seq, seq);
+  cx::st_release_sys(&h->seq, seq);   // releases this thread's header stores and all that cta_arrive ordered before
 }
 
 // four elements through the multicast mapping (16 bytes of fp32, 8 bytes of a 16-bit type)
@@ -161,12 +160,7 @@ __global__ void __launch_bounds__(kThreads) dense_send_kernel(const SendParams p
     }
   }
   cx::pdl_trigger();   // the reducing kernel queued behind this one may become resident and poll
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) s_last = (atomicAdd(&p.ctr->done, 1u) == gridDim.x - 1) ? 1u : 0u;
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
+  if (!cx::cta_arrive(&p.ctr->done, gridDim.x, &s_last)) return;
   if ((int)threadIdx.x < p.tg.count)
     publish_dense<T>(p.tg, threadIdx.x, p.has_ranges ? p.rg.len[threadIdx.x] : p.n, cx::seq_of(p.seq_cell, p.seq),
                      p.src_rank, p.dtype);
@@ -352,12 +346,7 @@ __device__ __forceinline__ void dense_reduce_body(const ReduceParams& p) {
     }
   }
   if (!p.has_push) return;
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) s_last = (atomicAdd(&p.ctr->pad[2], 1u) == gridDim.x - 1) ? 1u : 0u;
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
+  if (!cx::cta_arrive(&p.ctr->pad[2], gridDim.x, &s_last)) return;
   const uint32_t failed = *reinterpret_cast<volatile uint32_t*>(&p.ctr->pad[0]);
   if (!failed && (int)threadIdx.x < p.push.count)
     publish_dense<T>(p.push, threadIdx.x, p.n, cx::seq_of(p.seq_cell, p.push_seq), p.src_rank, p.dtype);

@@ -111,12 +111,7 @@ template <> struct MM<__half> {
 // [which * CX_MAX_PEERS + rank] of every rank's flag block (unless the launch is marked failed).
 __device__ __forceinline__ void arrive_and_publish(const MmParams& p, int counter, int group, int which,
                                                    uint64_t value, uint32_t* s_last) {
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) *s_last = (atomicAdd(&p.ctr[1 + counter], 1u) == (uint32_t)group - 1) ? 1u : 0u;
-  __syncthreads();
-  if (!*s_last) return;
-  __threadfence();
+  if (!cx::cta_arrive(&p.ctr[1 + counter], (uint32_t)group, s_last)) return;
   const uint32_t failed = *reinterpret_cast<volatile uint32_t*>(&p.ctr[0]);
   if (!failed && (int)threadIdx.x < p.ranks)
     cx::st_release_sys(p.peer_flags[threadIdx.x] + which * CX_MAX_PEERS + p.rank, value);

@@ -260,12 +260,7 @@ __global__ void __launch_bounds__(kThreads) rle_emit_kernel(const SendParams p) 
   if (valid > 0 && base + valid == p.n && q > 0)   // the thread that holds the last element closes the last run
     for (int t = 0; t < p.tg.count; ++t)
       reinterpret_cast<int32_t*>(reinterpret_cast<char*>(p.tg.ep[t].pairs) + runs_off)[q - 1] = (int)(p.n - prev);
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) s_lastblock = (atomicAdd(&p.meta->done, 1u) == gridDim.x - 1) ? 1u : 0u;
-  __syncthreads();
-  if (!s_lastblock) return;
-  __threadfence();
+  if (!cx::cta_arrive(&p.meta->done, gridDim.x, &s_lastblock)) return;
   if ((int)threadIdx.x < p.tg.count) {
     const CxEndpoint ep = p.tg.ep[threadIdx.x];
     int32_t* pay = reinterpret_cast<int32_t*>(ep.pairs);
@@ -279,7 +274,6 @@ __global__ void __launch_bounds__(kThreads) rle_emit_kernel(const SendParams p) 
     h->n = (uint32_t)p.n; h->nnz = (uint32_t)nnz_total; h->nnz_found = (uint32_t)nnz_total;
     h->kind = CX_KIND_RLE; h->threshold = thr; h->nsub = 0; h->src_rank = p.src_rank;
     h->dtype = CX_F32;
-    __threadfence_system();
     cx::st_release_sys(&h->seq, p.seq);
   }
   if (threadIdx.x == 0) p.meta->done = 0;

@@ -175,6 +175,7 @@ def test_compress_bulk_copy_kernel_matches_register_kernel(monkeypatch, n, dtype
             hdr, idx, val, counts = read_pairs(e1, slot)
             return hdr, idx, val, counts, comp.last_stats()
 
+        P.SparseSlot.create(e0, n, n)                 # allocations are symmetric across the ranks
         slot = P.SparseSlot.create(e1, n, n)
         comp = P.Compressor(e0, n)
         comp.set_threshold(1.0)
@@ -185,6 +186,7 @@ def test_compress_bulk_copy_kernel_matches_register_kernel(monkeypatch, n, dtype
             r.add_(0.5)                               # something to send in the second round
         # a slot that overflows: which sub-tiles find room is a matter of timing, the totals are not
         cap = max(n // 64, 8)
+        P.SparseSlot.create(e0, n, cap)
         slot = P.SparseSlot.create(e1, n, cap)
         hdr, idx, val, counts, st = run(cap, r.clone(), 1, slot, comp)
         assert hdr.nnz < hdr.nnz_found and st["status"] & _lib.ST_OVERFLOW
