@@ -44,6 +44,7 @@ struct MmParams {
   int64_t n;                 // elements
   int32_t rank, ranks;
   int32_t staged;            // 1: copy-in / copy-out run; 0: the vector is the staging block
+  int32_t bulk;              // 1: the copy groups move their slabs with the SM's copy engine
   int32_t one_shot;
   int64_t slab_vec;          // 16-byte vectors per slab
   int32_t nslabs;
@@ -136,7 +137,7 @@ __device__ __forceinline__ bool wait_all(const MmParams& p, int which, uint64_t 
 }
 
 #ifndef CX_MM_COPY_SHARE
-#define CX_MM_COPY_SHARE 10    // one CTA in this many copies in, one copies out
+#define CX_MM_COPY_SHARE 6     // one CTA in this many copies in, one copies out (2^28 fp32, 4 GPUs: 24 CTAs 2948 us, 14 CTAs 3324 us, 8 CTAs 4003 us)
 #endif
 #ifndef CX_MM_COPY_UNROLL
 #define CX_MM_COPY_UNROLL 16   // 16-byte loads in flight per thread of a copy group
@@ -193,11 +194,14 @@ __device__ __forceinline__ void reduce_broadcast(char* stage_mc, int64_t a, int6
 // padding is zeroed.
 template <typename T, bool IN>
 __device__ __forceinline__ void copy_slab(const MmParams& p, char* stage, int64_t v0, int64_t v1, int64_t full,
-                                          int64_t nvec, int64_t tid, int64_t tsz, bool user_vec) {
+                                          int64_t nvec, int64_t tid, int64_t tsz, bool user_vec,
+                                          bool body_done = false) {
   constexpr int64_t kPer = 16 / (int64_t)sizeof(T);
   const int64_t vf = min(v1, full);
   T* st = reinterpret_cast<T*>(stage);
-  if (user_vec) {
+  if (body_done) {
+    // the complete 16-byte vectors went through the copy engine; only the ragged end is left
+  } else if (user_vec) {
     if (vf > v0) {
       if (IN) copy_vec(reinterpret_cast<uint4*>(stage) + v0, reinterpret_cast<const uint4*>(p.in) + v0, vf - v0, tid, tsz, false);
       else copy_vec(reinterpret_cast<uint4*>(p.out) + v0, reinterpret_cast<const uint4*>(stage) + v0, vf - v0, tid, tsz, true);
@@ -217,8 +221,61 @@ __device__ __forceinline__ void copy_slab(const MmParams& p, char* stage, int64_
   }
 }
 
+// ---- staging copies by the SM's copy engine --------------------------------------------------------
+// A copy group is a handful of CTAs (most of the grid reduces), and with vector loads and stores
+// one SM moves 20-30 GB/s: the copies, not the switch, set the pace of the staged allreduce.  Here
+// ONE thread per copy CTA drives a ring of kBulkStages chunks in shared memory: bulk load of a
+// chunk (local global memory -> shared memory, counted in bytes on the stage's mbarrier), bulk
+// store of the landed chunk (shared -> local global memory, one bulk group per chunk), the next
+// load into a stage once the store that used it has read it.  Source and destination are this
+// GPU's own memory (the user's vector and this rank's staging block), 16-byte aligned, sizes
+// multiples of 16 bytes; nothing here is a multicast load.  Every mbarrier wait is bounded.
+constexpr int kBulkStages = 6;
+constexpr uint32_t kBulkChunk = 32 * 1024;
+constexpr size_t kBulkSmem = (size_t)kBulkStages * kBulkChunk + 8 * kBulkStages;
+
+// Chunks part, part + parts, ... of [src, src + bytes) go to dst.  `q` counts the loads this thread
+// has issued since the kernel began (stage and mbarrier phase follow from it).  False: a load did
+// not land in time (the copies still in flight were given a bounded chance to).
+__device__ __forceinline__ bool bulk_copy_range(char* dst, const char* src, int64_t bytes, int part, int parts,
+                                                unsigned char* sbuf, uint64_t* bars, uint32_t& q) {
+  const int64_t nchunks = (bytes + kBulkChunk - 1) / kBulkChunk;
+  const int64_t cnt = nchunks > part ? (nchunks - part + parts - 1) / parts : 0;
+  auto off = [&](int64_t i) { return ((int64_t)part + i * parts) * (int64_t)kBulkChunk; };
+  auto len = [&](int64_t i) { return (uint32_t)min((int64_t)kBulkChunk, bytes - off(i)); };
+  auto load = [&](int64_t i) {
+    const uint32_t s = (q + (uint32_t)i) % kBulkStages;
+    cx::mbar_expect_tx(&bars[s], len(i));
+    cx::bulk_load(sbuf + (size_t)s * kBulkChunk, src + off(i), len(i), &bars[s]);
+  };
+  int64_t loaded = 0;
+  for (; loaded < cnt && loaded < kBulkStages - 1; ++loaded) load(loaded);
+  for (int64_t i = 0; i < cnt; ++i) {
+    if (loaded < cnt) {
+      cx::bulk_wait_read_all();        // the store that used this stage (chunk i - 1) has read it
+      load(loaded++);
+    }
+    const uint32_t c = q + (uint32_t)i;
+    if (!cx::mbar_wait_bounded(&bars[c % kBulkStages], (c / kBulkStages) & 1u)) {
+      for (int64_t j = i + 1; j < loaded; ++j) {
+        const uint32_t d = q + (uint32_t)j;
+        cx::mbar_wait_bounded(&bars[d % kBulkStages], (d / kBulkStages) & 1u);
+      }
+      cx::bulk_wait_all();
+      q += (uint32_t)loaded;
+      return false;
+    }
+    cx::bulk_store(dst + off(i), sbuf + (size_t)(c % kBulkStages) * kBulkChunk, len(i));
+    cx::bulk_commit();
+  }
+  cx::bulk_wait_all();                  // the stores are complete: what follows may publish them
+  q += (uint32_t)cnt;
+  return true;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1) mm_allreduce_kernel(const MmParams p) {
+  extern __shared__ __align__(128) unsigned char s_dyn[];
   __shared__ uint32_t s_last, s_bad;
   const uint64_t seq = cx::seq_of(p.seq_cell, p.seq);
   const int64_t bytes = p.n * (int64_t)sizeof(T);
@@ -273,11 +330,37 @@ __global__ void __launch_bounds__(kThreads, 1) mm_allreduce_kernel(const MmParam
   // Without staging (the vector lives in the symmetric heap) only the reduce group exists; it
   // announces "ready" itself and does not leave before every rank's broadcast has landed.
   const int b = blockIdx.x;
+  const bool bulk = p.bulk && user_vec;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_dyn + (size_t)kBulkStages * kBulkChunk);
+  uint32_t bulk_q = 0;
+  bool bulk_ok = true;
+  if (bulk && (b < p.n_in || b >= p.n_in + p.n_red)) {
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < kBulkStages; ++s) cx::mbar_init(&bars[s], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      cx::fence_proxy_async();
+    }
+    __syncthreads();
+  }
+  // a copy that did not land: the launch is marked failed, nothing more is published
+  auto bulk_failed = [&]() {
+    if (p.status) atomicOr(p.status, (uint32_t)CX_ST_TIMEOUT);
+    atomicOr(&p.ctr[0], 1u);
+  };
   if (b < p.n_in) {
     const int64_t tid = (int64_t)b * kThreads + threadIdx.x, tsz = (int64_t)p.n_in * kThreads;
     for (int k = 0; k < p.nslabs; ++k) {
       const int64_t v0 = (int64_t)k * p.slab_vec, v1 = min(nvec, v0 + p.slab_vec);
-      copy_slab<T, true>(p, stage, v0, v1, full, nvec, tid, tsz, user_vec);
+      if (bulk) {
+        const int64_t vf = min(v1, full);
+        if (threadIdx.x == 0 && bulk_ok && vf > v0) {
+          bulk_ok = bulk_copy_range(stage + v0 * 16, reinterpret_cast<const char*>(p.in) + v0 * 16, (vf - v0) * 16, b,
+                                    p.n_in, s_dyn, bars, bulk_q);
+          if (!bulk_ok) bulk_failed();
+          cx::fence_proxy_async();     // the copy engine's writes, then the release of the flag
+        }
+      }
+      copy_slab<T, true>(p, stage, v0, v1, full, nvec, tid, tsz, user_vec, bulk);
       arrive_and_publish(p, 2 * k, p.n_in, 0, seq * 1024 + (k + 1), &s_last);
     }
   } else if (b < p.n_in + p.n_red) {
@@ -301,7 +384,16 @@ __global__ void __launch_bounds__(kThreads, 1) mm_allreduce_kernel(const MmParam
       alive = wait_all(p, 1, seq * 1024 + (k + 1), &s_bad);
       if (!alive) break;
       const int64_t v0 = (int64_t)k * p.slab_vec, v1 = min(nvec, v0 + p.slab_vec);
-      copy_slab<T, false>(p, stage, v0, v1, full, nvec, tid, tsz, user_vec);
+      if (bulk) {
+        const int64_t vf = min(v1, full);
+        if (threadIdx.x == 0 && bulk_ok && vf > v0) {
+          cx::fence_proxy_async();     // the acquire of the flags, then the copy engine's reads
+          bulk_ok = bulk_copy_range(reinterpret_cast<char*>(p.out) + v0 * 16, stage + v0 * 16, (vf - v0) * 16,
+                                    b - p.n_in - p.n_red, n_out, s_dyn, bars, bulk_q);
+          if (!bulk_ok) bulk_failed();
+        }
+      }
+      copy_slab<T, false>(p, stage, v0, v1, full, nvec, tid, tsz, user_vec, bulk);
     }
   }
   leave();
@@ -345,6 +437,29 @@ int cx_barrier_cuda(int rank, int ranks, void* const* flag_ptrs, uint64_t seq, u
 }
 
 extern "C" int64_t cx_mm_counter_bytes(void) { return (int64_t)sizeof(uint32_t) * (2 + 2 * kMaxSlabs + 2); }
+#ifndef CX_MM_BULK_DEFAULT
+#define CX_MM_BULK_DEFAULT 0
+#endif
+
+namespace {
+template <typename T>
+int launch_mm(const MmParams& p, int grid, size_t smem, cudaStream_t s) {
+  auto kern = mm_allreduce_kernel<T>;
+  if (smem) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cx_set_error("cx_mm_allreduce: cudaGetDevice", 0);
+    if (!configured[dev]) {
+      const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return cx_set_error("cx_mm_allreduce: shared memory opt-in", (int)e);
+      configured[dev] = true;
+    }
+  }
+  kern<<<grid, kThreads, smem, s>>>(p);
+  return 0;
+}
+}  // namespace
+
 extern "C" int64_t cx_mm_flag_bytes(void) { return (int64_t)sizeof(uint64_t) * 2 * CX_MAX_PEERS; }
 
 // See cx_common.h.  `stage` / `stage_mc`: this rank's block and its multicast alias (when `in`
@@ -400,13 +515,22 @@ int cx_mm_allreduce_cuda(int dtype, void* out, const void* in, void* stage, void
     p.n_in = copy;
     p.n_red = grid - 2 * copy;
   }
+  // COMPREX_MM_BULK (read per call): the copy groups use the copy engine
+  p.bulk = 0;
+  if (p.staged && !one_shot) {
+    const char* e = getenv("COMPREX_MM_BULK");
+    p.bulk = e ? atoi(e) != 0 : (CX_MM_BULK_DEFAULT != 0);
+  }
+  const size_t smem = p.bulk ? kBulkSmem : 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int rc = 0;
   switch (dtype) {
-    case CX_F32: mm_allreduce_kernel<float><<<grid, kThreads, 0, s>>>(p); break;
-    case CX_BF16: mm_allreduce_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(p); break;
-    case CX_F16: mm_allreduce_kernel<__half><<<grid, kThreads, 0, s>>>(p); break;
+    case CX_F32: rc = launch_mm<float>(p, grid, smem, s); break;
+    case CX_BF16: rc = launch_mm<__nv_bfloat16>(p, grid, smem, s); break;
+    case CX_F16: rc = launch_mm<__half>(p, grid, smem, s); break;
     default: return cx_set_error("cx_mm_allreduce: unsupported dtype", 0);
   }
+  if (rc) return rc;
   cx_note_launch();
   return cx_check_launch("mm_allreduce_kernel");
 }

@@ -512,3 +512,13 @@ def scenario_nvls_paths(rank, world, device):
 def test_switch_paths_match_plain_paths_gpus():
     out = run_ranks(gpu_world(), "scenario_nvls_paths", backend="nccl")
     assert all(o in ("ok", "no multicast") for o in out)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_switch_paths_with_copy_engine_staging_gpus():
+    """The same comparison with the staged allreduce cut into 1 MiB slabs and its copy groups
+    driven by the SM's copy engine (bulk copies through shared memory)."""
+    out = run_ranks(gpu_world(), "scenario_nvls_paths", backend="nccl",
+                    env={"COMPREX_MM_BULK": "1", "COMPREX_MM_SLAB_BYTES": str(1 << 20)})
+    assert all(o in ("ok", "no multicast") for o in out)
