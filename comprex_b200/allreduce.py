@@ -998,13 +998,15 @@ class Comprex_AllToOneAllreduce(_ComprexAllreduceBase):
 # because the phases overlap.
 _COST = {
     "floor_dense_us": 30.0,      # dense one-shot: two launches
-    "floor_two_shot_us": 55.0,   # dense reduce-scatter + allgather / through the switch
+    "floor_two_shot_us": 50.0,   # dense reduce-scatter + allgather / through the switch
     "floor_bigring_us": 40.0,    # threshold + compress + decode
-    "floor_ring_us": 50.0,       # 3 P launches on side streams (one graph), two dependent exchanges,
-    "floor_ring_per_rank_us": 9.0,   # ... plus this per rank
+    "floor_ring_us": 44.0,       # 3 P launches on side streams (one graph), two dependent exchanges,
+    "floor_ring_per_rank_us": 4.5,   # ... plus this per rank (55-85 us measured on 2 / 4 / 8 GPUs)
+    "ring_stream": 0.9,          # the Ring's chunk kernels overlap on side streams and its decode writes
+                                 # only the other ranks' chunks: less streaming time than the BigRing's passes
     "hbm_bpus": 6.0e6,           # streaming kernels
     "link_bpus": 5.5e5,          # into one GPU's port: peer stores and multicast stores alike
-    "dense_link_bpus": 4.3e5,    # dense allreduce of a vector outside the heap (staging copies included)
+    "dense_link_bpus": 7.5e5,    # dense allreduce of a vector outside the heap (staging copies included)
     "pair_us": 4.0e-6,           # decode of one (index, value) pair
 }
 
@@ -1020,8 +1022,9 @@ def schedule_costs(n: int, ratio: float, ranks: int, elem_bytes: int = 4) -> dic
              (c["floor_two_shot_us"] + 2.0 * (p - 1) / p * nb / c["dense_link_bpus"])) + 3.0 * nb / c["hbm_bpus"]
     bigring = (c["floor_bigring_us"] + (8.0 + elem_bytes) * n / c["hbm_bpus"] + (p - 1) * wire / c["link_bpus"]
                + p * pairs * c["pair_us"] + nb / c["hbm_bpus"])
-    ring = (c["floor_ring_us"] + c["floor_ring_per_rank_us"] * p + (8.0 + elem_bytes) * n / c["hbm_bpus"]
-            + 2.0 * (p - 1) / p * wire / c["link_bpus"] + (2.0 * p - 1) / p * pairs * c["pair_us"] + nb / c["hbm_bpus"])
+    ring = (c["floor_ring_us"] + c["floor_ring_per_rank_us"] * p
+            + c["ring_stream"] * ((8.0 + elem_bytes) * n + nb) / c["hbm_bpus"]
+            + 2.0 * (p - 1) / p * wire / c["link_bpus"] + (2.0 * p - 1) / p * pairs * c["pair_us"])
     return {"bigring": dense, "comprex_bigring": bigring, "comprex_ring": ring}
 
 

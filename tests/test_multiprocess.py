@@ -437,12 +437,12 @@ def scenario_nvls_paths(rank, world, device):
     same barriers; nothing here times out on purpose."""
     import comprex_b200 as cx
     os.environ["COMPREX_MM_MIN_RANKS"], os.environ["COMPREX_MM_MIN_BYTES"] = "2", "0"
-    env = cx.GaspiEnvironment(32 << 20, device=device, timeout_ms=5000)
+    env = cx.GaspiEnvironment(192 << 20, device=device, timeout_ms=5000)
     if not env.nvls:
         env.close()
         return "no multicast"
     os.environ["COMPREX_NVLS"] = "0"
-    plain = cx.GaspiEnvironment(32 << 20, device=device, timeout_ms=5000)
+    plain = cx.GaspiEnvironment(192 << 20, device=device, timeout_ms=5000)
     os.environ["COMPREX_NVLS"] = "1"
     assert not plain.nvls
     for dt in (torch.float32, torch.bfloat16, torch.float16):
@@ -486,10 +486,14 @@ def scenario_nvls_paths(rank, world, device):
         outs = {}
         for name, e in (("multicast", env), ("plain", plain)):
             ar = cls(e)
+            # roomy slots (25 % of a vector or chunk for a nominal 2 %): once a slot runs full, which
+            # survivors still fit depends on the order of the warps' reservations, and two runs may
+            # then differ legitimately (with 8 ranks the estimate comes from 125 samples and the 5 %
+            # slots this test once used came within 2 % of overflowing)
             if cls is cx.Comprex_AllToOneAllreduce:
-                ar.setup_connections(n, 1, 0, 0.02, 0.1)
+                ar.setup_connections(n, 1, 0, 0.02, 0.5)
             else:
-                ar.setup_connections(n, 1, 0.02, 0.1, **kw)
+                ar.setup_connections(n, 1, 0.02, 0.5, **kw)
             torch.manual_seed(77 + rank)
             x = torch.randn(n, device=device)
             res = []
@@ -497,6 +501,8 @@ def scenario_nvls_paths(rank, world, device):
                 y = x.clone()
                 ar.apply(y)
                 res.append(y)
+                st = ar.stats()
+                assert not (st and st.get("status", 0) & 4), (cls.__name__, name, "a slot overflowed", st)
             e.flush()
             outs[name] = res
         assert all(torch.equal(a, b) for a, b in zip(outs["multicast"], outs["plain"])), cls.__name__
