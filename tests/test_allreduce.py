@@ -204,3 +204,60 @@ def test_apply_checks_size_and_accepts_numpy():
     assert np.array_equal(v.reshape(-1), np.arange(100, dtype=np.float32))
     assert ar.getSize() == 100
     env.close()
+
+
+def test_select_schedule_follows_the_measured_regimes():
+    """The cost model ranks the three schedules the way the sweeps on 2, 4 and 8 B200 did: tiny and
+    dense vectors go to the dense kernels, the compressed BigRing wins while (P-1) payloads are
+    small, the compressed Ring for large vectors, high ratios and many peers."""
+    from comprex_b200.allreduce import schedule_costs, select_schedule
+    assert select_schedule(1 << 16, 0.01, 8) == "bigring"
+    assert select_schedule(1 << 16, 0.001, 2) == "bigring"
+    assert select_schedule(1 << 24, 1.0, 8) == "bigring"            # nothing to compress
+    assert select_schedule(1 << 20, 0.01, 4) == "comprex_bigring"
+    assert select_schedule(1 << 24, 0.01, 2) == "comprex_bigring"
+    assert select_schedule(1 << 24, 0.01, 8) == "comprex_bigring"
+    assert select_schedule(1 << 24, 0.1, 8) == "comprex_ring"
+    assert select_schedule(1 << 28, 0.01, 8) == "comprex_ring"
+    assert select_schedule(1 << 28, 0.1, 2) == "comprex_ring"
+    assert select_schedule(1000, 0.01, 1) == "comprex_bigring"      # a single rank exchanges nothing
+    # more peers cost the BigRing (P-1) payloads, the Ring 2 (P-1)/P of one
+    c4, c8 = schedule_costs(1 << 26, 0.1, 4), schedule_costs(1 << 26, 0.1, 8)
+    assert c8["comprex_bigring"] - c4["comprex_bigring"] > 4 * (c8["comprex_ring"] - c4["comprex_ring"])
+    # a 16-bit vector halves the dense traffic, not the pairs
+    assert schedule_costs(1 << 26, 0.01, 8, 2)["bigring"] < 0.6 * schedule_costs(1 << 26, 0.01, 8, 4)["bigring"]
+
+
+@pytest.mark.parametrize("n,ratio,want", [(3000, 0.01, "bigring"), (1 << 20, 0.01, "comprex_bigring")])
+def test_auto_allreduce_is_the_chosen_schedule(device, n, ratio, want):
+    """AutoAllreduce sets up the schedule select_schedule names and gives its bits."""
+    results = {}
+    for kind in ("auto", "explicit"):
+        w = cx.LoopbackWorld(3, device=device, timeout_ms=2000)
+        ars = []
+        for e in w.envs:
+            if kind == "auto":
+                a = cx.AutoAllreduce(e)
+                a.setup_connections(n, 1, ratio, 3.0)
+                assert a.choice == want and a.compressed == (want != "bigring")
+                ars.append(a.impl)
+            elif want == "bigring":
+                a = cx.BigRingAllreduce(e)
+                a.setup_connections(n, 1, ordered=True)
+                ars.append(a)
+            else:
+                a = cx.Comprex_BigRingAllreduce(e)
+                a.setup_connections(n, 1, ratio, 3.0, consistent=True)
+                ars.append(a)
+        out = []
+        for step in range(3):
+            torch.manual_seed(10 + step)
+            xs = [torch.randn(n).to(device) for _ in range(3)]
+            w.run(ars, "apply", [(x,) for x in xs])
+            assert all(torch.equal(x, xs[0]) for x in xs[1:])       # replicas agree in both cases
+            out.append(xs[0].cpu())
+        results[kind] = out
+        w.close()
+    for a, b in zip(results["auto"], results["explicit"]):
+        assert torch.equal(a, b)
+
