@@ -249,7 +249,7 @@ template <typename T>
 __device__ __forceinline__ void dense_reduce_body(const ReduceParams& p) {
   __shared__ uint32_t s_last;
   if (!wait_dense(p.src, p.timeout_ns, p.status, p.dtype, p.seq_cell)) {
-    // The verdict is per CTA, the bookkeeping is per grid: a CTA that gave up still arrives at
+    // The decision is per CTA, the bookkeeping is per grid: a CTA that gave up still arrives at
     // the completion counter of a pushing launch and marks the launch as failed, so that the
     // CTA arriving last publishes nothing and hands clean counters to the next launch.
     if (!p.has_push) return;
